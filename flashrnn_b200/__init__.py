@@ -1,0 +1,9 @@
+"""B200-native (sm_100a) backend for FlashRNN's fused recurrence.
+
+Public surface = the reference's: ``flashrnn``, ``FlashRNNConfig``, ``flashrnn_torch``
+(flashrnn/__init__.py:2-5 of the reference), running hand-written CUDA through a C ABI.
+"""
+
+from .functional import BACKEND, SIZES, FlashRNNConfig, flashrnn, flashrnn_torch, poll_errors
+
+__all__ = ["BACKEND", "SIZES", "FlashRNNConfig", "flashrnn", "flashrnn_torch", "poll_errors"]

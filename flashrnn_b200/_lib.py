@@ -1,0 +1,93 @@
+"""ctypes binding of ``libflashrnn_b200.so`` (the C ABI declared in ``include/flashrnn_b200.h``).
+
+There is no fallback: if the shared library is missing or does not export every entry point the
+import of the compute path fails with an explicit error.
+"""
+
+from __future__ import annotations
+
+import ctypes
+from ctypes import POINTER, c_int, c_int64, c_void_p
+from pathlib import Path
+
+LIB_PATH = Path(__file__).resolve().parent / "lib" / "libflashrnn_b200.so"
+
+CELLS = {"lstm": 0, "slstm": 1, "gru": 2, "elman": 3}
+
+ERROR_TEXT = {
+    -1: "unknown cell",
+    -2: "shape not supported by the sm_100a kernel family (see frnn_b200_plan)",
+    -3: "tensor-memory budget exceeded",
+    -4: "TMA descriptor could not be built",
+    -5: "bad argument",
+    101: "recurrent operand of a step never arrived",
+    102: "tensor-core completion barrier timed out",
+    103: "TMA input stage never filled",
+    104: "TMA input stage never released",
+    105: "epilogue barrier timed out",
+    106: "partial dh never arrived",
+    107: "dg operand barrier timed out",
+}
+
+
+class Plan(ctypes.Structure):
+    """Mirror of ``frnn_b200_plan_t``."""
+
+    _fields_ = [
+        ("gates_r", c_int), ("gates_w", c_int), ("gates_b", c_int), ("states", c_int), ("cache_gates", c_int),
+        ("unit", c_int), ("cluster", c_int), ("batch_tile", c_int), ("n_btiles", c_int), ("grid_ctas", c_int),
+        ("supported", c_int),
+        ("cache_bytes", c_int64), ("hbf_bytes", c_int64), ("dgr_bytes", c_int64), ("dbpart_bytes", c_int64),
+        ("wgrad_work_bytes", c_int64), ("wgrad_ksplit", c_int),
+    ]
+
+
+# name -> (restype, argtypes); must list every function declared in include/flashrnn_b200.h
+SIGNATURES = {
+    "frnn_b200_version": (c_int, []),
+    "frnn_b200_plan": (c_int, [c_int, c_int, c_int, c_int, c_int, POINTER(Plan)]),
+    "frnn_b200_forward": (c_int, [c_int, c_void_p, c_int, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p,
+                                  c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_int, c_int, c_void_p, c_void_p]),
+    "frnn_b200_backward": (c_int, [c_int, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p,
+                                   c_int, c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_int, c_int,
+                                   c_void_p, c_void_p]),
+    "frnn_b200_wgrad": (c_int, [c_int, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_int,
+                                c_int, c_int, c_void_p, c_void_p]),
+}
+
+_lib = None
+
+
+def load() -> ctypes.CDLL:
+    """Load the library once; raise if it is absent or incomplete."""
+    global _lib
+    if _lib is not None:
+        return _lib
+    if not LIB_PATH.exists():
+        raise RuntimeError(
+            f"{LIB_PATH} is missing: build it with `python -m flashrnn_b200.build` "
+            "(there is no CPU or PyTorch fallback for the recurrence)"
+        )
+    lib = ctypes.CDLL(str(LIB_PATH))
+    for name, (restype, argtypes) in SIGNATURES.items():
+        try:
+            fn = getattr(lib, name)
+        except AttributeError as exc:  # pragma: no cover - build problem
+            raise RuntimeError(f"{LIB_PATH} does not export {name}") from exc
+        fn.restype = restype
+        fn.argtypes = argtypes
+    _lib = lib
+    return lib
+
+
+def plan(cell: str, B: int, T: int, N: int, D: int) -> Plan:
+    out = Plan()
+    rc = load().frnn_b200_plan(CELLS[cell], B, T, N, D, ctypes.byref(out))
+    if rc != 0:
+        raise ValueError(f"frnn_b200_plan failed: {ERROR_TEXT.get(rc, rc)}")
+    return out
+
+
+def check(rc: int, what: str) -> None:
+    if rc != 0:
+        raise RuntimeError(f"{what} failed with code {rc}: {ERROR_TEXT.get(rc, 'CUDA error')}")

@@ -1,0 +1,178 @@
+// extern "C" boundary of the library: shape planning, argument checks, kernel dispatch.
+#include "../../include/flashrnn_b200.h"
+
+#include <mutex>
+
+#include "frnn_common.cuh"
+
+namespace frnn {
+
+int forward_dispatch(int cell, const FwdParams& p, const void* wx, int wx_bf16, int bv, int unit, cudaStream_t s);
+int backward_dispatch(int cell, const BwdParams& p, const float* cache, const float* history, const float* initial,
+                      const float* d_history, int wx_bf16, int bv, int unit, cudaStream_t s);
+int wgrad_plan(int gr, int B, int T, int N, int D, int* np_out, int* ksplit_out, int* cps_out);
+int wgrad_launch(int gr, int gb, const __nv_bfloat16* dgr, const __nv_bfloat16* hbf, const float* db_part, int n_btiles,
+                 float* dR, float* db, float* work, int* err, int B, int T, int N, int D, cudaStream_t s);
+
+namespace {
+
+using EncodeTiledFn = CUresult (*)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*,
+                                   const cuuint64_t*, const cuuint32_t*, const cuuint32_t*, CUtensorMapInterleave,
+                                   CUtensorMapSwizzle, CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
+
+EncodeTiledFn encode_tiled_fn() {
+  static EncodeTiledFn fn = nullptr;
+  static std::once_flag once;
+  std::call_once(once, [] {
+    void* sym = nullptr;
+    cudaDriverEntryPointQueryResult q;
+    if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &sym, cudaEnableDefault, &q) == cudaSuccess &&
+        q == cudaDriverEntryPointSuccess)
+      fn = reinterpret_cast<EncodeTiledFn>(sym);
+  });
+  return fn;
+}
+
+struct CellCounts {
+  int gr, gw, gb, s, gc;
+};
+bool cell_counts(int cell, CellCounts* c) {
+  switch (cell) {
+    case kLSTM: *c = {4, 4, 4, 2, 4}; return true;
+    case kSLSTM: *c = {4, 4, 4, 4, 4}; return true;
+    case kGRU: *c = {3, 3, 4, 1, 4}; return true;
+    case kElman: *c = {1, 1, 1, 1, 0}; return true;
+    default: return false;
+  }
+}
+
+}  // namespace
+
+int make_tensor_map(CUtensorMap* map, const void* base, int elem_bytes, int rank, const uint64_t* dims,
+                    const uint32_t* box) {
+  EncodeTiledFn fn = encode_tiled_fn();
+  if (fn == nullptr) return -4;
+  cuuint64_t gdims[5];
+  cuuint64_t gstrides[4];
+  cuuint32_t gbox[5], estr[5];
+  uint64_t stride = static_cast<uint64_t>(elem_bytes);
+  for (int i = 0; i < rank; ++i) {
+    gdims[i] = dims[i];
+    gbox[i] = box[i];
+    estr[i] = 1;
+    stride *= dims[i];
+    if (i < rank - 1) gstrides[i] = stride;
+  }
+  const CUtensorMapDataType dt = elem_bytes == 4 ? CU_TENSOR_MAP_DATA_TYPE_FLOAT32 : CU_TENSOR_MAP_DATA_TYPE_BFLOAT16;
+  const CUresult r = fn(map, dt, static_cast<cuuint32_t>(rank), const_cast<void*>(base), gdims, gstrides, gbox, estr,
+                        CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_NONE, CU_TENSOR_MAP_L2_PROMOTION_L2_128B,
+                        CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+  return r == CUDA_SUCCESS ? 0 : -4;
+}
+
+}  // namespace frnn
+
+using namespace frnn;
+
+extern "C" int frnn_b200_version(void) { return 1000; }
+
+extern "C" int frnn_b200_plan(int cell, int B, int T, int N, int D, frnn_b200_plan_t* out) {
+  if (out == nullptr) return -5;
+  CellCounts c;
+  if (!cell_counts(cell, &c)) return -1;
+  if (B < 1 || T < 1 || N < 1 || D < 1) return -5;
+  *out = frnn_b200_plan_t{};
+  out->gates_r = c.gr; out->gates_w = c.gw; out->gates_b = c.gb; out->states = c.s; out->cache_gates = c.gc;
+  out->unit = (D % 32 == 0) ? 32 : 16;
+  out->cluster = D / out->unit;
+  out->batch_tile = B <= 8 ? 8 : 16;
+  out->n_btiles = (B + out->batch_tile - 1) / out->batch_tile;
+  out->grid_ctas = N * out->n_btiles * out->cluster;
+  const int bt = 16;
+  const int rows = c.gr * out->unit;
+  const int mt = (rows + 127) / 128;
+  const int fwd_cols = ((mt * bt + 31) / 32 * 32) + mt * (D / 2);
+  const int mtb = (D + 127) / 128;
+  const int bwd_cols = ((mtb * bt + 31) / 32 * 32) + mtb * (rows / 2);
+  out->supported = (D % 16 == 0) && out->cluster <= 16 && fwd_cols <= 512 && bwd_cols <= 512;
+  const int64_t btnd = static_cast<int64_t>(B) * T * N * D;
+  out->cache_bytes = btnd * c.gc * 4;
+  out->hbf_bytes = static_cast<int64_t>(B) * (T + 1) * N * D * 2;
+  out->dgr_bytes = btnd * c.gr * 2;
+  out->dbpart_bytes = static_cast<int64_t>(out->n_btiles) * c.gb * N * D * 4;
+  int np = 0, ksplit = 1, cps = 0;
+  if (D % 16 == 0 && wgrad_plan(c.gr, B, T, N, D, &np, &ksplit, &cps) == 0) {
+    out->wgrad_ksplit = ksplit;
+    out->wgrad_work_bytes = ksplit > 1 ? static_cast<int64_t>(ksplit) * c.gr * N * D * D * 4 : 0;
+  } else {
+    out->supported = 0;
+  }
+  return 0;
+}
+
+extern "C" int frnn_b200_forward(int cell, const void* wx, int wx_bf16, const void* r_bf16, const float* bias,
+                                 const float* initial, float* history, float* carry, float* cache, void* hbf, int B,
+                                 int T, int N, int D, int slstm_zero_first, int wait_limit_ms, int* err,
+                                 void* stream) {
+  frnn_b200_plan_t plan;
+  const int rc = frnn_b200_plan(cell, B, T, N, D, &plan);
+  if (rc != 0) return rc;
+  if (!plan.supported) return -2;
+  if (!wx || !r_bf16 || !bias || !initial || !history || !carry || !err) return -5;
+  FwdParams p{};
+  p.R = static_cast<const __nv_bfloat16*>(r_bf16);
+  p.bias = bias;
+  p.initial = initial;
+  p.history = history;
+  p.carry = carry;
+  p.cache = cache;
+  p.hbf = static_cast<__nv_bfloat16*>(hbf);
+  p.err = err;
+  p.B = B; p.T = T; p.N = N; p.D = D;
+  p.C = plan.cluster;
+  p.wx_box_b = plan.batch_tile;  // rows past B are filled with zeros by TMA
+  p.slstm_zero_first = slstm_zero_first;
+  p.wait_limit_ns = (wait_limit_ms > 0 ? static_cast<unsigned long long>(wait_limit_ms) : 2000ull) * 1000000ull;
+  return forward_dispatch(cell, p, wx, wx_bf16, plan.batch_tile, plan.unit, static_cast<cudaStream_t>(stream));
+}
+
+extern "C" int frnn_b200_backward(int cell, const float* cache, const float* history, const float* initial,
+                                  const void* r_bf16, const float* d_history, const float* d_carry, void* dwx,
+                                  int wx_bf16, void* dgr, float* d_initial, float* db_part, int B, int T, int N, int D,
+                                  int slstm_zero_first, int wait_limit_ms, int* err, void* stream) {
+  frnn_b200_plan_t plan;
+  const int rc = frnn_b200_plan(cell, B, T, N, D, &plan);
+  if (rc != 0) return rc;
+  if (!plan.supported) return -2;
+  if ((!cache && plan.cache_gates > 0) || !history || !initial || !r_bf16 || !d_history || !d_carry || !dwx || !dgr ||
+      !d_initial || !db_part || !err)
+    return -5;
+  BwdParams p{};
+  p.R = static_cast<const __nv_bfloat16*>(r_bf16);
+  p.d_carry = d_carry;
+  p.dwx = dwx;
+  p.dgr = static_cast<__nv_bfloat16*>(dgr);
+  p.d_initial = d_initial;
+  p.db_part = db_part;
+  p.err = err;
+  p.B = B; p.T = T; p.N = N; p.D = D;
+  p.C = plan.cluster;
+  p.box_b = plan.batch_tile;  // rows past B are filled with zeros by TMA
+  p.slstm_zero_first = slstm_zero_first;
+  p.wait_limit_ns = (wait_limit_ms > 0 ? static_cast<unsigned long long>(wait_limit_ms) : 2000ull) * 1000000ull;
+  return backward_dispatch(cell, p, cache, history, initial, d_history, wx_bf16, plan.batch_tile, plan.unit,
+                           static_cast<cudaStream_t>(stream));
+}
+
+extern "C" int frnn_b200_wgrad(int cell, const void* dgr, const void* hbf, const float* db_part, float* dR, float* db,
+                               float* work, int B, int T, int N, int D, int* err, void* stream) {
+  frnn_b200_plan_t plan;
+  const int rc = frnn_b200_plan(cell, B, T, N, D, &plan);
+  if (rc != 0) return rc;
+  if (!plan.supported) return -2;
+  if (!dgr || !hbf || !db_part || !dR || !db || !err) return -5;
+  if (plan.wgrad_work_bytes > 0 && !work) return -5;
+  return wgrad_launch(plan.gates_r, plan.gates_b, static_cast<const __nv_bfloat16*>(dgr),
+                      static_cast<const __nv_bfloat16*>(hbf), db_part, plan.n_btiles, dR, db, work, err, B, T, N, D,
+                      static_cast<cudaStream_t>(stream));
+}

@@ -1,0 +1,165 @@
+// Per-cell pointwise arithmetic of the recurrence, forward and backward, in fp32.
+//
+// The formulas restate the step of `recurrence()` in the reference
+// (flashrnn/flashrnn2/reference.py:72-114) and the derivative torch autograd forms for it.
+// Gate order is (i, f, z, o) for lstm/slstm; gru uses W-gates (reset, update, candidate-input),
+// R-gates (candidate-recurrent, reset, update) and four biases (reference.py:84-89).
+#pragma once
+
+#include <cuda_runtime.h>
+
+namespace frnn {
+
+enum : int { kLSTM = 0, kSLSTM = 1, kGRU = 2, kElman = 3 };
+
+// GR: gates fed by R*h, GW: gates in Wx, GB: bias gates, S: states, GC: values cached per
+// (batch, step, unit) by a training forward for the backward pass.
+template <int CELL> struct CellTraits;
+template <> struct CellTraits<kLSTM>  { static constexpr int GR = 4, GW = 4, GB = 4, S = 2, GC = 4; };
+template <> struct CellTraits<kSLSTM> { static constexpr int GR = 4, GW = 4, GB = 4, S = 4, GC = 4; };
+template <> struct CellTraits<kGRU>   { static constexpr int GR = 3, GW = 3, GB = 4, S = 1, GC = 4; };
+template <> struct CellTraits<kElman> { static constexpr int GR = 1, GW = 1, GB = 1, S = 1, GC = 1; };
+
+__device__ __forceinline__ float sigmoid_f(float x) { return __frcp_rn(1.0f + __expf(-x)); }
+__device__ __forceinline__ float tanh_f(float x) {
+  // 1 - 2/(1+e^{2x}); saturates correctly at +-1 when e^{2x} over/underflows.
+  return 1.0f - 2.0f * __frcp_rn(1.0f + __expf(2.0f * x));
+}
+__device__ __forceinline__ float logsigmoid_f(float x) {
+  return fminf(x, 0.0f) - __logf(1.0f + __expf(-fabsf(x)));
+}
+
+// ---------------------------------------------------------------------------------------------
+// forward: st holds the previous state on entry and the new state on return.
+// ry = R*round_bf16(h_prev) for the GR recurrent gates, wx = this step's input gates.
+// cache receives what cell_backward needs (nothing useful for Elman).
+// ---------------------------------------------------------------------------------------------
+template <int CELL>
+__device__ __forceinline__ void cell_forward(const float* ry, const float* wx, const float* b,
+                                             float* st, float* cache, bool slstm_take_i) {
+  if constexpr (CELL == kLSTM) {
+    const float si = sigmoid_f((wx[0] + ry[0]) + b[0]);
+    const float sf = sigmoid_f((wx[1] + ry[1]) + b[1]);
+    const float tz = tanh_f((wx[2] + ry[2]) + b[2]);
+    const float so = sigmoid_f((wx[3] + ry[3]) + b[3]);
+    const float c = sf * st[1] + si * tz;
+    st[0] = so * tanh_f(c);
+    st[1] = c;
+    cache[0] = si; cache[1] = sf; cache[2] = tz; cache[3] = so;
+  } else if constexpr (CELL == kSLSTM) {
+    const float i = (wx[0] + ry[0]) + b[0];
+    const float f = (wx[1] + ry[1]) + b[1];
+    const float z = (wx[2] + ry[2]) + b[2];
+    const float o = (wx[3] + ry[3]) + b[3];
+    const float logf = logsigmoid_f(f) + st[3];
+    const float m = slstm_take_i ? i : fmaxf(i, logf);
+    const float ig = __expf(i - m);
+    const float fg = __expf(logf - m);
+    const float c = fg * st[1] + ig * tanh_f(z);
+    const float n = fmaxf(fg * st[2] + ig, 1.0f);
+    st[0] = sigmoid_f(o) * c / n;
+    st[1] = c; st[2] = n; st[3] = m;
+    cache[0] = i; cache[1] = f; cache[2] = z; cache[3] = o;
+  } else if constexpr (CELL == kGRU) {
+    const float cand = ry[0] + b[0];
+    const float r = sigmoid_f((wx[0] + ry[1]) + b[1]);
+    const float u = sigmoid_f((wx[1] + ry[2]) + b[2]);
+    const float v = tanh_f((wx[2] + b[3]) + r * cand);
+    st[0] = u * st[0] + (1.0f - u) * v;
+    cache[0] = cand; cache[1] = r; cache[2] = u; cache[3] = v;
+  } else {
+    st[0] = tanh_f((wx[0] + ry[0]) + b[0]);
+    cache[0] = 0.0f;
+  }
+}
+
+// ---------------------------------------------------------------------------------------------
+// backward of one step for one (batch, unit).
+//   ds    in : total gradient w.r.t. the NEW state (history gradient + everything carried back,
+//              including the R path into h);
+//         out: gradient w.r.t. the PREVIOUS state through the pointwise path only (the R path
+//              dgr * R is added by the caller).
+//   dgr / dgw / dgb: gradients of the recurrent pre-activations, the Wx gates and the biases.
+// slstm: follows autograd exactly, i.e. the stabiliser m carries a gradient and max(., 1) /
+// max(i, logf) split a tie 0.5 / 0.5 as torch.maximum does.
+// ---------------------------------------------------------------------------------------------
+template <int CELL>
+__device__ __forceinline__ void cell_backward(const float* cache, const float* sp, const float* sn,
+                                              float* ds, float* dgr, float* dgw, float* dgb,
+                                              bool slstm_take_i) {
+  if constexpr (CELL == kLSTM) {
+    const float si = cache[0], sf = cache[1], tz = cache[2], so = cache[3];
+    const float tc = tanh_f(sn[1]);
+    const float dh = ds[0];
+    const float dc = ds[1] + dh * so * (1.0f - tc * tc);
+    const float d_o = dh * tc * so * (1.0f - so);
+    const float d_f = dc * sp[1] * sf * (1.0f - sf);
+    const float d_i = dc * tz * si * (1.0f - si);
+    const float d_z = dc * si * (1.0f - tz * tz);
+    ds[0] = 0.0f;
+    ds[1] = dc * sf;
+    dgr[0] = d_i; dgr[1] = d_f; dgr[2] = d_z; dgr[3] = d_o;
+    dgw[0] = d_i; dgw[1] = d_f; dgw[2] = d_z; dgw[3] = d_o;
+    dgb[0] = d_i; dgb[1] = d_f; dgb[2] = d_z; dgb[3] = d_o;
+  } else if constexpr (CELL == kSLSTM) {
+    const float i = cache[0], f = cache[1], z = cache[2], o = cache[3];
+    const float c_p = sp[1], n_p = sp[2], m_p = sp[3];
+    const float c_n = sn[1], n_n = sn[2], m_n = sn[3];
+    const float so = sigmoid_f(o);
+    const float tz = tanh_f(z);
+    const float sgf = sigmoid_f(f);
+    const float logf = logsigmoid_f(f) + m_p;
+    const float ig = __expf(i - m_n);
+    const float fg = __expf(logf - m_n);
+    const float dh = ds[0];
+    const float inv_n = 1.0f / n_n;
+    const float dc = ds[1] + dh * so * inv_n;
+    const float dn = ds[2] - dh * so * c_n * inv_n * inv_n;
+    const float d_o = dh * (c_n * inv_n) * so * (1.0f - so);
+    const float pre_n = fg * n_p + ig;
+    const float mask = pre_n > 1.0f ? 1.0f : (pre_n == 1.0f ? 0.5f : 0.0f);
+    const float dpre = dn * mask;
+    const float d_ig = dc * tz + dpre;
+    const float d_fg = dc * c_p + dpre * n_p;
+    const float d_z = dc * ig * (1.0f - tz * tz);
+    float d_i = d_ig * ig;
+    float d_logf = d_fg * fg;
+    const float dm = ds[3] - d_i - d_logf;
+    if (slstm_take_i) {
+      d_i += dm;
+    } else if (i > logf) {
+      d_i += dm;
+    } else if (i < logf) {
+      d_logf += dm;
+    } else {
+      d_i += 0.5f * dm;
+      d_logf += 0.5f * dm;
+    }
+    const float d_f = d_logf * (1.0f - sgf);
+    ds[0] = 0.0f;
+    ds[1] = dc * fg;
+    ds[2] = dpre * fg;
+    ds[3] = d_logf;
+    dgr[0] = d_i; dgr[1] = d_f; dgr[2] = d_z; dgr[3] = d_o;
+    dgw[0] = d_i; dgw[1] = d_f; dgw[2] = d_z; dgw[3] = d_o;
+    dgb[0] = d_i; dgb[1] = d_f; dgb[2] = d_z; dgb[3] = d_o;
+  } else if constexpr (CELL == kGRU) {
+    const float cand = cache[0], r = cache[1], u = cache[2], v = cache[3];
+    const float dh = ds[0];
+    const float d_u = dh * (sp[0] - v) * u * (1.0f - u);
+    const float d_v = dh * (1.0f - u) * (1.0f - v * v);
+    const float d_r = d_v * cand * r * (1.0f - r);
+    const float d_cand = d_v * r;
+    ds[0] = dh * u;
+    dgr[0] = d_cand; dgr[1] = d_r; dgr[2] = d_u;
+    dgw[0] = d_r; dgw[1] = d_u; dgw[2] = d_v;
+    dgb[0] = d_cand; dgb[1] = d_r; dgb[2] = d_u; dgb[3] = d_v;
+  } else {
+    const float h = sn[0];
+    const float d = ds[0] * (1.0f - h * h);
+    ds[0] = 0.0f;
+    dgr[0] = d; dgw[0] = d; dgb[0] = d;
+  }
+}
+
+}  // namespace frnn

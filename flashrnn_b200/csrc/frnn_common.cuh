@@ -1,0 +1,127 @@
+// Shared declarations of the recurrence kernels: launch plan, kernel parameter blocks,
+// small vector helpers and the host-side TMA descriptor builder.
+#pragma once
+
+#include <cuda.h>
+#include <cuda_bf16.h>
+#include <cuda_runtime.h>
+#include <stdint.h>
+
+#include "cells.cuh"
+#include "sm100_ptx.cuh"
+
+namespace frnn {
+
+// Error codes written to err[0] by a kernel whose bounded wait ran out (0 = ok).
+enum : int {
+  kErrWaitH = 101,      // forward: recurrent operand of a step never arrived
+  kErrWaitMma = 102,    // tensor-core completion barrier
+  kErrWaitWx = 103,     // TMA stage never filled
+  kErrWaitEmpty = 104,  // TMA stage never released
+  kErrWaitEpi = 105,    // epilogue-internal barrier
+  kErrWaitPart = 106,   // backward: partial dh never arrived
+  kErrWaitDg = 107,     // backward: dg operand barrier
+};
+
+// How one (head, batch tile) group is laid out over a thread-block cluster.
+struct Plan {
+  int cell;
+  int unit;        // U: hidden units owned by one CTA
+  int cluster;     // C = D / U CTAs per group
+  int batch_tile;  // BV: batch rows per group
+  int n_btiles;    // ceil(B / BV)
+  int grid;        // N * n_btiles * C
+  int smem_fwd, smem_bwd;
+  int tmem_cols_fwd, tmem_cols_bwd;
+  int supported;   // 0 when the shape does not fit this kernel family
+};
+
+struct FwdParams {
+  const __nv_bfloat16* R;  // [GR][N][D][D] (out, in)
+  const float* bias;       // [GB][N][D]
+  const float* initial;    // [S][B][1][N][D]
+  float* history;          // [S][B][T][N][D]
+  float* carry;            // [S][B][1][N][D]
+  float* cache;            // [B][T][GC][N][D] or null (inference)
+  __nv_bfloat16* hbf;      // [B][T+1][N][D] bf16 copy of h_{-1..T-1}, or null
+  int* err;                // device int[4]
+  int B, T, N, D;
+  int C;
+  int wx_box_b;            // batch extent of the Wx TMA box
+  int slstm_zero_first;
+  unsigned long long wait_limit_ns;
+};
+
+struct BwdParams {
+  const __nv_bfloat16* R;   // [GR][N][D][D]
+  const float* d_carry;     // [S][B][1][N][D]
+  void* dwx;                // [B][T][GW][N][D] in the Wx dtype
+  __nv_bfloat16* dgr;       // [B][T][GR][N][D] bf16 operand of the dR contraction
+  float* d_initial;         // [S][B][1][N][D]
+  float* db_part;           // [n_btiles][GB][N][D]
+  int* err;
+  int B, T, N, D;
+  int C;
+  int box_b;
+  int slstm_zero_first;
+  unsigned long long wait_limit_ns;
+};
+
+template <int N>
+__device__ __forceinline__ void ld_f32_vec(const float* p, float* v) {
+  if constexpr (N % 4 == 0) {
+#pragma unroll
+    for (int i = 0; i < N; i += 4) {
+      const float4 t = *reinterpret_cast<const float4*>(p + i);
+      v[i] = t.x; v[i + 1] = t.y; v[i + 2] = t.z; v[i + 3] = t.w;
+    }
+  } else if constexpr (N % 2 == 0) {
+#pragma unroll
+    for (int i = 0; i < N; i += 2) {
+      const float2 t = *reinterpret_cast<const float2*>(p + i);
+      v[i] = t.x; v[i + 1] = t.y;
+    }
+  } else {
+#pragma unroll
+    for (int i = 0; i < N; ++i) v[i] = p[i];
+  }
+}
+template <int N>
+__device__ __forceinline__ void st_f32_vec(float* p, const float* v) {
+  if constexpr (N % 4 == 0) {
+#pragma unroll
+    for (int i = 0; i < N; i += 4)
+      *reinterpret_cast<float4*>(p + i) = make_float4(v[i], v[i + 1], v[i + 2], v[i + 3]);
+  } else if constexpr (N % 2 == 0) {
+#pragma unroll
+    for (int i = 0; i < N; i += 2) *reinterpret_cast<float2*>(p + i) = make_float2(v[i], v[i + 1]);
+  } else {
+#pragma unroll
+    for (int i = 0; i < N; ++i) p[i] = v[i];
+  }
+}
+template <int N>
+__device__ __forceinline__ void ld_bf16_vec(const __nv_bfloat16* p, float* v) {
+  static_assert(N % 2 == 0, "pairs");
+#pragma unroll
+  for (int i = 0; i < N; i += 2) {
+    const float2 t = __bfloat1622float2(*reinterpret_cast<const __nv_bfloat162*>(p + i));
+    v[i] = t.x; v[i + 1] = t.y;
+  }
+}
+__device__ __forceinline__ uint32_t pack_bf16x2(float lo, float hi) {
+  const __nv_bfloat162 t = __floats2bfloat162_rn(lo, hi);
+  return *reinterpret_cast<const uint32_t*>(&t);
+}
+
+// Byte offset of element (row, k) inside an un-swizzled K-major UMMA operand tile of `rows`
+// rows: 8x8 core matrices, K-adjacent core matrices `rows*16` bytes apart.
+__host__ __device__ __forceinline__ uint32_t kmajor_offset(int rows, int row, int k) {
+  return static_cast<uint32_t>((k >> 3) * (rows * 16) + (row >> 3) * 128 + (row & 7) * 16 + (k & 7) * 2);
+}
+
+// Host: build a tiled tensor map (no swizzle, no interleave). dims/box innermost first.
+int make_tensor_map(CUtensorMap* map, const void* base, int elem_bytes, int rank, const uint64_t* dims,
+                    const uint32_t* box);
+
+}  // namespace frnn

@@ -1,0 +1,469 @@
+// Persistent reverse-time (BPTT) recurrence for sm_100a.
+//
+// Same decomposition as the forward kernel: a cluster of C CTAs per (head, batch tile), CTA
+// `rank` owns U hidden units and keeps the SAME GR*U rows of R resident in tensor memory, but
+// transposed: operand A is R_slice^T [D x GR*U]. Per step t = T-1 .. 0 each CTA
+//   1. sums the C partial dh_t contributions that arrived for its units (fixed order), adds the
+//      history gradient and the pointwise carry, runs the cell backward -> dg_t,
+//   2. streams dg_t out (dWx, bf16 copy for the dR contraction), keeps db in registers,
+//   3. multiplies: partial dh_{t-1}[all D units] = R_slice^T * round_bf16(dg_t) on tcgen05,
+//   4. scatters the partial rows to the CTAs that own those units (async DSMEM stores that
+//      complete on the owner's mbarrier).
+// No atomics anywhere; dR itself is a separate contraction over (b, t).
+//
+// Replaces FLASHRNNCellFusedBackward (flashrnn/flashrnn/fused/flashrnn_fused_backward.cu:130-625).
+#include "frnn_common.cuh"
+
+namespace frnn {
+
+namespace {
+
+constexpr int kEpiThreads = 128;
+constexpr int kBwdThreads = 192;
+constexpr int kStages = 4;
+
+template <int CELL, int BV, int U, bool WX_BF16>
+struct BwdCfg {
+  using CT = CellTraits<CELL>;
+  static constexpr int BT = BV < 16 ? 16 : BV;
+  static constexpr int ROWS = CT::GR * U;  // K of the backward contraction
+  static constexpr int IPT = (U * BV / kEpiThreads) < 2 ? 2 : (U * BV / kEpiThreads);
+  static constexpr int TPB = U / IPT;
+  static constexpr int GCL = CELL == kElman ? 0 : CT::GC;  // cached gates actually loaded
+  static constexpr int STAGE_FLOATS = (GCL + 3 * CT::S) * BV * U;
+  static constexpr int STAGE_BYTES = STAGE_FLOATS * 4;
+  static constexpr int DGBUF_BYTES = BT * ROWS * 2;
+  static constexpr int DBUF_BYTES = BV * CT::GB * U * 4;
+  static_assert(ROWS % 16 == 0, "K must be a multiple of 16");
+  static_assert(IPT == 2 || IPT == 4 || IPT == 8, "items per thread");
+};
+
+__device__ __forceinline__ void report(int* err, int code, int detail) {
+  if (atomicCAS(err, 0, code) == 0) {
+    err[1] = detail;
+    err[2] = static_cast<int>(blockIdx.x);
+  }
+  __threadfence();
+}
+
+template <int CELL, int BV, int U, bool WX_BF16>
+__global__ void __launch_bounds__(kBwdThreads, 1)
+frnn_bwd_kernel(const BwdParams p, const __grid_constant__ CUtensorMap cache_map,
+                const __grid_constant__ CUtensorMap hist_map, const __grid_constant__ CUtensorMap init_map,
+                const __grid_constant__ CUtensorMap dhist_map) {
+  using Cfg = BwdCfg<CELL, BV, U, WX_BF16>;
+  using CT = typename Cfg::CT;
+  constexpr int BT = Cfg::BT, IPT = Cfg::IPT, TPB = Cfg::TPB, ROWS = Cfg::ROWS, S = CT::S, GCL = Cfg::GCL;
+
+  extern __shared__ __align__(1024) uint8_t smem[];
+  __shared__ __align__(8) uint64_t s_part_bar[2];
+  __shared__ __align__(8) uint64_t s_dg_bar;
+  __shared__ __align__(8) uint64_t s_mma_bar;
+  __shared__ __align__(8) uint64_t s_full[kStages];
+  __shared__ __align__(8) uint64_t s_empty[kStages];
+  __shared__ uint32_t s_tmem_base;
+
+  const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
+  const int D = p.D, N = p.N, T = p.T, B = p.B, C = p.C;
+  const int rank = static_cast<int>(cluster_cta_rank());
+  const int gid = blockIdx.x / C;
+  const int n = gid % N;
+  const int btile = gid / N;
+  const int b0 = btile * BV;
+  const int bv = min(BV, B - b0);
+  const int MTB = (D + 127) / 128;
+  const int a_col0 = (MTB * BT + 31) / 32 * 32;
+  uint32_t tmem_cols = 32;
+  while (tmem_cols < static_cast<uint32_t>(a_col0 + MTB * (ROWS / 2))) tmem_cols <<= 1;
+
+  // shared memory carve-up
+  const int part_bytes = C * BV * U * 4;  // one parity buffer
+  uint8_t* const dgbuf = smem;
+  float* const part = reinterpret_cast<float*>(smem + Cfg::DGBUF_BYTES);
+  float* const dbuf = reinterpret_cast<float*>(smem + Cfg::DGBUF_BYTES + 2 * part_bytes);
+  uint8_t* const stages = smem + ((Cfg::DGBUF_BYTES + 2 * part_bytes + Cfg::DBUF_BYTES + 127) & ~127);
+  const volatile int* abort_flag = p.err;
+  const uint64_t limit = p.wait_limit_ns;
+
+  if (tid == 0) {
+    mbar_init(smem_u32(&s_part_bar[0]), 1);
+    mbar_init(smem_u32(&s_part_bar[1]), 1);
+    mbar_init(smem_u32(&s_dg_bar), kEpiThreads);
+    mbar_init(smem_u32(&s_mma_bar), 1);
+    for (int s = 0; s < kStages; ++s) {
+      mbar_init(smem_u32(&s_full[s]), 1);
+      mbar_init(smem_u32(&s_empty[s]), kEpiThreads);
+    }
+    fence_mbar_init();
+  }
+  if (warp == 4) {
+    tmem_alloc(smem_u32(&s_tmem_base), tmem_cols);
+    tmem_relinquish_alloc();
+  }
+  for (int i = tid; i < Cfg::DGBUF_BYTES / 16; i += kBwdThreads)
+    reinterpret_cast<uint4*>(dgbuf)[i] = make_uint4(0u, 0u, 0u, 0u);
+  tc_fence_before_sync();
+  __syncthreads();
+  tc_fence_after_sync();
+  const uint32_t tbase = s_tmem_base;
+
+  if (warp < 4) {
+    // R_slice^T -> tensor memory: lane = input unit p, column c packs k = 2c, 2c+1 with
+    // k = g*U + u indexing the CTA's rows of R.
+    for (int j = 0; j < MTB; ++j) {
+      const int pp = j * 128 + tid;
+      const bool valid = pp < D;
+      for (int c0 = 0; c0 < ROWS / 2; c0 += 8) {
+        uint32_t r[8];
+#pragma unroll
+        for (int q = 0; q < 8; ++q) {
+          uint32_t v = 0u;
+          if (valid) {
+            const int k0 = 2 * (c0 + q), k1 = k0 + 1;
+            const __nv_bfloat16 lo = p.R[((static_cast<size_t>(k0 / U) * N + n) * D + rank * U + (k0 % U)) * D + pp];
+            const __nv_bfloat16 hi = p.R[((static_cast<size_t>(k1 / U) * N + n) * D + rank * U + (k1 % U)) * D + pp];
+            v = static_cast<uint32_t>(__bfloat16_as_ushort(lo)) | (static_cast<uint32_t>(__bfloat16_as_ushort(hi)) << 16);
+          }
+          r[q] = v;
+        }
+        tmem_st_x8(tmem_addr(tbase, 32 * warp, a_col0 + j * (ROWS / 2) + c0), r);
+      }
+    }
+    tmem_st_wait();
+  }
+
+  const int ib = tid / TPB, uq = tid % TPB;
+  const bool active = warp < 4 && tid < BV * TPB && ib < bv;
+  const int ul = uq * IPT;
+  const int d0 = rank * U + ul;
+  const size_t BND = static_cast<size_t>(B) * N * D;
+  const size_t item_bn = (static_cast<size_t>(b0 + ib) * N + n) * D + d0;
+  float dcar[S][IPT];      // gradient carried to the state of the step being processed
+  float dbacc[CT::GB][IPT];
+#pragma unroll
+  for (int g = 0; g < CT::GB; ++g)
+#pragma unroll
+    for (int j = 0; j < IPT; ++j) dbacc[g][j] = 0.0f;
+#pragma unroll
+  for (int q = 0; q < S; ++q)
+#pragma unroll
+    for (int j = 0; j < IPT; ++j) dcar[q][j] = 0.0f;
+  if (active) {
+#pragma unroll
+    for (int q = 0; q < S; ++q) ld_f32_vec<IPT>(p.d_carry + q * BND + item_bn, dcar[q]);
+  }
+  const uint32_t part_tx = static_cast<uint32_t>(C) * bv * U * 4u;
+  if (tid == 0) {
+    mbar_arrive_expect_tx(smem_u32(&s_part_bar[1]), part_tx);                 // iteration 1 (or final if T == 1)
+    if (T >= 2) mbar_arrive_expect_tx(smem_u32(&s_part_bar[0]), part_tx);     // iteration 2
+  }
+  if (warp == 5 && lane == 0) {
+    tma_prefetch_desc(&cache_map);
+    tma_prefetch_desc(&hist_map);
+    tma_prefetch_desc(&init_map);
+    tma_prefetch_desc(&dhist_map);
+  }
+  fence_proxy_async();
+  tc_fence_before_sync();
+  __syncthreads();
+  cluster_sync_all();
+  tc_fence_after_sync();
+
+  if (warp == 4) {
+    if (lane == 0) {
+      const uint32_t idesc = umma_idesc_bf16(128, BT, false, false);
+      const uint32_t db_addr = smem_u32(dgbuf);
+      for (int it = 0; it < T; ++it) {
+        if (!mbar_wait_bounded<false>(smem_u32(&s_dg_bar), it & 1, limit, abort_flag)) {
+          report(p.err, kErrWaitDg, it);
+          break;
+        }
+        tc_fence_after_sync();
+        for (int j = 0; j < MTB; ++j) {
+          for (int kk = 0; kk < ROWS / 16; ++kk) {
+            const uint64_t bdesc = umma_smem_desc(db_addr + kk * 2 * (BT * 16), BT * 16, 128);
+            umma_bf16_ts(tbase + j * BT, tbase + a_col0 + j * (ROWS / 2) + kk * 8, bdesc, idesc, kk > 0 ? 1u : 0u);
+          }
+        }
+        umma_commit(smem_u32(&s_mma_bar));
+      }
+    }
+  } else if (warp == 5) {
+    if (lane == 0) {
+      const uint32_t stage_tx = static_cast<uint32_t>(p.box_b) * U * 4u * (GCL + 3 * S);
+      const int sbu = p.box_b * U;  // floats per state plane in a stage
+      for (int it = 0; it < T; ++it) {
+        const int s = it % kStages;
+        const int t = T - 1 - it;
+        if (it >= kStages) {
+          if (!mbar_wait_bounded<false>(smem_u32(&s_empty[s]), ((it / kStages) - 1) & 1, limit, abort_flag)) {
+            report(p.err, kErrWaitEmpty, it);
+            break;
+          }
+        }
+        const uint32_t bar = smem_u32(&s_full[s]);
+        float* sb = reinterpret_cast<float*>(stages + s * Cfg::STAGE_BYTES);
+        mbar_arrive_expect_tx(bar, stage_tx);
+        if (GCL > 0) tma_load_5d(smem_u32(sb), &cache_map, bar, rank * U, n, 0, t, b0);
+        float* q = sb + GCL * sbu;
+        tma_load_5d(smem_u32(q), &hist_map, bar, rank * U, n, t, b0, 0);
+        q += S * sbu;
+        if (t > 0) tma_load_5d(smem_u32(q), &hist_map, bar, rank * U, n, t - 1, b0, 0);
+        else tma_load_5d(smem_u32(q), &init_map, bar, rank * U, n, 0, b0, 0);
+        q += S * sbu;
+        tma_load_5d(smem_u32(q), &dhist_map, bar, rank * U, n, t, b0, 0);
+      }
+    }
+  } else {
+    const size_t ND = static_cast<size_t>(N) * D;
+    const int sbu = p.box_b * U;
+    const uint32_t dg_off = kmajor_offset(BT, ib, ul);
+    for (int it = 0; it <= T; ++it) {
+      const int t = T - 1 - it;
+      float ds[S][IPT];
+#pragma unroll
+      for (int q = 0; q < S; ++q)
+#pragma unroll
+        for (int j = 0; j < IPT; ++j) ds[q][j] = dcar[q][j];
+      float cache[CT::GC][IPT], sn[S][IPT], sp[S][IPT];
+      if (it < T) {
+        const int s = it % kStages;
+        if (!mbar_wait_bounded<false>(smem_u32(&s_full[s]), (it / kStages) & 1, limit, abort_flag)) {
+          report(p.err, kErrWaitWx, it);
+          break;
+        }
+        if (active) {
+          const float* sb = reinterpret_cast<const float*>(stages + s * Cfg::STAGE_BYTES);
+#pragma unroll
+          for (int g = 0; g < GCL; ++g) ld_f32_vec<IPT>(sb + (ib * GCL + g) * U + ul, cache[g]);
+          const float* q = sb + GCL * sbu;
+#pragma unroll
+          for (int k = 0; k < S; ++k) ld_f32_vec<IPT>(q + k * sbu + ib * U + ul, sn[k]);
+          q += S * sbu;
+#pragma unroll
+          for (int k = 0; k < S; ++k) ld_f32_vec<IPT>(q + k * sbu + ib * U + ul, sp[k]);
+          q += S * sbu;
+#pragma unroll
+          for (int k = 0; k < S; ++k) {
+            float dhv[IPT];
+            ld_f32_vec<IPT>(q + k * sbu + ib * U + ul, dhv);
+#pragma unroll
+            for (int j = 0; j < IPT; ++j) ds[k][j] += dhv[j];
+          }
+        }
+        mbar_arrive(smem_u32(&s_empty[s]));
+      }
+      if (it >= 1) {
+        // partial dh for this step from every CTA of the cluster
+        const int pb = it & 1;
+        if (!mbar_wait_bounded<true>(smem_u32(&s_part_bar[pb]), ((it - 1) >> 1) & 1, limit, abort_flag)) {
+          report(p.err, kErrWaitPart, it);
+          break;
+        }
+        if (tid == 0 && it + 2 <= T) mbar_arrive_expect_tx(smem_u32(&s_part_bar[pb]), part_tx);
+        if (active) {
+          const float* pbuf = part + static_cast<size_t>(pb) * (part_bytes / 4) + ib * U + ul;
+          for (int src = 0; src < C; ++src) {
+            float v[IPT];
+            ld_f32_vec<IPT>(pbuf + src * BV * U, v);
+#pragma unroll
+            for (int j = 0; j < IPT; ++j) ds[0][j] += v[j];
+          }
+        }
+      }
+      if (it == T) {
+        if (active) {
+#pragma unroll
+          for (int q = 0; q < S; ++q) st_f32_vec<IPT>(p.d_initial + q * BND + item_bn, ds[q]);
+        }
+        break;
+      }
+      uint32_t dgp[CT::GR][IPT / 2];
+      if (active) {
+        float dgr[CT::GR][IPT], dgw[CT::GW][IPT];
+        const bool take_i = CELL == kSLSTM && t == 0 && p.slstm_zero_first != 0;
+#pragma unroll
+        for (int j = 0; j < IPT; ++j) {
+          float cj[CT::GC], snj[S], spj[S], dsj[S], gr[CT::GR], gw[CT::GW], gb[CT::GB];
+#pragma unroll
+          for (int g = 0; g < GCL; ++g) cj[g] = cache[g][j];
+#pragma unroll
+          for (int q = 0; q < S; ++q) { snj[q] = sn[q][j]; spj[q] = sp[q][j]; dsj[q] = ds[q][j]; }
+          cell_backward<CELL>(cj, spj, snj, dsj, gr, gw, gb, take_i);
+#pragma unroll
+          for (int q = 0; q < S; ++q) dcar[q][j] = dsj[q];
+#pragma unroll
+          for (int g = 0; g < CT::GR; ++g) dgr[g][j] = gr[g];
+#pragma unroll
+          for (int g = 0; g < CT::GW; ++g) dgw[g][j] = gw[g];
+#pragma unroll
+          for (int g = 0; g < CT::GB; ++g) dbacc[g][j] += gb[g];
+        }
+#pragma unroll
+        for (int g = 0; g < CT::GR; ++g)
+#pragma unroll
+          for (int j = 0; j < IPT; j += 2) dgp[g][j / 2] = pack_bf16x2(dgr[g][j], dgr[g][j + 1]);
+        // operand B of the dh contraction: [batch rows x (g, u)] K-major
+#pragma unroll
+        for (int g = 0; g < CT::GR; ++g) {
+          uint8_t* dst = dgbuf + dg_off + (g * U / 8) * (BT * 16);
+          if constexpr (IPT == 2) *reinterpret_cast<uint32_t*>(dst) = dgp[g][0];
+          else if constexpr (IPT == 4) *reinterpret_cast<uint2*>(dst) = make_uint2(dgp[g][0], dgp[g][1]);
+          else *reinterpret_cast<uint4*>(dst) = make_uint4(dgp[g][0], dgp[g][1], dgp[g][2], dgp[g][3]);
+        }
+        // streams to global memory
+        const size_t row = (static_cast<size_t>(b0 + ib) * T + t);
+        __nv_bfloat16* dgr_g = p.dgr + (row * CT::GR * N + n) * D + d0;
+#pragma unroll
+        for (int g = 0; g < CT::GR; ++g)
+#pragma unroll
+          for (int j = 0; j < IPT; j += 2) *reinterpret_cast<uint32_t*>(dgr_g + g * ND + j) = dgp[g][j / 2];
+        if constexpr (WX_BF16) {
+          __nv_bfloat16* dwx_g = static_cast<__nv_bfloat16*>(p.dwx) + (row * CT::GW * N + n) * D + d0;
+#pragma unroll
+          for (int g = 0; g < CT::GW; ++g)
+#pragma unroll
+            for (int j = 0; j < IPT; j += 2)
+              *reinterpret_cast<uint32_t*>(dwx_g + g * ND + j) = pack_bf16x2(dgw[g][j], dgw[g][j + 1]);
+        } else {
+          float* dwx_g = static_cast<float*>(p.dwx) + (row * CT::GW * N + n) * D + d0;
+#pragma unroll
+          for (int g = 0; g < CT::GW; ++g) st_f32_vec<IPT>(dwx_g + g * ND, dgw[g]);
+        }
+      }
+      fence_proxy_async();
+      tc_fence_before_sync();
+      mbar_arrive(smem_u32(&s_dg_bar));
+      if (!mbar_wait_bounded<false>(smem_u32(&s_mma_bar), it & 1, limit, abort_flag)) {
+        report(p.err, kErrWaitMma, it);
+        break;
+      }
+      tc_fence_after_sync();
+      // scatter partial dh_{t-1} rows to the CTAs that own those units
+      const int nb = (it + 1) & 1;
+      const uint32_t part_base = smem_u32(part) + static_cast<uint32_t>(nb) * part_bytes + static_cast<uint32_t>(rank) * BV * U * 4;
+      const uint32_t bar_local = smem_u32(&s_part_bar[nb]);
+      for (int j = 0; j < MTB; ++j) {
+        uint32_t r[BV / 8][8];
+#pragma unroll
+        for (int c = 0; c < BV / 8; ++c) tmem_ld_x8(tmem_addr(tbase, 32 * warp, j * BT + 8 * c), r[c]);
+        tmem_ld_wait();
+        const int pp = j * 128 + tid;
+        if (pp < D) {
+          const int dest = pp / U, pl = pp % U;
+          const uint32_t ra = map_to_cta(part_base + pl * 4, dest);
+          const uint32_t rb = map_to_cta(bar_local, dest);
+#pragma unroll
+          for (int c = 0; c < BV / 8; ++c)
+#pragma unroll
+            for (int q = 0; q < 8; ++q)
+              if (8 * c + q < bv) st_async_b32(ra + (8 * c + q) * U * 4, r[c][q], rb);
+        }
+      }
+      tc_fence_before_sync();
+    }
+  }
+
+  // bias gradient: reduce the per-thread sums over the batch rows of this tile
+  if (active) {
+#pragma unroll
+    for (int g = 0; g < CT::GB; ++g) st_f32_vec<IPT>(dbuf + (ib * CT::GB + g) * U + ul, dbacc[g]);
+  }
+  if (*abort_flag != 0) {
+    const uint64_t t0 = global_timer_ns();
+    while (global_timer_ns() - t0 < 200000ull) __nanosleep(1000);
+  }
+  tc_fence_before_sync();
+  __syncthreads();
+  for (int i = tid; i < CT::GB * U; i += kBwdThreads) {
+    float acc = 0.0f;
+    for (int b = 0; b < bv; ++b) acc += dbuf[b * CT::GB * U + i];
+    const int g = i / U, u = i % U;
+    p.db_part[((static_cast<size_t>(btile) * CT::GB + g) * N + n) * D + rank * U + u] = acc;
+  }
+  cluster_sync_all();
+  if (warp == 4) tmem_dealloc(tbase, tmem_cols);
+}
+
+template <int CELL, int BV, int U, bool WX_BF16>
+int launch_bwd(const BwdParams& p, const float* cache, const float* history, const float* initial,
+               const float* d_history, cudaStream_t stream) {
+  using Cfg = BwdCfg<CELL, BV, U, WX_BF16>;
+  using CT = typename Cfg::CT;
+  const int part_bytes = p.C * BV * U * 4;
+  const int smem = ((Cfg::DGBUF_BYTES + 2 * part_bytes + Cfg::DBUF_BYTES + 127) & ~127) + kStages * Cfg::STAGE_BYTES;
+  const int MTB = (p.D + 127) / 128;
+  if (((MTB * Cfg::BT + 31) / 32 * 32) + MTB * (Cfg::ROWS / 2) > 512) return -3;
+  if (smem > 227 * 1024) return -2;
+  const uint64_t uD = p.D, uN = p.N, uT = p.T, uB = p.B;
+  const uint32_t ub = static_cast<uint32_t>(p.box_b);
+  CUtensorMap cache_map, hist_map, init_map, dhist_map;
+  {
+    const uint64_t dims[5] = {uD, uN, static_cast<uint64_t>(Cfg::GCL > 0 ? Cfg::GCL : 1), uT, uB};
+    const uint32_t box[5] = {U, 1u, static_cast<uint32_t>(Cfg::GCL > 0 ? Cfg::GCL : 1), 1u, ub};
+    // Elman has no cache: describe the history instead so that the (unused) map is valid.
+    const void* base = Cfg::GCL > 0 ? static_cast<const void*>(cache) : static_cast<const void*>(history);
+    if (make_tensor_map(&cache_map, base, 4, 5, dims, box) != 0) return -4;
+  }
+  {
+    const uint64_t dims[5] = {uD, uN, uT, uB, static_cast<uint64_t>(CT::S)};
+    const uint32_t box[5] = {U, 1u, 1u, ub, static_cast<uint32_t>(CT::S)};
+    if (make_tensor_map(&hist_map, history, 4, 5, dims, box) != 0) return -4;
+    if (make_tensor_map(&dhist_map, d_history, 4, 5, dims, box) != 0) return -4;
+    const uint64_t dims1[5] = {uD, uN, 1u, uB, static_cast<uint64_t>(CT::S)};
+    if (make_tensor_map(&init_map, initial, 4, 5, dims1, box) != 0) return -4;
+  }
+  auto kern = frnn_bwd_kernel<CELL, BV, U, WX_BF16>;
+  cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, smem);
+  if (e != cudaSuccess) return static_cast<int>(e);
+  if (p.C > 8) {
+    e = cudaFuncSetAttribute(kern, cudaFuncAttributeNonPortableClusterSizeAllowed, 1);
+    if (e != cudaSuccess) return static_cast<int>(e);
+  }
+  const int n_btiles = (p.B + BV - 1) / BV;
+  cudaLaunchConfig_t cfg = {};
+  cfg.gridDim = dim3(static_cast<unsigned>(p.N * n_btiles * p.C));
+  cfg.blockDim = dim3(kBwdThreads);
+  cfg.dynamicSmemBytes = smem;
+  cfg.stream = stream;
+  cudaLaunchAttribute attr[1];
+  attr[0].id = cudaLaunchAttributeClusterDimension;
+  attr[0].val.clusterDim.x = static_cast<unsigned>(p.C);
+  attr[0].val.clusterDim.y = 1;
+  attr[0].val.clusterDim.z = 1;
+  cfg.attrs = attr;
+  cfg.numAttrs = 1;
+  e = cudaLaunchKernelEx(&cfg, kern, p, cache_map, hist_map, init_map, dhist_map);
+  return static_cast<int>(e);
+}
+
+template <int CELL, int BV, int U>
+int launch_bwd_dt(const BwdParams& p, const float* cache, const float* history, const float* initial,
+                  const float* d_history, int wx_bf16, cudaStream_t s) {
+  return wx_bf16 ? launch_bwd<CELL, BV, U, true>(p, cache, history, initial, d_history, s)
+                 : launch_bwd<CELL, BV, U, false>(p, cache, history, initial, d_history, s);
+}
+template <int CELL>
+int launch_bwd_cell(const BwdParams& p, const float* cache, const float* history, const float* initial,
+                    const float* d_history, int wx_bf16, int bv, int unit, cudaStream_t s) {
+  if (bv == 8 && unit == 32) return launch_bwd_dt<CELL, 8, 32>(p, cache, history, initial, d_history, wx_bf16, s);
+  if (bv == 16 && unit == 32) return launch_bwd_dt<CELL, 16, 32>(p, cache, history, initial, d_history, wx_bf16, s);
+  if (bv == 8 && unit == 16) return launch_bwd_dt<CELL, 8, 16>(p, cache, history, initial, d_history, wx_bf16, s);
+  if (bv == 16 && unit == 16) return launch_bwd_dt<CELL, 16, 16>(p, cache, history, initial, d_history, wx_bf16, s);
+  return -2;
+}
+
+}  // namespace
+
+int backward_dispatch(int cell, const BwdParams& p, const float* cache, const float* history, const float* initial,
+                      const float* d_history, int wx_bf16, int bv, int unit, cudaStream_t s) {
+  switch (cell) {
+    case kLSTM: return launch_bwd_cell<kLSTM>(p, cache, history, initial, d_history, wx_bf16, bv, unit, s);
+    case kSLSTM: return launch_bwd_cell<kSLSTM>(p, cache, history, initial, d_history, wx_bf16, bv, unit, s);
+    case kGRU: return launch_bwd_cell<kGRU>(p, cache, history, initial, d_history, wx_bf16, bv, unit, s);
+    case kElman: return launch_bwd_cell<kElman>(p, cache, history, initial, d_history, wx_bf16, bv, unit, s);
+    default: return -1;
+  }
+}
+
+}  // namespace frnn

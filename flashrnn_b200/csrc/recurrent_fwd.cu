@@ -1,0 +1,386 @@
+// Persistent forward recurrence for sm_100a.
+//
+// One thread-block cluster of C CTAs handles one (head, batch tile) for the whole sequence.
+// CTA `rank` owns U = D / C hidden units: its GR*U rows of the head's recurrent matrix are
+// loaded once into tensor memory and stay there (operand A of every tcgen05.mma), the rounded
+// hidden state of the previous step is operand B in shared memory, and the fp32 accumulator
+// lives in tensor memory too. Per step: UMMA -> tcgen05.ld -> cell epilogue (adds Wx_t + b,
+// applies the cell) -> stores all states -> pushes round_bf16(h_t) of its units into the
+// operand buffer of every CTA of the cluster with asynchronous DSMEM stores that complete on the
+// receiver's mbarrier. Wx_t tiles are prefetched by TMA through a small ring.
+//
+// Replaces FLASHRNNCellFusedForward (flashrnn/flashrnn/fused/flashrnn_fused_forward.cu:147-660)
+// with the arithmetic of reference.recurrence (flashrnn/flashrnn2/reference.py:72-114).
+#include "frnn_common.cuh"
+
+namespace frnn {
+
+namespace {
+
+constexpr int kEpiThreads = 128;
+constexpr int kFwdThreads = 192;  // 4 epilogue warps + MMA warp + TMA warp
+constexpr int kWxStages = 4;
+
+template <int CELL, int BV, int U, bool WX_BF16>
+struct FwdCfg {
+  using CT = CellTraits<CELL>;
+  static constexpr int BT = BV < 16 ? 16 : BV;  // UMMA N (M=128 needs a multiple of 16)
+  static constexpr int ROWS = CT::GR * U;       // rows of R owned by the CTA, gate-major
+  static constexpr int MT = (ROWS + 127) / 128;
+  static constexpr int IPT = (U * BV / kEpiThreads) < 2 ? 2 : (U * BV / kEpiThreads);
+  static constexpr int TPB = U / IPT;  // threads per batch row in the cell phase
+  static constexpr int ACC_COLS = MT * BT;
+  static constexpr int A_COL0 = (ACC_COLS + 31) / 32 * 32;
+  static constexpr int WX_ES = WX_BF16 ? 2 : 4;
+  static constexpr int WX_STAGE_BYTES = BV * CT::GW * U * WX_ES;
+  static constexpr int GROW = MT * 128;  // floats per batch row of the gate buffer
+  static constexpr int GBUF_BYTES = BV * GROW * 4;
+  static_assert(IPT == 2 || IPT == 4 || IPT == 8, "items per thread");
+  static_assert(U % IPT == 0 && BV * TPB <= kEpiThreads, "item mapping");
+};
+
+__device__ __forceinline__ void report(int* err, int code, int detail) {
+  if (atomicCAS(err, 0, code) == 0) {
+    err[1] = detail;
+    err[2] = static_cast<int>(blockIdx.x);
+  }
+  __threadfence();
+}
+
+template <int CELL, int BV, int U, bool WX_BF16>
+__global__ void __launch_bounds__(kFwdThreads, 1)
+frnn_fwd_kernel(const FwdParams p, const __grid_constant__ CUtensorMap wx_map) {
+  using Cfg = FwdCfg<CELL, BV, U, WX_BF16>;
+  using CT = typename Cfg::CT;
+  constexpr int BT = Cfg::BT, MT = Cfg::MT, IPT = Cfg::IPT, TPB = Cfg::TPB;
+
+  extern __shared__ __align__(1024) uint8_t smem[];
+  __shared__ __align__(8) uint64_t s_hbar[2];
+  __shared__ __align__(8) uint64_t s_mma_bar;
+  __shared__ __align__(8) uint64_t s_epi_bar;
+  __shared__ __align__(8) uint64_t s_wx_full[kWxStages];
+  __shared__ __align__(8) uint64_t s_wx_empty[kWxStages];
+  __shared__ uint32_t s_tmem_base;
+
+  const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
+  const int D = p.D, N = p.N, T = p.T, B = p.B, C = p.C;
+  const int rank = static_cast<int>(cluster_cta_rank());
+  const int gid = blockIdx.x / C;
+  const int n = gid % N;
+  const int b0 = (gid / N) * BV;
+  const int bv = min(BV, B - b0);
+  const int hbuf_bytes = BT * D * 2;
+  uint8_t* const hbuf = smem;
+  float* const gbuf = reinterpret_cast<float*>(smem + 2 * hbuf_bytes);
+  uint8_t* const wxs = smem + ((2 * hbuf_bytes + Cfg::GBUF_BYTES + 127) & ~127);
+  const volatile int* abort_flag = p.err;
+  const uint64_t limit = p.wait_limit_ns;
+  const int a_cols = MT * (D / 2);
+  uint32_t tmem_cols = 32;
+  while (tmem_cols < static_cast<uint32_t>(Cfg::A_COL0 + a_cols)) tmem_cols <<= 1;
+
+  // ---------------- prologue ----------------
+  if (tid == 0) {
+    mbar_init(smem_u32(&s_hbar[0]), 1);
+    mbar_init(smem_u32(&s_hbar[1]), 1);
+    mbar_init(smem_u32(&s_mma_bar), 1);
+    mbar_init(smem_u32(&s_epi_bar), kEpiThreads);
+    for (int s = 0; s < kWxStages; ++s) {
+      mbar_init(smem_u32(&s_wx_full[s]), 1);
+      mbar_init(smem_u32(&s_wx_empty[s]), kEpiThreads);
+    }
+    fence_mbar_init();
+  }
+  if (warp == 4) {
+    tmem_alloc(smem_u32(&s_tmem_base), tmem_cols);
+    tmem_relinquish_alloc();
+  }
+  for (int i = tid; i < 2 * hbuf_bytes / 16; i += kFwdThreads)
+    reinterpret_cast<uint4*>(hbuf)[i] = make_uint4(0u, 0u, 0u, 0u);
+  __syncthreads();
+  // round_bf16(initial h) of the whole head for this batch tile -> operand buffer 0
+  for (int i = tid; i < bv * (D / 2); i += kFwdThreads) {
+    const int b = i / (D / 2), k = 2 * (i % (D / 2));
+    const float2 v = *reinterpret_cast<const float2*>(p.initial + (static_cast<size_t>(b0 + b) * N + n) * D + k);
+    *reinterpret_cast<uint32_t*>(hbuf + kmajor_offset(BT, b, k)) = pack_bf16x2(v.x, v.y);
+  }
+  tc_fence_before_sync();
+  __syncthreads();
+  tc_fence_after_sync();
+  const uint32_t tbase = s_tmem_base;
+
+  if (warp < 4) {
+    // R rows of this CTA -> tensor memory (lane = row, 32-bit column = two consecutive k)
+    for (int j = 0; j < MT; ++j) {
+      const int rr = j * 128 + tid;
+      const bool valid = rr < Cfg::ROWS;
+      const int g = valid ? rr / U : 0, u = valid ? rr % U : 0;
+      const __nv_bfloat16* src = p.R + ((static_cast<size_t>(g) * N + n) * D + rank * U + u) * D;
+      for (int c0 = 0; c0 < D / 2; c0 += 8) {
+        uint32_t r[8] = {0u, 0u, 0u, 0u, 0u, 0u, 0u, 0u};
+        if (valid) {
+          const uint4 lo = __ldg(reinterpret_cast<const uint4*>(src + 2 * c0));
+          const uint4 hi = __ldg(reinterpret_cast<const uint4*>(src + 2 * c0 + 8));
+          r[0] = lo.x; r[1] = lo.y; r[2] = lo.z; r[3] = lo.w;
+          r[4] = hi.x; r[5] = hi.y; r[6] = hi.z; r[7] = hi.w;
+        }
+        tmem_st_x8(tmem_addr(tbase, 32 * warp, Cfg::A_COL0 + j * (D / 2) + c0), r);
+      }
+    }
+    tmem_st_wait();
+  }
+
+  // cell-phase item of this thread: batch row `ib`, units [d0, d0 + IPT) of the head
+  const int ib = tid / TPB, uq = tid % TPB;
+  const bool active = warp < 4 && tid < BV * TPB && ib < bv;
+  const int ul = uq * IPT;          // unit offset inside the CTA's slice
+  const int d0 = rank * U + ul;     // unit offset inside the head
+  float st[CT::S][IPT];
+  float bias[CT::GB][IPT];
+  const size_t sBTND = static_cast<size_t>(B) * T * N * D;
+  const size_t item_bn = (static_cast<size_t>(b0 + ib) * N + n) * D + d0;  // into [B][1][N][D]
+  if (active) {
+#pragma unroll
+    for (int s = 0; s < CT::S; ++s)
+      ld_f32_vec<IPT>(p.initial + static_cast<size_t>(s) * B * N * D + item_bn, st[s]);
+#pragma unroll
+    for (int g = 0; g < CT::GB; ++g)
+      ld_f32_vec<IPT>(p.bias + (static_cast<size_t>(g) * N + n) * D + d0, bias[g]);
+    if (p.hbf != nullptr) {
+      __nv_bfloat16* dst = p.hbf + ((static_cast<size_t>(b0 + ib) * (T + 1)) * N + n) * D + d0;
+#pragma unroll
+      for (int j = 0; j < IPT; j += 2)
+        *reinterpret_cast<uint32_t*>(dst + j) = pack_bf16x2(st[0][j], st[0][j + 1]);
+    }
+  }
+  const uint32_t h_tx_bytes = static_cast<uint32_t>(D) * bv * 2u;
+  if (warp == 4 && lane == 0) {
+    if (T >= 2) mbar_arrive_expect_tx(smem_u32(&s_hbar[1]), h_tx_bytes);
+    if (T >= 3) mbar_arrive_expect_tx(smem_u32(&s_hbar[0]), h_tx_bytes);
+    tma_prefetch_desc(&wx_map);
+  }
+  fence_proxy_async();
+  tc_fence_before_sync();
+  __syncthreads();
+  cluster_sync_all();
+  tc_fence_after_sync();
+
+  // ---------------- main loops ----------------
+  if (warp == 4) {
+    if (lane == 0) {
+      const uint32_t idesc = umma_idesc_bf16(128, BT, false, false);
+      for (int t = 0; t < T; ++t) {
+        const int pb = t & 1;
+        if (t >= 1) {
+          if (!mbar_wait_bounded<true>(smem_u32(&s_hbar[pb]), ((t - 1) >> 1) & 1, limit, abort_flag)) {
+            report(p.err, kErrWaitH, t);
+            break;
+          }
+          if (t + 2 <= T - 1) mbar_arrive_expect_tx(smem_u32(&s_hbar[pb]), h_tx_bytes);
+        }
+        fence_proxy_async();
+        tc_fence_after_sync();
+        const uint32_t hb = smem_u32(hbuf + pb * hbuf_bytes);
+        for (int j = 0; j < MT; ++j) {
+          for (int kk = 0; kk < D / 16; ++kk) {
+            const uint64_t bdesc = umma_smem_desc(hb + kk * 2 * (BT * 16), BT * 16, 128);
+            umma_bf16_ts(tbase + j * BT, tbase + Cfg::A_COL0 + j * (D / 2) + kk * 8, bdesc, idesc,
+                         kk > 0 ? 1u : 0u);
+          }
+        }
+        umma_commit(smem_u32(&s_mma_bar));
+      }
+    }
+  } else if (warp == 5) {
+    if (lane == 0) {
+      const uint32_t stage_tx = static_cast<uint32_t>(p.wx_box_b) * CT::GW * U * Cfg::WX_ES;
+      for (int t = 0; t < T; ++t) {
+        const int s = t % kWxStages;
+        if (t >= kWxStages) {
+          if (!mbar_wait_bounded<false>(smem_u32(&s_wx_empty[s]), ((t / kWxStages) - 1) & 1, limit, abort_flag)) {
+            report(p.err, kErrWaitEmpty, t);
+            break;
+          }
+        }
+        mbar_arrive_expect_tx(smem_u32(&s_wx_full[s]), stage_tx);
+        tma_load_5d(smem_u32(wxs + s * Cfg::WX_STAGE_BYTES), &wx_map, smem_u32(&s_wx_full[s]), rank * U, n, 0, t, b0);
+      }
+    }
+  } else {
+    float* hist = p.history + (static_cast<size_t>(b0 + ib) * T * N + n) * D + d0;
+    float* cache = p.cache == nullptr ? nullptr : p.cache + ((static_cast<size_t>(b0 + ib) * T * CT::GC) * N + n) * D + d0;
+    __nv_bfloat16* hbf = p.hbf == nullptr ? nullptr : p.hbf + ((static_cast<size_t>(b0 + ib) * (T + 1) + 1) * N + n) * D + d0;
+    const uint32_t h_off = kmajor_offset(BT, ib, d0);
+    const size_t ND = static_cast<size_t>(N) * D;
+    for (int t = 0; t < T; ++t) {
+      const int s = t % kWxStages;
+      if (!mbar_wait_bounded<false>(smem_u32(&s_wx_full[s]), (t / kWxStages) & 1, limit, abort_flag)) {
+        report(p.err, kErrWaitWx, t);
+        break;
+      }
+      float wx[CT::GW][IPT];
+      if (active) {
+        const uint8_t* ws = wxs + s * Cfg::WX_STAGE_BYTES;
+#pragma unroll
+        for (int g = 0; g < CT::GW; ++g) {
+          const int e = (ib * CT::GW + g) * U + ul;
+          if constexpr (WX_BF16) ld_bf16_vec<IPT>(reinterpret_cast<const __nv_bfloat16*>(ws) + e, wx[g]);
+          else ld_f32_vec<IPT>(reinterpret_cast<const float*>(ws) + e, wx[g]);
+        }
+      }
+      mbar_arrive(smem_u32(&s_wx_empty[s]));
+      if (!mbar_wait_bounded<false>(smem_u32(&s_mma_bar), t & 1, limit, abort_flag)) {
+        report(p.err, kErrWaitMma, t);
+        break;
+      }
+      tc_fence_after_sync();
+      // phase 1: accumulator rows (lane = gate row) -> gate buffer [batch][row]
+      {
+        uint32_t r[MT][BV / 8][8];
+#pragma unroll
+        for (int j = 0; j < MT; ++j)
+#pragma unroll
+          for (int c = 0; c < BV / 8; ++c) tmem_ld_x8(tmem_addr(tbase, 32 * warp, j * BT + 8 * c), r[j][c]);
+        tmem_ld_wait();
+#pragma unroll
+        for (int j = 0; j < MT; ++j)
+#pragma unroll
+          for (int c = 0; c < BV / 8; ++c)
+#pragma unroll
+            for (int q = 0; q < 8; ++q) gbuf[(8 * c + q) * Cfg::GROW + j * 128 + tid] = __uint_as_float(r[j][c][q]);
+      }
+      tc_fence_before_sync();
+      mbar_arrive(smem_u32(&s_epi_bar));
+      if (!mbar_wait_bounded<false>(smem_u32(&s_epi_bar), t & 1, limit, abort_flag)) {
+        report(p.err, kErrWaitEpi, t);
+        break;
+      }
+      // phase 2: the cell, for IPT consecutive units of one batch row
+      if (active) {
+        float ry[CT::GR][IPT];
+#pragma unroll
+        for (int g = 0; g < CT::GR; ++g) ld_f32_vec<IPT>(gbuf + ib * Cfg::GROW + g * U + ul, ry[g]);
+        float cv[CT::GC][IPT];
+        const bool take_i = CELL == kSLSTM && t == 0 && p.slstm_zero_first != 0;
+#pragma unroll
+        for (int j = 0; j < IPT; ++j) {
+          float ryj[CT::GR], wxj[CT::GW], bj[CT::GB], sj[CT::S], cj[CT::GC];
+#pragma unroll
+          for (int g = 0; g < CT::GR; ++g) ryj[g] = ry[g][j];
+#pragma unroll
+          for (int g = 0; g < CT::GW; ++g) wxj[g] = wx[g][j];
+#pragma unroll
+          for (int g = 0; g < CT::GB; ++g) bj[g] = bias[g][j];
+#pragma unroll
+          for (int q = 0; q < CT::S; ++q) sj[q] = st[q][j];
+          cell_forward<CELL>(ryj, wxj, bj, sj, cj, take_i);
+#pragma unroll
+          for (int q = 0; q < CT::S; ++q) st[q][j] = sj[q];
+#pragma unroll
+          for (int q = 0; q < CT::GC; ++q) cv[q][j] = cj[q];
+        }
+        uint32_t hp[IPT / 2];
+#pragma unroll
+        for (int j = 0; j < IPT; j += 2) hp[j / 2] = pack_bf16x2(st[0][j], st[0][j + 1]);
+        if (t + 1 < T) {
+          const uint32_t dst = smem_u32(hbuf + ((t + 1) & 1) * hbuf_bytes) + h_off;
+          const uint32_t bar = smem_u32(&s_hbar[(t + 1) & 1]);
+          for (int d = 0; d < C; ++d) {
+            const uint32_t ra = map_to_cta(dst, d), rb = map_to_cta(bar, d);
+            if constexpr (IPT == 2) st_async_b32(ra, hp[0], rb);
+            else if constexpr (IPT == 4) st_async_v2_b32(ra, hp[0], hp[1], rb);
+            else st_async_v4_b32(ra, hp[0], hp[1], hp[2], hp[3], rb);
+          }
+        }
+#pragma unroll
+        for (int q = 0; q < CT::S; ++q) st_f32_vec<IPT>(hist + q * sBTND + t * ND, st[q]);
+        if (cache != nullptr && CELL != kElman) {
+#pragma unroll
+          for (int q = 0; q < CT::GC; ++q) st_f32_vec<IPT>(cache + (static_cast<size_t>(t) * CT::GC + q) * ND, cv[q]);
+        }
+        if (hbf != nullptr) {
+#pragma unroll
+          for (int j = 0; j < IPT; j += 2) *reinterpret_cast<uint32_t*>(hbf + t * ND + j) = hp[j / 2];
+        }
+      }
+    }
+    if (active) {
+#pragma unroll
+      for (int q = 0; q < CT::S; ++q) st_f32_vec<IPT>(p.carry + static_cast<size_t>(q) * B * N * D + item_bn, st[q]);
+    }
+  }
+
+  // ---------------- teardown ----------------
+  if (*abort_flag != 0) {
+    // give copies that are still in flight time to land before shared memory is released
+    const uint64_t t0 = global_timer_ns();
+    while (global_timer_ns() - t0 < 200000ull) __nanosleep(1000);
+  }
+  tc_fence_before_sync();
+  __syncthreads();
+  cluster_sync_all();
+  if (warp == 4) tmem_dealloc(tbase, tmem_cols);
+}
+
+template <int CELL, int BV, int U, bool WX_BF16>
+int launch_fwd(const FwdParams& p, const void* wx, cudaStream_t stream) {
+  using Cfg = FwdCfg<CELL, BV, U, WX_BF16>;
+  using CT = typename Cfg::CT;
+  const int hbuf_bytes = Cfg::BT * p.D * 2;
+  const int smem = ((2 * hbuf_bytes + Cfg::GBUF_BYTES + 127) & ~127) + kWxStages * Cfg::WX_STAGE_BYTES;
+  if (Cfg::A_COL0 + Cfg::MT * (p.D / 2) > 512) return -3;
+  CUtensorMap map;
+  const uint64_t dims[5] = {static_cast<uint64_t>(p.D), static_cast<uint64_t>(p.N), static_cast<uint64_t>(CT::GW),
+                            static_cast<uint64_t>(p.T), static_cast<uint64_t>(p.B)};
+  const uint32_t box[5] = {static_cast<uint32_t>(U), 1u, static_cast<uint32_t>(CT::GW), 1u, static_cast<uint32_t>(p.wx_box_b)};
+  if (make_tensor_map(&map, wx, Cfg::WX_ES, 5, dims, box) != 0) return -4;
+  auto kern = frnn_fwd_kernel<CELL, BV, U, WX_BF16>;
+  cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, smem);
+  if (e != cudaSuccess) return static_cast<int>(e);
+  if (p.C > 8) {
+    e = cudaFuncSetAttribute(kern, cudaFuncAttributeNonPortableClusterSizeAllowed, 1);
+    if (e != cudaSuccess) return static_cast<int>(e);
+  }
+  const int n_btiles = (p.B + BV - 1) / BV;
+  cudaLaunchConfig_t cfg = {};
+  cfg.gridDim = dim3(static_cast<unsigned>(p.N * n_btiles * p.C));
+  cfg.blockDim = dim3(kFwdThreads);
+  cfg.dynamicSmemBytes = smem;
+  cfg.stream = stream;
+  cudaLaunchAttribute attr[1];
+  attr[0].id = cudaLaunchAttributeClusterDimension;
+  attr[0].val.clusterDim.x = static_cast<unsigned>(p.C);
+  attr[0].val.clusterDim.y = 1;
+  attr[0].val.clusterDim.z = 1;
+  cfg.attrs = attr;
+  cfg.numAttrs = 1;
+  e = cudaLaunchKernelEx(&cfg, kern, p, map);
+  return static_cast<int>(e);
+}
+
+template <int CELL, int BV, int U>
+int launch_fwd_dt(const FwdParams& p, const void* wx, int wx_bf16, cudaStream_t s) {
+  return wx_bf16 ? launch_fwd<CELL, BV, U, true>(p, wx, s) : launch_fwd<CELL, BV, U, false>(p, wx, s);
+}
+template <int CELL>
+int launch_fwd_cell(const FwdParams& p, const void* wx, int wx_bf16, int bv, int unit, cudaStream_t s) {
+  if (bv == 8 && unit == 32) return launch_fwd_dt<CELL, 8, 32>(p, wx, wx_bf16, s);
+  if (bv == 16 && unit == 32) return launch_fwd_dt<CELL, 16, 32>(p, wx, wx_bf16, s);
+  if (bv == 8 && unit == 16) return launch_fwd_dt<CELL, 8, 16>(p, wx, wx_bf16, s);
+  if (bv == 16 && unit == 16) return launch_fwd_dt<CELL, 16, 16>(p, wx, wx_bf16, s);
+  return -2;
+}
+
+}  // namespace
+
+int forward_dispatch(int cell, const FwdParams& p, const void* wx, int wx_bf16, int bv, int unit, cudaStream_t s) {
+  switch (cell) {
+    case kLSTM: return launch_fwd_cell<kLSTM>(p, wx, wx_bf16, bv, unit, s);
+    case kSLSTM: return launch_fwd_cell<kSLSTM>(p, wx, wx_bf16, bv, unit, s);
+    case kGRU: return launch_fwd_cell<kGRU>(p, wx, wx_bf16, bv, unit, s);
+    case kElman: return launch_fwd_cell<kElman>(p, wx, wx_bf16, bv, unit, s);
+    default: return -1;
+  }
+}
+
+}  // namespace frnn

@@ -1,0 +1,267 @@
+"""Host side of the B200 recurrence backend: the reference's two public call signatures.
+
+* ``flashrnn(Wx, R, b, states, function, config, backend, dtype)`` mirrors
+  flashrnn/flashrnn/flashrnn.py:1117-1138 (same tensor layouts, ``states=None`` means zeros).
+* ``flashrnn_torch(wx, recurrent, bias, initial, *, cell, numerics)`` mirrors
+  flashrnn/flashrnn2/torch_backend.py:12-67 (same validation and error behaviour).
+
+Both run the hand-written sm_100a kernels through the C ABI; there is no other code path.
+State, history, carry and every gradient accumulation are fp32; R and the recurrent hidden
+operand are rounded to bf16 for the tensor cores, i.e. the reference's ``fp32_state_bf16_mma``
+numerics. The carry returned by one call is a valid ``states`` / ``initial`` of the next one and
+stays connected to autograd.
+"""
+
+from __future__ import annotations
+
+from dataclasses import dataclass
+from typing import Optional
+
+import torch
+
+from . import _lib
+
+# (recurrent gates, Wx gates, bias gates, states); reference.py:16-21, flashrnn.py:46-68
+SIZES = {"lstm": (4, 4, 4, 2), "slstm": (4, 4, 4, 4), "gru": (3, 3, 4, 1), "elman": (1, 1, 1, 1)}
+BACKEND = "b200"
+_DTYPES = {"bfloat16": torch.bfloat16, "float32": torch.float32}
+
+_pending_errors: list = []
+
+
+def _ptr(t: Optional[torch.Tensor]):
+    return None if t is None else t.data_ptr()
+
+
+def _stream(device) -> int:
+    return torch.cuda.current_stream(device).cuda_stream
+
+
+def _raise_device_error(err: torch.Tensor, what: str) -> None:
+    code, step, cta = (int(v) for v in err[:3].tolist())
+    if code != 0:
+        raise RuntimeError(
+            f"{what}: device-side wait ran out (code {code}: {_lib.ERROR_TEXT.get(code, '?')}, step {step}, CTA {cta})"
+        )
+
+
+def _track(err: torch.Tensor, what: str) -> None:
+    """Remember an error word; it is read once the kernels that write it have finished."""
+    ev = torch.cuda.Event()
+    ev.record(torch.cuda.current_stream(err.device))
+    _pending_errors.append((ev, err, what))
+
+
+def poll_errors(block: bool = False) -> None:
+    """Raise if a finished launch reported a device-side error. ``block=True`` waits for all."""
+    keep = []
+    while _pending_errors:
+        ev, err, what = _pending_errors.pop(0)
+        if block:
+            ev.synchronize()
+        if ev.query():
+            _raise_device_error(err, what)
+        else:
+            keep.append((ev, err, what))
+    _pending_errors.extend(keep)
+
+
+class _Recurrence(torch.autograd.Function):
+    """One fused forward launch; backward = one BPTT launch + the dR/db contraction."""
+
+    @staticmethod
+    def forward(ctx, wx, recurrent, bias, initial, cell: str, zero_first: bool):
+        lib = _lib.load()
+        poll_errors()
+        B, T, _, N, D = wx.shape
+        gr, gw, gb, S = SIZES[cell]
+        dev = wx.device
+        wx_c = wx.contiguous()
+        r_bf = recurrent.detach().to(torch.bfloat16).contiguous()
+        b32 = bias.detach().to(torch.float32).contiguous()
+        init32 = initial.detach().to(torch.float32).contiguous()
+        plan = _lib.plan(cell, B, T, N, D)
+        if not plan.supported:
+            raise ValueError(
+                f"flashrnn_b200: cell={cell} D={D} is outside the sm_100a kernel family "
+                f"(needs D/{plan.unit} <= 16 CTAs per head and the R slice resident in tensor memory)"
+            )
+        history = torch.empty((S, B, T, N, D), dtype=torch.float32, device=dev)
+        carry = torch.empty((S, B, 1, N, D), dtype=torch.float32, device=dev)
+        train = any(ctx.needs_input_grad[:4])
+        cache = hbf = None
+        if train:
+            if plan.cache_bytes:
+                cache = torch.empty(plan.cache_bytes // 4, dtype=torch.float32, device=dev)
+            hbf = torch.empty(plan.hbf_bytes // 2, dtype=torch.bfloat16, device=dev)
+        err = torch.zeros(4, dtype=torch.int32, device=dev)
+        rc = lib.frnn_b200_forward(
+            _lib.CELLS[cell], wx_c.data_ptr(), int(wx_c.dtype == torch.bfloat16), r_bf.data_ptr(), b32.data_ptr(),
+            init32.data_ptr(), history.data_ptr(), carry.data_ptr(), _ptr(cache), _ptr(hbf), B, T, N, D,
+            int(zero_first), 0, err.data_ptr(), _stream(dev),
+        )
+        _lib.check(rc, "frnn_b200_forward")
+        _track(err, "frnn_b200_forward")
+        if train:
+            ctx.save_for_backward(r_bf, init32, history, cache if cache is not None else history.new_empty(0), hbf)
+            ctx.cell, ctx.zero_first = cell, zero_first
+            ctx.shape = (B, T, N, D)
+            ctx.dtypes = (wx.dtype, recurrent.dtype, bias.dtype, initial.dtype)
+            ctx.plan = plan
+        return history, carry
+
+    @staticmethod
+    def backward(ctx, d_history, d_carry):
+        lib = _lib.load()
+        poll_errors()
+        r_bf, init32, history, cache, hbf = ctx.saved_tensors
+        cell, plan = ctx.cell, ctx.plan
+        B, T, N, D = ctx.shape
+        gr, gw, gb, S = SIZES[cell]
+        dev = history.device
+        wx_dtype = ctx.dtypes[0]
+        if d_history is None:
+            d_history = torch.zeros_like(history)
+        if d_carry is None:
+            d_carry = torch.zeros((S, B, 1, N, D), dtype=torch.float32, device=dev)
+        d_history = d_history.to(torch.float32).contiguous()
+        d_carry = d_carry.to(torch.float32).contiguous()
+        dwx = torch.empty((B, T, gw, N, D), dtype=wx_dtype, device=dev)
+        dgr = torch.empty(plan.dgr_bytes // 2, dtype=torch.bfloat16, device=dev)
+        d_initial = torch.empty((S, B, 1, N, D), dtype=torch.float32, device=dev)
+        db_part = torch.empty(plan.dbpart_bytes // 4, dtype=torch.float32, device=dev)
+        dR = torch.empty((gr, N, D, D), dtype=torch.float32, device=dev)
+        db = torch.empty((gb, N, D), dtype=torch.float32, device=dev)
+        work = None
+        if plan.wgrad_work_bytes:
+            work = torch.empty(plan.wgrad_work_bytes // 4, dtype=torch.float32, device=dev)
+        err = torch.zeros(4, dtype=torch.int32, device=dev)
+        stream = _stream(dev)
+        rc = lib.frnn_b200_backward(
+            _lib.CELLS[cell], _ptr(cache) if cache.numel() else None, history.data_ptr(), init32.data_ptr(),
+            r_bf.data_ptr(), d_history.data_ptr(), d_carry.data_ptr(), dwx.data_ptr(),
+            int(wx_dtype == torch.bfloat16), dgr.data_ptr(), d_initial.data_ptr(), db_part.data_ptr(), B, T, N, D,
+            int(ctx.zero_first), 0, err.data_ptr(), stream,
+        )
+        _lib.check(rc, "frnn_b200_backward")
+        rc = lib.frnn_b200_wgrad(
+            _lib.CELLS[cell], dgr.data_ptr(), hbf.data_ptr(), db_part.data_ptr(), dR.data_ptr(), db.data_ptr(),
+            _ptr(work), B, T, N, D, err.data_ptr(), stream,
+        )
+        _lib.check(rc, "frnn_b200_wgrad")
+        _track(err, "frnn_b200_backward")
+        need = ctx.needs_input_grad
+        return (
+            dwx if need[0] else None,
+            dR.to(ctx.dtypes[1]) if need[1] else None,
+            db.to(ctx.dtypes[2]) if need[2] else None,
+            d_initial.to(ctx.dtypes[3]) if need[3] else None,
+            None,
+            None,
+        )
+
+
+def _pad_width(t: torch.Tensor, pad: int, dims) -> torch.Tensor:
+    """Zero-pad the given (negative) dims by ``pad`` at the end."""
+    spec = []
+    for d in range(-1, -t.ndim - 1, -1):
+        spec += [0, pad if d in dims else 0]
+    return torch.nn.functional.pad(t, spec)
+
+
+def _run(wx, recurrent, bias, initial, cell: str):
+    if not wx.is_cuda:
+        raise RuntimeError("flashrnn_b200 runs on CUDA devices only (sm_100a); there is no CPU path")
+    D = wx.shape[-1]
+    zero_first = bool(cell == "slstm" and bool(torch.all(initial[2] == 0)))
+    pad = (-D) % 16
+    if pad:
+        # The kernels tile the head width in multiples of 16; zero rows/columns of R, zero
+        # inputs and zero initial state keep the padded units at exactly zero.
+        wx = _pad_width(wx, pad, (-1,))
+        recurrent = _pad_width(recurrent, pad, (-1, -2))
+        bias = _pad_width(bias, pad, (-1,))
+        initial = _pad_width(initial, pad, (-1,))
+    history, carry = _Recurrence.apply(wx, recurrent, bias, initial, cell, zero_first)
+    if pad:
+        history, carry = history[..., :D], carry[..., :D]
+    return history, carry
+
+
+def flashrnn_torch(wx, recurrent, bias, initial, *, cell: str = "lstm", numerics: str = "fp32_state_bf16_mma"):
+    """Return full history ``[S,B,T,H,D]`` and carry ``[S,B,1,H,D]`` (both fp32).
+
+    Same argument checks as flashrnn/flashrnn2/torch_backend.py:36-58. The only numerical policy
+    this backend implements is ``fp32_state_bf16_mma``; fp32 inputs follow the reference contract
+    exactly, bf16 inputs (Wx, R, b, initial rounded by the caller) are accepted as an extension.
+    """
+    if cell not in SIZES:
+        raise ValueError(f"unsupported cell: {cell}")
+    if numerics != "fp32_state_bf16_mma":
+        if numerics == "mathematical":
+            raise ValueError("the B200 backend implements numerics='fp32_state_bf16_mma' only")
+        raise ValueError(f"unsupported numerical policy: {numerics}")
+    tensors = (wx, recurrent, bias, initial)
+    if any(t.layout != torch.strided for t in tensors):
+        raise ValueError("inputs must have strided tensor layout")
+    if tuple(t.ndim for t in tensors) != (5, 4, 3, 5):
+        raise ValueError("expected wx/R/b/initial ranks 5/4/3/5")
+    if any(size < 1 for size in wx.shape):
+        raise ValueError("batch, time, gates, heads and width must be positive")
+    if wx.dtype not in (torch.bfloat16, torch.float32):
+        raise ValueError("fp32_state_bf16_mma requires FP32 inputs (BF16 inputs are accepted as pre-rounded)")
+    if any(t.dtype != wx.dtype for t in tensors):
+        raise ValueError("all inputs must have the same dtype")
+    if any(t.device != wx.device for t in tensors):
+        raise ValueError("all inputs must be on the same device")
+    batch, steps, gates, heads, width = wx.shape
+    gr, gw, gb, S = SIZES[cell]
+    if gates != gw:
+        raise ValueError("expected nonempty sequence and matching input gate count")
+    if recurrent.shape != (gr, heads, width, width):
+        raise ValueError("recurrent weights must have layout [G,N,D,P]")
+    if bias.shape != (gb, heads, width):
+        raise ValueError("bias gate count does not match cell")
+    if initial.shape != (S, batch, 1, heads, width):
+        raise ValueError("initial state must have layout [S,B,1,N,D]")
+    with torch.autocast("cuda", enabled=False):
+        return _run(wx, recurrent, bias, initial, cell)
+
+
+@dataclass
+class FlashRNNConfig:
+    """The fields of the reference's FlashRNNConfig (flashrnn.py:121-170) this backend honours."""
+
+    function: str = "lstm"
+    backend: str = BACKEND
+    dtype: str = "bfloat16"
+    head_dim: int = -1
+    num_heads: int = -1
+    batch_size: int = -1
+
+
+def flashrnn(Wx, R, b, states=None, function: str = "lstm", config: Optional[FlashRNNConfig] = None,
+             backend: str = BACKEND, dtype: str = "bfloat16"):
+    """``Wx[B,T,G,N,D], R[G,N,D,D], b[G,N,D], states[S,B,1,N,D]`` -> ``(states[S,B,T,N,D], last[S,B,1,N,D])``.
+
+    ``dtype`` is the operand dtype of the streamed input (``Wx`` is cast to it, R always goes to
+    the tensor cores in bf16); bias and states keep fp32, and the returned states are fp32.
+    """
+    if config is not None:
+        function, backend, dtype = config.function, config.backend, config.dtype
+    if backend != BACKEND:
+        raise ValueError(f"Unknown backend {backend}: this library provides backend='{BACKEND}' only")
+    if function not in SIZES:
+        raise ValueError(f"Unknown function {function}")
+    if dtype not in _DTYPES:
+        raise ValueError(f"Unsupported dtype {dtype}: use 'bfloat16' or 'float32'")
+    gr, gw, gb, S = SIZES[function]
+    B, T, G, N, D = Wx.shape
+    if G != gw or R.shape != (gr, N, D, D) or b.shape != (gb, N, D):
+        raise ValueError(f"shape mismatch for {function}: Wx {tuple(Wx.shape)}, R {tuple(R.shape)}, b {tuple(b.shape)}")
+    if states is None:
+        states = torch.zeros((S, B, 1, N, D), dtype=torch.float32, device=Wx.device)
+    elif states.shape != (S, B, 1, N, D):
+        raise ValueError("states must have layout [S,B,1,N,D]")
+    with torch.autocast("cuda", enabled=False):
+        return _run(Wx.to(_DTYPES[dtype]), R, b.to(torch.float32), states.to(torch.float32), function)

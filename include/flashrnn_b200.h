@@ -1,0 +1,96 @@
+/*
+ * flashrnn_b200 — C ABI of the sm_100a fused recurrence (forward, BPTT backward, dR/db).
+ *
+ * All pointers are DEVICE pointers owned by the caller; the library never allocates, frees or
+ * synchronises, and every launch goes to the CUDA stream passed as `stream` (a cudaStream_t).
+ * Tensors are dense and use the public layouts of the reference:
+ *   Wx[B,T,GW,N,D]  R[GR,N,D,D] (gate, head, out, in)  b[GB,N,D]  states[S,B,T|1,N,D].
+ * Return value: 0 on success, a positive cudaError_t, or a negative library code
+ *   -1 unknown cell, -2 shape not supported by this kernel family (see frnn_b200_plan),
+ *   -3 tensor-memory budget exceeded, -4 TMA descriptor could not be built, -5 bad argument.
+ * Device-side problems (a bounded wait that ran out) are reported through the caller-owned
+ * `err` array (int[4], zeroed by the caller): err[0] = code (101..107), err[1] = step,
+ * err[2] = CTA. The kernels then leave in an orderly way; the context stays usable.
+ *
+ * Counterparts in the reference (0z5a/flashrnn):
+ *   flashrnn/flashrnn/fused/flashrnn.cc:56-347      pybind class FlashRNNFuncFused
+ *   flashrnn/flashrnn2/hybrid_fw2d.cu:404-419       extern "C" frnn_hybrid_fw2d (ctypes ABI model)
+ *   flashrnn/flashrnn2/hybrid_bw2d.cu:664-678       extern "C" frnn_hybrid_bw2d
+ */
+#ifndef FLASHRNN_B200_H_
+#define FLASHRNN_B200_H_
+
+#include <stddef.h>
+#include <stdint.h>
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+enum { FRNN_CELL_LSTM = 0, FRNN_CELL_SLSTM = 1, FRNN_CELL_GRU = 2, FRNN_CELL_ELMAN = 3 };
+
+/* Gate / state counts of a cell, as rnn_function_registry (flashrnn/flashrnn/flashrnn.py:46-68)
+ * and SIZES (flashrnn/flashrnn2/reference.py:16-21) define them. */
+typedef struct frnn_b200_plan {
+  int gates_r, gates_w, gates_b, states, cache_gates;
+  int unit;        /* hidden units owned by one CTA                              */
+  int cluster;     /* CTAs per (head, batch tile) group = D / unit               */
+  int batch_tile;  /* batch rows per group                                        */
+  int n_btiles;    /* ceil(B / batch_tile)                                        */
+  int grid_ctas;   /* N * n_btiles * cluster                                      */
+  int supported;   /* 1 if the shape runs on this kernel family                   */
+  int64_t cache_bytes;   /* float  [B,T,cache_gates,N,D]   forward -> backward     */
+  int64_t hbf_bytes;     /* bf16   [B,T+1,N,D]             forward -> wgrad        */
+  int64_t dgr_bytes;     /* bf16   [B,T,gates_r,N,D]       backward -> wgrad       */
+  int64_t dbpart_bytes;  /* float  [n_btiles,gates_b,N,D]  backward -> wgrad       */
+  int64_t wgrad_work_bytes; /* float [wgrad_ksplit, gates_r,N,D,D] split-K partials, 0 if none */
+  int wgrad_ksplit;
+} frnn_b200_plan_t;
+
+/* Library / ABI version (major*1000 + minor). */
+int frnn_b200_version(void);
+
+/* Describe how (cell, B, T, N, D) is executed and how much scratch the caller must provide.
+ * Replaces the per-shape constraint solving + JIT of the reference
+ * (flashrnn/flashrnn/flashrnn.py:383-677, cuda_init_parametric.py). D must be a multiple of 16. */
+int frnn_b200_plan(int cell, int B, int T, int N, int D, frnn_b200_plan_t* out);
+
+/* Forward recurrence over T steps (flashrnn/flashrnn/fused/flashrnn.cc:69-145 forward();
+ * arithmetic of flashrnn/flashrnn2/reference.py:72-114 with fp32 state and bf16 R / h operands).
+ *   wx        : Wx, fp32 (wx_bf16 = 0) or bf16 (wx_bf16 = 1)
+ *   r_bf16    : R rounded to bf16
+ *   bias, initial : fp32
+ *   history   : out fp32 [S,B,T,N,D];  carry: out fp32 [S,B,1,N,D]
+ *   cache, hbf: scratch written for the backward pass, or NULL for inference
+ *   slstm_zero_first: 1 if every element of initial n is zero (reference.py:99)
+ *   wait_limit_ms: bound for every in-kernel wait (0 = default 2000 ms)              */
+int frnn_b200_forward(int cell, const void* wx, int wx_bf16, const void* r_bf16, const float* bias,
+                      const float* initial, float* history, float* carry, float* cache, void* hbf,
+                      int B, int T, int N, int D, int slstm_zero_first, int wait_limit_ms, int* err,
+                      void* stream);
+
+/* Reverse-time recurrence (flashrnn/flashrnn/fused/flashrnn.cc:147-247 backward();
+ * gradient structure of flashrnn/flashrnn/vanilla_fwbw/bw.py:20-98).
+ *   cache, history, initial : as written / passed in the forward call
+ *   d_history [S,B,T,N,D], d_carry [S,B,1,N,D] : incoming gradients, fp32
+ *   dwx  : out, [B,T,GW,N,D] in the Wx dtype
+ *   dgr  : out scratch, bf16 [B,T,GR,N,D] (operand of frnn_b200_wgrad)
+ *   d_initial : out fp32 [S,B,1,N,D];  db_part: out scratch fp32 [n_btiles,GB,N,D]    */
+int frnn_b200_backward(int cell, const float* cache, const float* history, const float* initial,
+                       const void* r_bf16, const float* d_history, const float* d_carry, void* dwx,
+                       int wx_bf16, void* dgr, float* d_initial, float* db_part, int B, int T, int N,
+                       int D, int slstm_zero_first, int wait_limit_ms, int* err, void* stream);
+
+/* dR[g,n,o,p] = sum_{b,t} dgr[b,t,g,n,o] * hbf[b,t,n,p] and db = sum over batch tiles of
+ * db_part (the cuBLAS GEMM + gradientBiasAggregationKernel of
+ * flashrnn/flashrnn/fused/flashrnn_fused_backward.cu:1050-1070, 627-666). Outputs fp32,
+ * overwritten (not accumulated). `work`: split-K scratch of plan.wgrad_work_bytes (may be
+ * NULL when that is 0).                                                               */
+int frnn_b200_wgrad(int cell, const void* dgr, const void* hbf, const float* db_part, float* dR,
+                    float* db, float* work, int B, int T, int N, int D, int* err, void* stream);
+
+#ifdef __cplusplus
+}
+#endif
+
+#endif /* FLASHRNN_B200_H_ */
