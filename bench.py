@@ -1,0 +1,331 @@
+#!/usr/bin/env python
+"""Benchmark of the fused recurrence hot path: fwd+bwd (B*T)/s on the headline workload.
+
+    python bench.py [--gpus N] [--steps K] [--warmup W] [--impl b200|reference]
+
+A "step" is one forward + BPTT backward (+ dR/db) of the whole workload
+(LSTM bf16, B=8, T=1024, N=3, D=256, seeded synthetic inputs) with loss = sum(h) and
+gradients for all four inputs. With N > 1 every rank runs the same-shaped workload on its own
+batch shard (weak scaling over batch; no collective inside the time loop) and the weight
+gradients dR/db are all-reduced over NCCL once per step.
+
+Prints ONE JSON line (rank 0). `value` is timed with CUDA events with the inputs resident in
+HBM; `e2e` goes through the public `flashrnn(...)` call with pinned HOST inputs, host->device
+copies and a device->host read of the loss inside the timed region.
+"""
+
+from __future__ import annotations
+
+import argparse
+import json
+import os
+import statistics
+import subprocess
+import sys
+import threading
+import time
+from pathlib import Path
+
+import torch
+
+ROOT = Path(__file__).resolve().parent
+sys.path.insert(0, str(ROOT))
+
+WORKLOAD = "cfg2_lstm_bf16_B8_T1024_N3_D256"
+METRIC = "fwd+bwd (B*T)/sec, LSTM bf16 B8 T1024 N3 D256"
+CELL, B, T, N, D, SEED = "lstm", 8, 1024, 3, 256, 1
+GR = 4
+FLOP_FWD = 2 * GR * D * D * N * B * T          # R*h contraction of the forward kernel
+FLOP_BWD = 2 * GR * D * D * N * B * T          # R^T*dg contraction of the backward kernel
+FLOP_WGRAD = 2 * GR * D * D * N * B * T        # dR contraction
+CPU_SAMPLE_T = 128                              # bounded CPU sample: same B, N, D, first 128 steps
+
+
+def _peaks():
+    p = ROOT / "MEASURED_PEAKS.json"
+    if p.exists():
+        d = json.loads(p.read_text())
+        return float(d["bf16_tflops"]), float(d["hbm_gbs"]), "measured"
+    return 1590.0, 6650.0, "fallback"
+
+
+class ClockSampler:
+    """Samples SM clocks / throttle reasons with nvidia-smi while the timed region runs."""
+
+    FIELDS = ("clocks.sm,clocks.max.sm,clocks_event_reasons.hw_slowdown,clocks_event_reasons.hw_thermal_slowdown,"
+              "clocks_event_reasons.sw_thermal_slowdown,clocks_event_reasons.sw_power_cap")
+
+    def __init__(self, index: int):
+        self.index, self.proc, self.lines = index, None, []
+
+    def __enter__(self):
+        try:
+            self.proc = subprocess.Popen(
+                ["nvidia-smi", "-i", str(self.index), f"--query-gpu={self.FIELDS}", "--format=csv,noheader,nounits",
+                 "-lms", "100"], stdout=subprocess.PIPE, stderr=subprocess.DEVNULL, text=True)
+            self.thread = threading.Thread(target=self._read, daemon=True)
+            self.thread.start()
+        except OSError:
+            self.proc = None
+        return self
+
+    def _read(self):
+        for line in self.proc.stdout:
+            self.lines.append(line.strip())
+
+    def __exit__(self, *exc):
+        if self.proc is not None:
+            time.sleep(0.15)
+            self.proc.terminate()
+            try:
+                self.proc.wait(timeout=5)
+            except subprocess.TimeoutExpired:
+                self.proc.kill()
+
+    def summary(self):
+        sm, mx, reasons = [], [], set()
+        names = ("hw_slowdown", "hw_thermal_slowdown", "sw_thermal_slowdown", "sw_power_cap")
+        for line in self.lines:
+            parts = [p.strip() for p in line.split(",")]
+            if len(parts) < 6:
+                continue
+            try:
+                sm.append(float(parts[0]))
+                mx.append(float(parts[1]))
+            except ValueError:
+                continue
+            for name, val in zip(names, parts[2:6]):
+                if val.lower().startswith("active"):
+                    reasons.add(name)
+        if not sm:
+            return {"sm_mhz": None, "sm_max_mhz": None, "reasons": [], "samples": 0}
+        return {"sm_mhz": statistics.median(sm), "sm_max_mhz": max(mx), "reasons": sorted(reasons), "samples": len(sm)}
+
+
+def cpu_baseline(threads: int | None = None, steps: int = 1):
+    """Time the CPU oracle (forward + explicit BPTT) on a bounded sample of the workload."""
+    from flashrnn_b200.workloads import make_inputs
+    from oracle import recurrence_port as port
+
+    if threads:
+        torch.set_num_threads(threads)
+    wx, R, b, initial = make_inputs(CELL, B, CPU_SAMPLE_T, N, D, SEED)
+    d_history = torch.zeros((2, B, CPU_SAMPLE_T, N, D))
+    d_history[0] = 1.0
+    d_carry = torch.zeros((2, B, 1, N, D))
+    port.forward_backward(wx[:, :8], R, b, initial, CELL, d_history[:, :, :8], d_carry)  # warm-up
+    times = []
+    for _ in range(steps):
+        t0 = time.perf_counter()
+        port.forward_backward(wx, R, b, initial, CELL, d_history, d_carry)
+        times.append(time.perf_counter() - t0)
+    dt = sum(times) / len(times)
+    return {
+        "value": B * CPU_SAMPLE_T / dt, "unit": "(B*T)/s", "cores": torch.get_num_threads(), "kind": "port",
+        "sample": f"oracle port (torch CPU, fp32 state, bf16-rounded operands), B={B} N={N} D={D}, first "
+                  f"{CPU_SAMPLE_T} of {T} steps, fwd + explicit BPTT, {dt:.2f} s per pass",
+    }, dt
+
+
+def run_reference(args):
+    rank = int(os.environ.get("RANK", "0"))
+    if rank != 0:
+        return
+    base, dt = cpu_baseline(steps=max(1, min(args.steps, 3)))
+    line = {
+        "impl": "reference", "metric": METRIC, "value": base["value"], "unit": "(B*T)/s", "n_gpus": args.gpus,
+        "steps": args.steps, "warmup": args.warmup, "ms_per_step": dt * 1e3 * (T / CPU_SAMPLE_T),
+        "higher_is_better": True, "scaling": "weak", "vs_baseline": None, "dtype": "f32 state, bf16 operands",
+        "data": "synthetic", "config": {"workload": WORKLOAD, "sample": base["sample"]},
+        "cpu_baseline": base,
+        "e2e": {"value": base["value"], "unit": "(B*T)/s", "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
+        "gpu_launches": 0,
+    }
+    print(json.dumps(line))
+
+
+def main():
+    ap = argparse.ArgumentParser()
+    ap.add_argument("--gpus", type=int, default=1)
+    ap.add_argument("--steps", type=int, default=20)
+    ap.add_argument("--warmup", type=int, default=3)
+    ap.add_argument("--impl", default="b200", choices=("b200", "reference"))
+    ap.add_argument("--no-cpu-baseline", action="store_true")
+    args = ap.parse_args()
+    if args.impl == "reference":
+        return run_reference(args)
+    args.warmup = max(args.warmup, 3)
+
+    world = int(os.environ.get("WORLD_SIZE", "1"))
+    rank = int(os.environ.get("RANK", "0"))
+    local_rank = int(os.environ.get("LOCAL_RANK", "0"))
+    if not torch.cuda.is_available():
+        raise SystemExit("bench.py needs a CUDA device: the recurrence has no CPU path")
+    torch.cuda.set_device(local_rank)
+    dev = torch.device("cuda", local_rank)
+    dist = None
+    if world > 1:
+        import torch.distributed as dist
+
+        dist.init_process_group("nccl", device_id=dev)
+
+    from flashrnn_b200 import _lib, flashrnn, poll_errors
+    from flashrnn_b200.workloads import make_inputs
+
+    _lib.load()
+    # every rank holds its own batch shard of a global batch of world*B sequences
+    wx32, R32, b32, init32 = make_inputs(CELL, B, T, N, D, SEED + rank)
+    R32, b32 = make_inputs(CELL, B, T, N, D, SEED)[1:3]  # weights are replicated
+    h_wx = wx32.to(torch.bfloat16).pin_memory()
+    h_R, h_b, h_init = R32.pin_memory(), b32.pin_memory(), init32.pin_memory()
+    d_wx, d_R, d_b, d_init = (t.to(dev) for t in (h_wx, h_R, h_b, h_init))
+    flush = torch.empty(256 * 1024 * 1024, dtype=torch.uint8, device=dev)
+
+    def step_resident():
+        leaves = [t.detach().requires_grad_(True) for t in (d_wx, d_R, d_b, d_init)]
+        hist, _ = flashrnn(*leaves, function=CELL, backend="b200", dtype="bfloat16")
+        hist[0].sum().backward()
+        if dist is not None:
+            dist.all_reduce(leaves[1].grad)
+            dist.all_reduce(leaves[2].grad)
+        return leaves
+
+    def step_e2e():
+        leaves = [t.to(dev, non_blocking=True).requires_grad_(True) for t in (h_wx, h_R, h_b, h_init)]
+        hist, _ = flashrnn(*leaves, function=CELL, backend="b200", dtype="bfloat16")
+        loss = hist[0].sum()
+        loss.backward()
+        if dist is not None:
+            dist.all_reduce(leaves[1].grad)
+            dist.all_reduce(leaves[2].grad)
+        return float(loss.item())
+
+    def barrier():
+        torch.cuda.synchronize()
+        if dist is not None:
+            dist.barrier()
+        torch.cuda.synchronize()
+
+    def timed(fn, steps):
+        total_ms = 0.0
+        for _ in range(steps):
+            flush.fill_(1)  # evict L2 between timed iterations (untimed)
+            e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+            e0.record()
+            fn()
+            e1.record()
+            e1.synchronize()
+            total_ms += e0.elapsed_time(e1)
+        return total_ms
+
+    for _ in range(args.warmup):
+        step_resident()
+        step_e2e()
+    poll_errors(block=True)
+    barrier()
+    with ClockSampler(local_rank) as clocks:
+        ms = timed(step_resident, args.steps)
+        barrier()
+        ms_e2e = timed(step_e2e, args.steps)
+        barrier()
+    poll_errors(block=True)
+
+    # per-kernel durations, measured with the same inputs through the C ABI
+    breakdown = kernel_breakdown(_lib, dev, d_wx, d_R, d_b, d_init, flush, max(3, min(args.steps, 10)))
+
+    t_ms = torch.tensor([ms, ms_e2e], dtype=torch.float64, device=dev)
+    if dist is not None:
+        dist.all_reduce(t_ms, op=dist.ReduceOp.MAX)
+    ms, ms_e2e = (float(v) for v in t_ms.tolist())
+    if rank == 0:
+        bf16_peak, hbm_peak, peak_kind = _peaks()
+        value = world * B * T * args.steps / (ms * 1e-3)
+        e2e_value = world * B * T * args.steps / (ms_e2e * 1e-3)
+        dom = max(("fwd", "bwd"), key=lambda k: breakdown[k])
+        flops = FLOP_FWD if dom == "fwd" else FLOP_BWD
+        achieved = flops / (breakdown[dom] * 1e-3) / 1e12
+        line = {
+            "metric": METRIC, "value": value, "unit": "(B*T)/s", "n_gpus": world, "steps": args.steps,
+            "warmup": args.warmup, "ms_per_step": ms / args.steps, "higher_is_better": True, "scaling": "weak",
+            "vs_baseline": None, "dtype": "bf16 operands, f32 state/accumulate", "data": "synthetic",
+            "config": {"workload": WORKLOAD, "cell": CELL, "B_per_gpu": B, "T": T, "N": N, "D": D,
+                       "sharding": "batch (weights replicated, dR/db all-reduced)" if world > 1 else "none",
+                       "l2": "256 MiB written between timed steps (untimed)"},
+            "e2e": {"value": e2e_value, "unit": "(B*T)/s", "ms_per_step": ms_e2e / args.steps,
+                    "h2d_bytes_per_step": sum(t.numel() * t.element_size() for t in (h_wx, h_R, h_b, h_init)),
+                    "d2h_bytes_per_step": 4},
+            "gpu_launches": args.steps * 5,
+            "kernels_ms": breakdown,
+            "roofline": {"bound": "tensor", "kernel": f"frnn_{dom}_kernel", "achieved": achieved, "peak": bf16_peak,
+                         "unit": "TFLOP/s", "frac": achieved / bf16_peak, "peak_source": peak_kind,
+                         "traffic": None,
+                         "note": "step-latency bound: T dependent steps; see DESIGN.md for the per-step budget"},
+            "clocks": clocks.summary(),
+        }
+        if not args.no_cpu_baseline and world == 1:
+            line["cpu_baseline"], _ = cpu_baseline()
+        print(json.dumps(line))
+    if dist is not None:
+        dist.destroy_process_group()
+
+
+def kernel_breakdown(_lib, dev, d_wx, d_R, d_b, d_init, flush, reps):
+    """Average duration (ms) of each of our kernels on the workload, CUDA events on the launch stream."""
+    lib = _lib.load()
+    plan = _lib.plan(CELL, B, T, N, D)
+    S, gw, gb = 2, 4, 4
+    f32, bf = torch.float32, torch.bfloat16
+    history = torch.empty((S, B, T, N, D), dtype=f32, device=dev)
+    carry = torch.empty((S, B, 1, N, D), dtype=f32, device=dev)
+    cache = torch.empty(plan.cache_bytes // 4, dtype=f32, device=dev)
+    hbf = torch.empty(plan.hbf_bytes // 2, dtype=bf, device=dev)
+    d_history = torch.zeros_like(history)
+    d_history[0] = 1.0
+    d_carry = torch.zeros_like(carry)
+    dwx = torch.empty_like(d_wx)
+    dgr = torch.empty(plan.dgr_bytes // 2, dtype=bf, device=dev)
+    d_initial = torch.empty_like(carry)
+    db_part = torch.empty(plan.dbpart_bytes // 4, dtype=f32, device=dev)
+    dR = torch.empty((GR, N, D, D), dtype=f32, device=dev)
+    db = torch.empty((gb, N, D), dtype=f32, device=dev)
+    work = torch.empty(max(plan.wgrad_work_bytes // 4, 1), dtype=f32, device=dev)
+    err = torch.zeros(4, dtype=torch.int32, device=dev)
+    stream = torch.cuda.current_stream(dev).cuda_stream
+    cid = _lib.CELLS[CELL]
+    d_R = d_R.to(bf).contiguous()
+
+    def fwd():
+        _lib.check(lib.frnn_b200_forward(cid, d_wx.data_ptr(), 1, d_R.data_ptr(), d_b.data_ptr(), d_init.data_ptr(),
+                                         history.data_ptr(), carry.data_ptr(), cache.data_ptr(), hbf.data_ptr(),
+                                         B, T, N, D, 0, 0, err.data_ptr(), stream), "forward")
+
+    def bwd():
+        _lib.check(lib.frnn_b200_backward(cid, cache.data_ptr(), history.data_ptr(), d_init.data_ptr(),
+                                          d_R.data_ptr(), d_history.data_ptr(), d_carry.data_ptr(), dwx.data_ptr(), 1,
+                                          dgr.data_ptr(), d_initial.data_ptr(), db_part.data_ptr(), B, T, N, D, 0, 0,
+                                          err.data_ptr(), stream), "backward")
+
+    def wgrad():
+        _lib.check(lib.frnn_b200_wgrad(cid, dgr.data_ptr(), hbf.data_ptr(), db_part.data_ptr(), dR.data_ptr(),
+                                       db.data_ptr(), work.data_ptr(), B, T, N, D, err.data_ptr(), stream), "wgrad")
+
+    out = {}
+    for name, fn in (("fwd", fwd), ("bwd", bwd), ("wgrad", wgrad)):
+        fn()
+        total = 0.0
+        for _ in range(reps):
+            flush.fill_(1)
+            e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+            e0.record()
+            fn()
+            e1.record()
+            e1.synchronize()
+            total += e0.elapsed_time(e1)
+        out[name] = total / reps
+    if int(err[0].item()) != 0:
+        raise RuntimeError(f"device-side error {err.tolist()}")
+    return out
+
+
+if __name__ == "__main__":
+    main()

@@ -1,0 +1,132 @@
+"""Parity of the CUDA path (through the C ABI) with the reference vectors and the CPU oracle.
+
+Tolerance (the north star's): max-abs 2e-2 for O(1) tensors; tensors whose magnitude is large
+(dR, db, sLSTM c/n) are judged by the error normalised by max|ref| <= 1e-2, the reference's own
+convention (tools/bw_qualify.py:12-17).
+"""
+
+import pytest
+import torch
+
+from oracle import recurrence_port as port
+from tests import _golden
+
+pytestmark = pytest.mark.gpu
+
+ATOL, RTOL_SCALED = 2e-2, 1e-2
+
+
+def _check(name, key, got, ref, log):
+    r = _golden.report(key, got.detach().cpu().float(), ref)
+    log.append(r)
+    assert r["max_abs"] <= ATOL or r["scaled"] <= RTOL_SCALED, (name, r)
+    assert torch.isfinite(got).all(), (name, key)
+
+
+def _run_gpu(g, dev, dtype=torch.float32):
+    from flashrnn_b200 import flashrnn_torch, poll_errors
+
+    meta = g["meta"]
+    T, n_chunks = meta["T"], meta["n_chunks"]
+    step = T // n_chunks
+    leaves = [g[k].to(dev).to(dtype).requires_grad_(True) for k in ("wx", "R", "b", "initial")]
+    wx, R, b, carry = leaves
+    pieces = []
+    for c in range(n_chunks):
+        h, carry = flashrnn_torch(wx[:, c * step:(c + 1) * step], R, b, carry, cell=meta["cell"],
+                                  numerics="fp32_state_bf16_mma")
+        pieces.append(h)
+    history = torch.cat(pieces, dim=2)
+    loss = (history * g["d_history"].to(dev)).sum() + (carry * g["d_carry"].to(dev)).sum()
+    loss.backward()
+    torch.cuda.synchronize()
+    poll_errors(block=True)
+    return history, carry, [t.grad for t in leaves]
+
+
+@pytest.mark.parametrize("name", _golden.CASES)
+def test_cuda_matches_reference_vectors(name, cuda_device):
+    g = _golden.load(name)
+    s = g["meta"]["time_stride"]
+    history, carry, (dwx, dR, db, dinit) = _run_gpu(g, cuda_device)
+    log = []
+    assert history.dtype == torch.float32 and carry.dtype == torch.float32
+    _check(name, "history", history[:, :, ::s], g["history"], log)
+    _check(name, "carry", carry, g["carry"], log)
+    _check(name, "dwx", dwx[:, ::s], g["dwx"], log)
+    _check(name, "dR", dR, g["dR"], log)
+    _check(name, "db", db, g["db"], log)
+    _check(name, "d_initial", dinit, g["d_initial"], log)
+    print(name, [(r["name"], f"{r['max_abs']:.2e}", f"{r['scaled']:.2e}") for r in log])
+
+
+# (cell, B, T, N, D, seed, zero_initial): shapes that exercise every launch plan
+SHAPES = [
+    ("lstm", 8, 48, 3, 256, 21, False),    # headline geometry: cluster of 8, batch tile 8
+    ("lstm", 16, 20, 2, 128, 22, False),   # batch tile 16
+    ("lstm", 20, 12, 1, 64, 23, False),    # two batch tiles, the second ragged (4 rows)
+    ("lstm", 3, 17, 2, 48, 24, False),     # unit 16, cluster of 3, ragged batch
+    ("lstm", 4, 10, 1, 384, 25, False),    # cluster of 12 (non-portable size)
+    ("lstm", 2, 6, 1, 512, 26, False),     # cluster of 16
+    ("slstm", 16, 40, 4, 128, 27, True),   # sLSTM geometry of the third config
+    ("slstm", 5, 16, 2, 64, 28, False),
+    ("gru", 16, 24, 1, 256, 29, False),
+    ("gru", 6, 9, 3, 32, 30, False),
+    ("elman", 16, 30, 2, 128, 31, False),
+    ("elman", 1, 1, 1, 16, 32, False),     # single step, single row
+    ("lstm", 1, 1, 1, 3, 33, False),       # the reference's smallest portable-gate shape
+    ("gru", 3, 3, 2, 7, 34, False),
+]
+
+
+@pytest.mark.parametrize("shape", SHAPES, ids=lambda s: f"{s[0]}-B{s[1]}-T{s[2]}-N{s[3]}-D{s[4]}")
+def test_cuda_matches_oracle(shape, cuda_device):
+    from flashrnn_b200.workloads import make_inputs
+
+    cell, B, T, N, D, seed, zero = shape
+    wx, R, b, initial = make_inputs(cell, B, T, N, D, seed, zero)
+    gen = torch.Generator().manual_seed(seed + 500)
+    S = port.SIZES[cell][3]
+    d_history = torch.randn((S, B, T, N, D), generator=gen)
+    d_carry = torch.randn((S, B, 1, N, D), generator=gen)
+    ref_h, ref_c, (r_dwx, r_dR, r_db, r_dinit) = port.forward_backward(wx, R, b, initial, cell, d_history, d_carry)
+    g = dict(meta=dict(cell=cell, T=T, n_chunks=1), wx=wx, R=R, b=b, initial=initial, d_history=d_history, d_carry=d_carry)
+    history, carry, (dwx, dR, db, dinit) = _run_gpu(g, cuda_device)
+    log = []
+    name = str(shape)
+    _check(name, "history", history, ref_h, log)
+    _check(name, "carry", carry, ref_c, log)
+    _check(name, "dwx", dwx, r_dwx, log)
+    _check(name, "dR", dR, r_dR, log)
+    _check(name, "db", db, r_db, log)
+    _check(name, "d_initial", dinit, r_dinit, log)
+    print(name, [(r["name"], f"{r['max_abs']:.2e}", f"{r['scaled']:.2e}") for r in log])
+
+
+def test_carry_continuation_is_exact(cuda_device):
+    """Two chunks with the carry passed on reproduce the single call bit for bit (fp32 carry)."""
+    from flashrnn_b200 import flashrnn_torch
+    from flashrnn_b200.workloads import make_inputs
+
+    for cell in ("lstm", "slstm", "gru", "elman"):
+        wx, R, b, initial = (t.to(cuda_device) for t in make_inputs(cell, 8, 32, 2, 64, 40, cell == "slstm"))
+        full, full_c = flashrnn_torch(wx, R, b, initial, cell=cell)
+        h1, c1 = flashrnn_torch(wx[:, :13], R, b, initial, cell=cell)
+        h2, c2 = flashrnn_torch(wx[:, 13:], R, b, c1, cell=cell)
+        assert torch.equal(torch.cat((h1, h2), dim=2), full), cell
+        assert torch.equal(c2, full_c), cell
+        assert torch.equal(full[:, :, -1:], full_c), cell
+
+
+def test_bf16_inputs_and_flashrnn_entry(cuda_device):
+    """flashrnn(..., dtype='bfloat16') == flashrnn_torch on the pre-rounded inputs; states=None is zeros."""
+    from flashrnn_b200 import flashrnn, flashrnn_torch
+    from flashrnn_b200.workloads import make_inputs
+
+    wx, R, b, initial = (t.to(cuda_device) for t in make_inputs("lstm", 8, 16, 3, 256, 41, True))
+    h_a, c_a = flashrnn(wx, R, b, None, function="lstm", backend="b200", dtype="bfloat16")
+    h_b, c_b = flashrnn_torch(wx.bfloat16().float(), R, b, initial, cell="lstm")
+    assert h_a.shape == (2, 8, 16, 3, 256) and c_a.shape == (2, 8, 1, 3, 256)
+    assert torch.equal(h_a, h_b) and torch.equal(c_a, c_b)
+    with pytest.raises(ValueError):
+        flashrnn(wx, R, b, None, function="lstm", backend="cuda_fused")
