@@ -241,8 +241,8 @@ def main():
         bf16_peak, hbm_peak, peak_kind = _peaks()
         value = world * B * T * args.steps / (ms * 1e-3)
         e2e_value = world * B * T * args.steps / (ms_e2e * 1e-3)
-        dom = max(("fwd", "bwd"), key=lambda k: breakdown[k])
-        flops = FLOP_FWD if dom == "fwd" else FLOP_BWD
+        dom = max(("fwd", "bwd", "wgrad"), key=lambda k: breakdown[k])
+        flops = {"fwd": FLOP_FWD, "bwd": FLOP_BWD, "wgrad": FLOP_WGRAD}[dom]
         achieved = flops / (breakdown[dom] * 1e-3) / 1e12
         line = {
             "metric": METRIC, "value": value, "unit": "(B*T)/s", "n_gpus": world, "steps": args.steps,
@@ -289,7 +289,7 @@ def kernel_breakdown(_lib, dev, d_wx, d_R, d_b, d_init, flush, reps):
     dR = torch.empty((GR, N, D, D), dtype=f32, device=dev)
     db = torch.empty((gb, N, D), dtype=f32, device=dev)
     work = torch.empty(max(plan.wgrad_work_bytes // 4, 1), dtype=f32, device=dev)
-    err = torch.zeros(4, dtype=torch.int32, device=dev)
+    err = torch.zeros(32, dtype=torch.int32, device=dev)
     stream = torch.cuda.current_stream(dev).cuda_stream
     cid = _lib.CELLS[CELL]
     d_R = d_R.to(bf).contiguous()
@@ -324,6 +324,18 @@ def kernel_breakdown(_lib, dev, d_wx, d_R, d_b, d_init, flush, reps):
         out[name] = total / reps
     if int(err[0].item()) != 0:
         raise RuntimeError(f"device-side error {err.tolist()}")
+    # in-kernel phase timers of CTA 0 (SM cycles per step)
+    names = ("input_wait", "operand_or_mma_wait", "acc_read_or_cell", "sync_or_mma_wait", "cell_exchange_or_scatter")
+    for name, fn in (("fwd", fwd), ("bwd", bwd)):
+        err.zero_()
+        err[3] = 1
+        fn()
+        torch.cuda.synchronize()
+        v = err.tolist()
+        out[name + "_phase_cycles_per_step"] = {**{k: round(v[8 + i] / T, 1) for i, k in enumerate(names)},
+                                                "x5": round(v[13] / T, 1), "x6": round(v[14] / T, 1),
+                                                "mma_warp_wait": round(v[16] / T, 1), "mma_warp_issue": round(v[17] / T, 1)}
+    err.zero_()
     return out
 
 

@@ -20,10 +20,23 @@ template <> struct CellTraits<kSLSTM> { static constexpr int GR = 4, GW = 4, GB 
 template <> struct CellTraits<kGRU>   { static constexpr int GR = 3, GW = 3, GB = 4, S = 1, GC = 4; };
 template <> struct CellTraits<kElman> { static constexpr int GR = 1, GW = 1, GB = 1, S = 1, GC = 1; };
 
-__device__ __forceinline__ float sigmoid_f(float x) { return __frcp_rn(1.0f + __expf(-x)); }
+// MUFU-based primitives: ex2.approx / rcp.approx are accurate to about 2 ulp, far inside the
+// tolerance of a bf16-operand recurrence, and take one instruction each where the IEEE-rounded
+// reciprocal takes a dozen.
+__device__ __forceinline__ float rcp_fast(float x) {
+  float r;
+  asm("rcp.approx.ftz.f32 %0, %1;" : "=f"(r) : "f"(x));
+  return r;
+}
+__device__ __forceinline__ float exp2_fast(float x) {
+  float r;
+  asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(r) : "f"(x));
+  return r;
+}
+__device__ __forceinline__ float sigmoid_f(float x) { return rcp_fast(1.0f + exp2_fast(-1.4426950408889634f * x)); }
 __device__ __forceinline__ float tanh_f(float x) {
   // 1 - 2/(1+e^{2x}); saturates correctly at +-1 when e^{2x} over/underflows.
-  return 1.0f - 2.0f * __frcp_rn(1.0f + __expf(2.0f * x));
+  return 1.0f - 2.0f * rcp_fast(1.0f + exp2_fast(2.885390081777927f * x));
 }
 __device__ __forceinline__ float logsigmoid_f(float x) {
   return fminf(x, 0.0f) - __logf(1.0f + __expf(-fabsf(x)));

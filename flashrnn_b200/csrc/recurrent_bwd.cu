@@ -84,6 +84,7 @@ frnn_bwd_kernel(const BwdParams p, const __grid_constant__ CUtensorMap cache_map
   uint8_t* const stages = smem + ((Cfg::DGBUF_BYTES + 2 * part_bytes + Cfg::DBUF_BYTES + 127) & ~127);
   const volatile int* abort_flag = p.err;
   const uint64_t limit = p.wait_limit_ns;
+  const bool prof = p.err[3] != 0 && blockIdx.x == 0 && lane == 0 && (warp == 0 || warp == 4);
 
   if (tid == 0) {
     mbar_init(smem_u32(&s_part_bar[0]), 1);
@@ -173,12 +174,15 @@ frnn_bwd_kernel(const BwdParams p, const __grid_constant__ CUtensorMap cache_map
     if (lane == 0) {
       const uint32_t idesc = umma_idesc_bf16(128, BT, false, false);
       const uint32_t db_addr = smem_u32(dgbuf);
+      long long pw = 0, pi = 0;
       for (int it = 0; it < T; ++it) {
+        const long long m0 = prof ? clock64() : 0;
         if (!mbar_wait_bounded<false>(smem_u32(&s_dg_bar), it & 1, limit, abort_flag)) {
           report(p.err, kErrWaitDg, it);
           break;
         }
         tc_fence_after_sync();
+        const long long m1 = prof ? clock64() : 0;
         for (int j = 0; j < MTB; ++j) {
           for (int kk = 0; kk < ROWS / 16; ++kk) {
             const uint64_t bdesc = umma_smem_desc(db_addr + kk * 2 * (BT * 16), BT * 16, 128);
@@ -186,7 +190,9 @@ frnn_bwd_kernel(const BwdParams p, const __grid_constant__ CUtensorMap cache_map
           }
         }
         umma_commit(smem_u32(&s_mma_bar));
+        if (prof) { pw += m1 - m0; pi += clock64() - m1; }
       }
+      if (prof) { p.err[16] = static_cast<int>(pw); p.err[17] = static_cast<int>(pi); }
     }
   } else if (warp == 5) {
     if (lane == 0) {
@@ -218,8 +224,10 @@ frnn_bwd_kernel(const BwdParams p, const __grid_constant__ CUtensorMap cache_map
     const size_t ND = static_cast<size_t>(N) * D;
     const int sbu = p.box_b * U;
     const uint32_t dg_off = kmajor_offset(BT, ib, ul);
+    long long pc[5] = {0, 0, 0, 0, 0};
     for (int it = 0; it <= T; ++it) {
       const int t = T - 1 - it;
+      const long long c0 = prof ? clock64() : 0;
       float ds[S][IPT];
 #pragma unroll
       for (int q = 0; q < S; ++q)
@@ -253,6 +261,7 @@ frnn_bwd_kernel(const BwdParams p, const __grid_constant__ CUtensorMap cache_map
         }
         mbar_arrive(smem_u32(&s_empty[s]));
       }
+      const long long c1 = prof ? clock64() : 0;
       if (it >= 1) {
         // partial dh for this step from every CTA of the cluster
         const int pb = it & 1;
@@ -271,6 +280,7 @@ frnn_bwd_kernel(const BwdParams p, const __grid_constant__ CUtensorMap cache_map
           }
         }
       }
+      const long long c2 = prof ? clock64() : 0;
       if (it == T) {
         if (active) {
 #pragma unroll
@@ -334,11 +344,13 @@ frnn_bwd_kernel(const BwdParams p, const __grid_constant__ CUtensorMap cache_map
       fence_proxy_async();
       tc_fence_before_sync();
       mbar_arrive(smem_u32(&s_dg_bar));
+      const long long c3 = prof ? clock64() : 0;
       if (!mbar_wait_bounded<false>(smem_u32(&s_mma_bar), it & 1, limit, abort_flag)) {
         report(p.err, kErrWaitMma, it);
         break;
       }
       tc_fence_after_sync();
+      const long long c4 = prof ? clock64() : 0;
       // scatter partial dh_{t-1} rows to the CTAs that own those units
       const int nb = (it + 1) & 1;
       const uint32_t part_base = smem_u32(part) + static_cast<uint32_t>(nb) * part_bytes + static_cast<uint32_t>(rank) * BV * U * 4;
@@ -361,6 +373,13 @@ frnn_bwd_kernel(const BwdParams p, const __grid_constant__ CUtensorMap cache_map
         }
       }
       tc_fence_before_sync();
+      if (prof) {
+        pc[0] += c1 - c0; pc[1] += c2 - c1; pc[2] += c3 - c2; pc[3] += c4 - c3; pc[4] += clock64() - c4;
+      }
+    }
+    if (prof) {
+#pragma unroll
+      for (int q = 0; q < 5; ++q) p.err[8 + q] = static_cast<int>(pc[q]);
     }
   }
 

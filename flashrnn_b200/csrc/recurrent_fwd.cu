@@ -75,6 +75,7 @@ frnn_fwd_kernel(const FwdParams p, const __grid_constant__ CUtensorMap wx_map) {
   uint8_t* const wxs = smem + ((2 * hbuf_bytes + Cfg::GBUF_BYTES + 127) & ~127);
   const volatile int* abort_flag = p.err;
   const uint64_t limit = p.wait_limit_ns;
+  const bool prof = p.err[3] != 0 && blockIdx.x == 0 && lane == 0 && (warp == 0 || warp == 4);
   const int a_cols = MT * (D / 2);
   uint32_t tmem_cols = 32;
   while (tmem_cols < static_cast<uint32_t>(Cfg::A_COL0 + a_cols)) tmem_cols <<= 1;
@@ -169,8 +170,10 @@ frnn_fwd_kernel(const FwdParams p, const __grid_constant__ CUtensorMap wx_map) {
   if (warp == 4) {
     if (lane == 0) {
       const uint32_t idesc = umma_idesc_bf16(128, BT, false, false);
+      long long pw = 0, pi = 0;
       for (int t = 0; t < T; ++t) {
         const int pb = t & 1;
+        const long long m0 = prof ? clock64() : 0;
         if (t >= 1) {
           if (!mbar_wait_bounded<true>(smem_u32(&s_hbar[pb]), ((t - 1) >> 1) & 1, limit, abort_flag)) {
             report(p.err, kErrWaitH, t);
@@ -180,6 +183,7 @@ frnn_fwd_kernel(const FwdParams p, const __grid_constant__ CUtensorMap wx_map) {
         }
         fence_proxy_async();
         tc_fence_after_sync();
+        const long long m1 = prof ? clock64() : 0;
         const uint32_t hb = smem_u32(hbuf + pb * hbuf_bytes);
         for (int j = 0; j < MT; ++j) {
           for (int kk = 0; kk < D / 16; ++kk) {
@@ -189,7 +193,9 @@ frnn_fwd_kernel(const FwdParams p, const __grid_constant__ CUtensorMap wx_map) {
           }
         }
         umma_commit(smem_u32(&s_mma_bar));
+        if (prof) { pw += m1 - m0; pi += clock64() - m1; }
       }
+      if (prof) { p.err[16] = static_cast<int>(pw); p.err[17] = static_cast<int>(pi); }
     }
   } else if (warp == 5) {
     if (lane == 0) {
@@ -211,13 +217,23 @@ frnn_fwd_kernel(const FwdParams p, const __grid_constant__ CUtensorMap wx_map) {
     float* cache = p.cache == nullptr ? nullptr : p.cache + ((static_cast<size_t>(b0 + ib) * T * CT::GC) * N + n) * D + d0;
     __nv_bfloat16* hbf = p.hbf == nullptr ? nullptr : p.hbf + ((static_cast<size_t>(b0 + ib) * (T + 1) + 1) * N + n) * D + d0;
     const uint32_t h_off = kmajor_offset(BT, ib, d0);
+    // distance from this CTA's shared window to every peer's (constant for the whole kernel)
+    uint32_t peer_delta[16];
+    {
+      const uint32_t base = smem_u32(smem);
+#pragma unroll
+      for (int d = 0; d < 16; ++d) peer_delta[d] = d < C ? map_to_cta(base, d) - base : 0u;
+    }
     const size_t ND = static_cast<size_t>(N) * D;
+    long long pc[7] = {0, 0, 0, 0, 0, 0, 0};
     for (int t = 0; t < T; ++t) {
       const int s = t % kWxStages;
+      const long long c0 = prof ? clock64() : 0;
       if (!mbar_wait_bounded<false>(smem_u32(&s_wx_full[s]), (t / kWxStages) & 1, limit, abort_flag)) {
         report(p.err, kErrWaitWx, t);
         break;
       }
+      const long long c1 = prof ? clock64() : 0;
       float wx[CT::GW][IPT];
       if (active) {
         const uint8_t* ws = wxs + s * Cfg::WX_STAGE_BYTES;
@@ -234,6 +250,7 @@ frnn_fwd_kernel(const FwdParams p, const __grid_constant__ CUtensorMap wx_map) {
         break;
       }
       tc_fence_after_sync();
+      const long long c2 = prof ? clock64() : 0;
       // phase 1: accumulator rows (lane = gate row) -> gate buffer [batch][row]
       {
         uint32_t r[MT][BV / 8][8];
@@ -250,12 +267,15 @@ frnn_fwd_kernel(const FwdParams p, const __grid_constant__ CUtensorMap wx_map) {
             for (int q = 0; q < 8; ++q) gbuf[(8 * c + q) * Cfg::GROW + j * 128 + tid] = __uint_as_float(r[j][c][q]);
       }
       tc_fence_before_sync();
+      const long long c3 = prof ? clock64() : 0;
       mbar_arrive(smem_u32(&s_epi_bar));
       if (!mbar_wait_bounded<false>(smem_u32(&s_epi_bar), t & 1, limit, abort_flag)) {
         report(p.err, kErrWaitEpi, t);
         break;
       }
+      const long long c4 = prof ? clock64() : 0;
       // phase 2: the cell, for IPT consecutive units of one batch row
+      long long c5 = 0, c6 = 0;
       if (active) {
         float ry[CT::GR][IPT];
 #pragma unroll
@@ -282,16 +302,21 @@ frnn_fwd_kernel(const FwdParams p, const __grid_constant__ CUtensorMap wx_map) {
         uint32_t hp[IPT / 2];
 #pragma unroll
         for (int j = 0; j < IPT; j += 2) hp[j / 2] = pack_bf16x2(st[0][j], st[0][j + 1]);
+        if (prof) c5 = clock64();
         if (t + 1 < T) {
           const uint32_t dst = smem_u32(hbuf + ((t + 1) & 1) * hbuf_bytes) + h_off;
           const uint32_t bar = smem_u32(&s_hbar[(t + 1) & 1]);
-          for (int d = 0; d < C; ++d) {
-            const uint32_t ra = map_to_cta(dst, d), rb = map_to_cta(bar, d);
-            if constexpr (IPT == 2) st_async_b32(ra, hp[0], rb);
-            else if constexpr (IPT == 4) st_async_v2_b32(ra, hp[0], hp[1], rb);
-            else st_async_v4_b32(ra, hp[0], hp[1], hp[2], hp[3], rb);
+#pragma unroll
+          for (int d = 0; d < 16; ++d) {
+            if (d < C) {
+              const uint32_t ra = dst + peer_delta[d], rb = bar + peer_delta[d];
+              if constexpr (IPT == 2) st_async_b32(ra, hp[0], rb);
+              else if constexpr (IPT == 4) st_async_v2_b32(ra, hp[0], hp[1], rb);
+              else st_async_v4_b32(ra, hp[0], hp[1], hp[2], hp[3], rb);
+            }
           }
         }
+        if (prof) c6 = clock64();
 #pragma unroll
         for (int q = 0; q < CT::S; ++q) st_f32_vec<IPT>(hist + q * sBTND + t * ND, st[q]);
         if (cache != nullptr && CELL != kElman) {
@@ -303,6 +328,14 @@ frnn_fwd_kernel(const FwdParams p, const __grid_constant__ CUtensorMap wx_map) {
           for (int j = 0; j < IPT; j += 2) *reinterpret_cast<uint32_t*>(hbf + t * ND + j) = hp[j / 2];
         }
       }
+      if (prof) {
+        pc[0] += c1 - c0; pc[1] += c2 - c1; pc[2] += c3 - c2; pc[3] += c4 - c3; pc[4] += c5 - c4;
+        pc[5] += c6 - c5; pc[6] += clock64() - c6;
+      }
+    }
+    if (prof) {
+#pragma unroll
+      for (int q = 0; q < 7; ++q) p.err[8 + q] = static_cast<int>(pc[q]);
     }
     if (active) {
 #pragma unroll

@@ -94,7 +94,7 @@ class _Recurrence(torch.autograd.Function):
             if plan.cache_bytes:
                 cache = torch.empty(plan.cache_bytes // 4, dtype=torch.float32, device=dev)
             hbf = torch.empty(plan.hbf_bytes // 2, dtype=torch.bfloat16, device=dev)
-        err = torch.zeros(4, dtype=torch.int32, device=dev)
+        err = torch.zeros(32, dtype=torch.int32, device=dev)
         rc = lib.frnn_b200_forward(
             _lib.CELLS[cell], wx_c.data_ptr(), int(wx_c.dtype == torch.bfloat16), r_bf.data_ptr(), b32.data_ptr(),
             init32.data_ptr(), history.data_ptr(), carry.data_ptr(), _ptr(cache), _ptr(hbf), B, T, N, D,
@@ -135,7 +135,7 @@ class _Recurrence(torch.autograd.Function):
         work = None
         if plan.wgrad_work_bytes:
             work = torch.empty(plan.wgrad_work_bytes // 4, dtype=torch.float32, device=dev)
-        err = torch.zeros(4, dtype=torch.int32, device=dev)
+        err = torch.zeros(32, dtype=torch.int32, device=dev)
         stream = _stream(dev)
         rc = lib.frnn_b200_backward(
             _lib.CELLS[cell], _ptr(cache) if cache.numel() else None, history.data_ptr(), init32.data_ptr(),

@@ -9,8 +9,13 @@
  *   -1 unknown cell, -2 shape not supported by this kernel family (see frnn_b200_plan),
  *   -3 tensor-memory budget exceeded, -4 TMA descriptor could not be built, -5 bad argument.
  * Device-side problems (a bounded wait that ran out) are reported through the caller-owned
- * `err` array (int[4], zeroed by the caller): err[0] = code (101..107), err[1] = step,
+ * `err` array (int[32], zeroed by the caller): err[0] = code (101..107), err[1] = step,
  * err[2] = CTA. The kernels then leave in an orderly way; the context stays usable.
+ * In-kernel phase timers (the counterpart of the reference's %globaltimer phase probes,
+ * flashrnn/flashrnn2/hybrid_fw2d.cu:85-89,366-373): if the caller sets err[3] = 1, CTA 0 adds up
+ * SM clock cycles per phase over all steps into err[8..12] (epilogue warp: input wait, operand /
+ * tensor-core wait, accumulator read, epilogue sync, cell + stores + exchange) and err[16..17]
+ * (MMA warp: operand wait, issue).
  *
  * Counterparts in the reference (0z5a/flashrnn):
  *   flashrnn/flashrnn/fused/flashrnn.cc:56-347      pybind class FlashRNNFuncFused
