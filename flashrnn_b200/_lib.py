@@ -20,6 +20,7 @@ ERROR_TEXT = {
     -3: "tensor-memory budget exceeded",
     -4: "TMA descriptor could not be built",
     -5: "bad argument",
+    -6: "problem too large for the built-in scratch of frnn_b200_wgrad_noalloc",
     101: "recurrent operand of a step never arrived",
     102: "tensor-core completion barrier timed out",
     103: "TMA input stage never filled",
@@ -53,6 +54,8 @@ SIGNATURES = {
                                    c_void_p, c_void_p]),
     "frnn_b200_wgrad": (c_int, [c_int, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_int,
                                 c_int, c_int, c_void_p, c_void_p]),
+    "frnn_b200_wgrad_noalloc": (c_int, [c_int, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_int, c_int,
+                                        c_int, c_void_p, c_void_p]),
 }
 
 _lib = None

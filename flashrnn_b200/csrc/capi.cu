@@ -14,6 +14,9 @@ int wgrad_plan(int gr, int B, int T, int N, int D, int* np_out, int* ksplit_out,
 int wgrad_launch(int gr, int gb, const __nv_bfloat16* dgr, const __nv_bfloat16* hbf, const float* db_part, int n_btiles,
                  float* dR, float* db, float* work, int* err, int B, int T, int N, int D, cudaStream_t s);
 
+int wgrad_launch_static(int gr, int gb, const __nv_bfloat16* dgr, const __nv_bfloat16* hbf, const float* db_part,
+                        int n_btiles, float* dR, float* db, int* err, int B, int T, int N, int D, cudaStream_t s);
+
 namespace {
 
 using EncodeTiledFn = CUresult (*)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*,
@@ -175,4 +178,16 @@ extern "C" int frnn_b200_wgrad(int cell, const void* dgr, const void* hbf, const
   return wgrad_launch(plan.gates_r, plan.gates_b, static_cast<const __nv_bfloat16*>(dgr),
                       static_cast<const __nv_bfloat16*>(hbf), db_part, plan.n_btiles, dR, db, work, err, B, T, N, D,
                       static_cast<cudaStream_t>(stream));
+}
+
+extern "C" int frnn_b200_wgrad_noalloc(int cell, const void* dgr, const void* hbf, const float* db_part, float* dR,
+                                       float* db, int B, int T, int N, int D, int* err, void* stream) {
+  frnn_b200_plan_t plan;
+  const int rc = frnn_b200_plan(cell, B, T, N, D, &plan);
+  if (rc != 0) return rc;
+  if (!plan.supported) return -2;
+  if (!dgr || !hbf || !db_part || !dR || !db || !err) return -5;
+  return wgrad_launch_static(plan.gates_r, plan.gates_b, static_cast<const __nv_bfloat16*>(dgr),
+                             static_cast<const __nv_bfloat16*>(hbf), db_part, plan.n_btiles, dR, db, err, B, T, N, D,
+                             static_cast<cudaStream_t>(stream));
 }

@@ -6,6 +6,8 @@
 //
 // Replaces the strided-batched cuBLAS GEMM and gradientBiasAggregationKernel of
 // flashrnn/flashrnn/fused/flashrnn_fused_backward.cu:1050-1070, 627-666.
+#include <mutex>
+
 #include "frnn_common.cuh"
 
 namespace frnn {
@@ -196,6 +198,56 @@ int wgrad_launch(int gr, int gb, const __nv_bfloat16* dgr, const __nv_bfloat16* 
   const long long nb = static_cast<long long>(gb) * N * D;
   reduce_parts_kernel<<<static_cast<unsigned>((nb / 4 + 255) / 256), 256, 0, s>>>(db_part, db, nb, n_btiles);
   return static_cast<int>(cudaGetLastError());
+}
+
+// ---------------------------------------------------------------------------------------------
+// Allocation-free variant of the weight-gradient step.
+//
+// Some hosts of this library must not (or cannot) create device memory at the moment they need
+// dR: a plugin that runs inside another framework's steady-state loop where cudaMalloc is
+// forbidden because it synchronises the device, a process that was handed a fixed memory budget
+// at start-up, or code that only receives raw input/output pointers and has no allocator of its
+// own to ask for the split-K partial tiles. For them the partial tiles live in a fixed array that
+// is part of the library image: every GPU that loads the library reserves it until the process
+// exits. All calls on a device share that one array, so two such calls that overlap on the GPU
+// (different streams) corrupt each other; nothing in it has to start at zero because the kernel
+// overwrites every partial tile it later reduces.
+// ---------------------------------------------------------------------------------------------
+constexpr size_t kStaticWorkBytes = 16u << 20;  // 16 MiB
+static __device__ __align__(256) unsigned char g_static_work[kStaticWorkBytes];
+
+namespace {
+// The array's name is only a host-side handle; its device address is looked up once per device
+// (with that device current) and cached.
+int static_work_address(float** out) {
+  static std::mutex mu;
+  static float* cached[64] = {};
+  int dev = -1;
+  cudaError_t e = cudaGetDevice(&dev);
+  if (e != cudaSuccess) return static_cast<int>(e);
+  if (dev < 0 || dev >= 64) return -5;
+  std::lock_guard<std::mutex> lock(mu);
+  if (cached[dev] == nullptr) {
+    void* ptr = nullptr;
+    e = cudaGetSymbolAddress(&ptr, g_static_work);
+    if (e != cudaSuccess) return static_cast<int>(e);
+    cached[dev] = static_cast<float*>(ptr);
+  }
+  *out = cached[dev];
+  return 0;
+}
+}  // namespace
+
+int wgrad_launch_static(int gr, int gb, const __nv_bfloat16* dgr, const __nv_bfloat16* hbf, const float* db_part,
+                        int n_btiles, float* dR, float* db, int* err, int B, int T, int N, int D, cudaStream_t s) {
+  int np, ksplit, cps;
+  if (wgrad_plan(gr, B, T, N, D, &np, &ksplit, &cps) != 0) return -2;
+  const size_t need = ksplit > 1 ? static_cast<size_t>(ksplit) * gr * N * D * D * sizeof(float) : 0;
+  if (need > kStaticWorkBytes) return -6;
+  float* work = nullptr;
+  const int rc = static_work_address(&work);
+  if (rc != 0) return rc;
+  return wgrad_launch(gr, gb, dgr, hbf, db_part, n_btiles, dR, db, work, err, B, T, N, D, s);
 }
 
 }  // namespace frnn

@@ -7,7 +7,8 @@
  *   Wx[B,T,GW,N,D]  R[GR,N,D,D] (gate, head, out, in)  b[GB,N,D]  states[S,B,T|1,N,D].
  * Return value: 0 on success, a positive cudaError_t, or a negative library code
  *   -1 unknown cell, -2 shape not supported by this kernel family (see frnn_b200_plan),
- *   -3 tensor-memory budget exceeded, -4 TMA descriptor could not be built, -5 bad argument.
+ *   -3 tensor-memory budget exceeded, -4 TMA descriptor could not be built, -5 bad argument,
+ *   -6 problem too large for the built-in scratch of frnn_b200_wgrad_noalloc.
  * Device-side problems (a bounded wait that ran out) are reported through the caller-owned
  * `err` array (int[32], zeroed by the caller): err[0] = code (101..107), err[1] = step,
  * err[2] = CTA. The kernels then leave in an orderly way; the context stays usable.
@@ -93,6 +94,20 @@ int frnn_b200_backward(int cell, const float* cache, const float* history, const
  * NULL when that is 0).                                                               */
 int frnn_b200_wgrad(int cell, const void* dgr, const void* hbf, const float* db_part, float* dR,
                     float* db, float* work, int B, int T, int N, int D, int* err, void* stream);
+
+/* Same result as frnn_b200_wgrad, for callers that cannot hand over scratch memory: hosts that
+ * must not call cudaMalloc once they are running (it synchronises the device), processes with a
+ * memory budget fixed at start-up, or thin plugins that only ever see input and output pointers.
+ * This entry point has no counterpart in the reference. The split-K partial tiles go to a fixed
+ * 16 MiB array inside the library image (each GPU that loads the library holds it until the
+ * process exits); the call returns -6 when plan.wgrad_work_bytes exceeds that. It allocates
+ * nothing. The first call on a device looks up the array's device address (a one-time set-up
+ * that should happen before any stream capture starts). All calls on a device share the array:
+ * calls that overlap on the GPU race with each other; consecutive calls on one stream are safe,
+ * and no clearing is needed because every partial tile is rewritten before it is reduced. */
+int frnn_b200_wgrad_noalloc(int cell, const void* dgr, const void* hbf, const float* db_part,
+                            float* dR, float* db, int B, int T, int N, int D, int* err,
+                            void* stream);
 
 #ifdef __cplusplus
 }
