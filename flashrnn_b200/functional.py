@@ -169,11 +169,16 @@ def _pad_width(t: torch.Tensor, pad: int, dims) -> torch.Tensor:
     return torch.nn.functional.pad(t, spec)
 
 
-def _run(wx, recurrent, bias, initial, cell: str):
+def _run(wx, recurrent, bias, initial, cell: str, zero_normalizer: Optional[bool] = None):
     if not wx.is_cuda:
         raise RuntimeError("flashrnn_b200 runs on CUDA devices only (sm_100a); there is no CPU path")
     D = wx.shape[-1]
-    zero_first = bool(cell == "slstm" and bool(torch.all(initial[2] == 0)))
+    if cell != "slstm":
+        zero_first = False
+    elif zero_normalizer is not None:
+        zero_first = bool(zero_normalizer)  # predicate of the whole logical call, given by a sharding caller
+    else:
+        zero_first = bool(torch.all(initial[2] == 0))
     pad = (-D) % 16
     if pad:
         # The kernels tile the head width in multiples of 16; zero rows/columns of R, zero
@@ -188,12 +193,15 @@ def _run(wx, recurrent, bias, initial, cell: str):
     return history, carry
 
 
-def flashrnn_torch(wx, recurrent, bias, initial, *, cell: str = "lstm", numerics: str = "fp32_state_bf16_mma"):
+def flashrnn_torch(wx, recurrent, bias, initial, *, cell: str = "lstm", numerics: str = "fp32_state_bf16_mma",
+                   zero_normalizer: Optional[bool] = None):
     """Return full history ``[S,B,T,H,D]`` and carry ``[S,B,1,H,D]`` (both fp32).
 
     Same argument checks as flashrnn/flashrnn2/torch_backend.py:36-58. The only numerical policy
     this backend implements is ``fp32_state_bf16_mma``; fp32 inputs follow the reference contract
     exactly, bf16 inputs (Wx, R, b, initial rounded by the caller) are accepted as an extension.
+    ``zero_normalizer`` (sLSTM only) overrides the "all initial n == 0" predicate of the first step; a
+    batch/head shard passes the predicate of the unsharded call (state_contract.py:81-97).
     """
     if cell not in SIZES:
         raise ValueError(f"unsupported cell: {cell}")
@@ -225,7 +233,7 @@ def flashrnn_torch(wx, recurrent, bias, initial, *, cell: str = "lstm", numerics
     if initial.shape != (S, batch, 1, heads, width):
         raise ValueError("initial state must have layout [S,B,1,N,D]")
     with torch.autocast("cuda", enabled=False):
-        return _run(wx, recurrent, bias, initial, cell)
+        return _run(wx, recurrent, bias, initial, cell, zero_normalizer)
 
 
 @dataclass
@@ -241,7 +249,7 @@ class FlashRNNConfig:
 
 
 def flashrnn(Wx, R, b, states=None, function: str = "lstm", config: Optional[FlashRNNConfig] = None,
-             backend: str = BACKEND, dtype: str = "bfloat16"):
+             backend: str = BACKEND, dtype: str = "bfloat16", zero_normalizer: Optional[bool] = None):
     """``Wx[B,T,G,N,D], R[G,N,D,D], b[G,N,D], states[S,B,1,N,D]`` -> ``(states[S,B,T,N,D], last[S,B,1,N,D])``.
 
     ``dtype`` is the operand dtype of the streamed input (``Wx`` is cast to it, R always goes to
@@ -264,4 +272,5 @@ def flashrnn(Wx, R, b, states=None, function: str = "lstm", config: Optional[Fla
     elif states.shape != (S, B, 1, N, D):
         raise ValueError("states must have layout [S,B,1,N,D]")
     with torch.autocast("cuda", enabled=False):
-        return _run(Wx.to(_DTYPES[dtype]), R, b.to(torch.float32), states.to(torch.float32), function)
+        return _run(Wx.to(_DTYPES[dtype]), R, b.to(torch.float32), states.to(torch.float32), function,
+                    zero_normalizer)

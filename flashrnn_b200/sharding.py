@@ -1,0 +1,59 @@
+"""Host-side helpers for running the recurrence on several GPUs (one process per GPU).
+
+Batch rows and heads are independent in the time loop (block-diagonal R, reference.py:83), so a
+rank simply runs the kernels on its slice. What has to be shared:
+
+* under batch sharding every rank holds all of R and b, so dR/db are partial sums that are
+  all-reduced once per backward (the only collective of the path);
+* the sLSTM first-step predicate "all of the initial n is zero" is a reduction over the
+  UNSHARDED initial state (state_contract.py:52-58, tests/flashrnn2/test_persistent_contract.py:67-133)
+  and must be computed before slicing and handed to every rank.
+"""
+
+from __future__ import annotations
+
+from typing import Optional, Tuple
+
+import torch
+
+
+def shard_range(total: int, world: int, rank: int) -> Tuple[int, int]:
+    """Contiguous near-equal split of ``range(total)``; the first ``total % world`` ranks get one more."""
+    if world < 1 or not 0 <= rank < world:
+        raise ValueError("need world >= 1 and 0 <= rank < world")
+    base, rem = divmod(total, world)
+    start = rank * base + min(rank, rem)
+    return start, start + base + (1 if rank < rem else 0)
+
+
+def choose_axis(B: int, N: int, world: int) -> str:
+    """'heads' when the heads divide evenly (no collective at all), else 'batch'."""
+    if world > 1 and N % world == 0:
+        return "heads"
+    return "batch"
+
+
+def slstm_zero_normalizer(initial: torch.Tensor) -> bool:
+    """The first-step predicate of one logical call, over the whole (unsharded) initial state."""
+    return bool(torch.all(initial[2] == 0))
+
+
+def shard_inputs(Wx, R, b, states, world: int, rank: int, axis: Optional[str] = None):
+    """Slice one logical call for ``rank``. Returns (Wx, R, b, states, axis)."""
+    B, _, _, N, _ = Wx.shape
+    axis = axis or choose_axis(B, N, world)
+    if axis == "heads":
+        lo, hi = shard_range(N, world, rank)
+        return Wx[:, :, :, lo:hi], R[:, lo:hi], b[:, lo:hi], states[:, :, :, lo:hi], axis
+    lo, hi = shard_range(B, world, rank)
+    return Wx[lo:hi], R, b, states[:, lo:hi], axis
+
+
+def allreduce_weight_grads(dR: torch.Tensor, db: torch.Tensor, axis: str, group=None) -> None:
+    """Sum dR/db over the ranks of a batch-sharded call (in place). A no-op for head sharding."""
+    import torch.distributed as dist
+
+    if axis != "batch" or not dist.is_initialized() or dist.get_world_size(group) == 1:
+        return
+    dist.all_reduce(dR, group=group)
+    dist.all_reduce(db, group=group)

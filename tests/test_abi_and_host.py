@@ -1,0 +1,64 @@
+"""CPU-side checks: the library loads and exports the declared ABI; host argument checks."""
+
+import re
+from pathlib import Path
+
+import pytest
+import torch
+
+from flashrnn_b200 import _lib, flashrnn, flashrnn_torch
+from flashrnn_b200.workloads import make_inputs
+
+ROOT = Path(__file__).resolve().parent.parent
+
+
+def test_library_exports_every_declared_symbol():
+    header = (ROOT / "include" / "flashrnn_b200.h").read_text()
+    declared = set(re.findall(r"^int\s+(frnn_b200_\w+)\s*\(", header, flags=re.M))
+    assert declared, "no declarations found"
+    assert declared == set(_lib.SIGNATURES), (declared, set(_lib.SIGNATURES))
+    lib = _lib.load()
+    for name in declared:
+        assert getattr(lib, name) is not None
+    assert lib.frnn_b200_version() >= 1000
+
+
+def test_plan_describes_the_headline_workload():
+    p = _lib.plan("lstm", 8, 1024, 3, 256)
+    assert (p.gates_r, p.gates_w, p.gates_b, p.states) == (4, 4, 4, 2)
+    assert (p.unit, p.cluster, p.batch_tile, p.n_btiles, p.grid_ctas, p.supported) == (32, 8, 8, 1, 24, 1)
+    assert p.cache_bytes == 8 * 1024 * 4 * 3 * 256 * 4 and p.hbf_bytes == 8 * 1025 * 3 * 256 * 2
+    g = _lib.plan("gru", 16, 10, 2, 48)
+    assert (g.gates_r, g.gates_b, g.unit, g.cluster, g.n_btiles) == (3, 4, 16, 3, 1)
+    assert not _lib.plan("lstm", 8, 8, 1, 768).supported      # needs the 2-D split kernel
+    assert not _lib.plan("lstm", 8, 8, 1, 40).supported       # the ABI wants D % 16 == 0 (Python pads)
+
+
+def test_argument_checks_mirror_the_reference():
+    wx, R, b, init = make_inputs("lstm", 2, 3, 2, 16, 0)
+    with pytest.raises(ValueError, match="unsupported cell"):
+        flashrnn_torch(wx, R, b, init, cell="rnn")
+    with pytest.raises(ValueError, match="numerical policy|fp32_state_bf16_mma"):
+        flashrnn_torch(wx, R, b, init, numerics="mathematical")
+    with pytest.raises(ValueError, match="ranks"):
+        flashrnn_torch(wx[0], R, b, init)
+    with pytest.raises(ValueError, match="same dtype"):
+        flashrnn_torch(wx, R.double(), b, init)
+    with pytest.raises(ValueError, match="gate count"):
+        flashrnn_torch(wx[:, :, :3], R, b, init)
+    with pytest.raises(ValueError, match=r"\[G,N,D,P\]"):
+        flashrnn_torch(wx, R[:, :1], b, init)
+    with pytest.raises(ValueError, match="bias"):
+        flashrnn_torch(wx, R, b[:3], init)
+    with pytest.raises(ValueError, match=r"\[S,B,1,N,D\]"):
+        flashrnn_torch(wx, R, b, init[:1])
+    with pytest.raises(ValueError, match="Unknown backend"):
+        flashrnn(wx, R, b, backend="cuda_fused")
+    with pytest.raises(ValueError, match="Unknown function"):
+        flashrnn(wx, R, b, function="mlstm")
+
+
+def test_there_is_no_cpu_path():
+    wx, R, b, init = make_inputs("lstm", 2, 3, 2, 16, 0)
+    with pytest.raises(RuntimeError, match="CUDA devices only"):
+        flashrnn_torch(wx, R, b, init)
