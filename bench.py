@@ -334,6 +334,7 @@ def kernel_breakdown(_lib, dev, d_wx, d_R, d_b, d_init, flush, reps):
         v = err.tolist()
         out[name + "_phase_cycles_per_step"] = {**{k: round(v[8 + i] / T, 1) for i, k in enumerate(names)},
                                                 "x5": round(v[13] / T, 1), "x6": round(v[14] / T, 1),
+                                                "commit_to_epilogue": round(v[15] / T, 1), "push_to_mma_wake": round(v[18] / T, 1),
                                                 "mma_warp_wait": round(v[16] / T, 1), "mma_warp_issue": round(v[17] / T, 1)}
     err.zero_()
     return out

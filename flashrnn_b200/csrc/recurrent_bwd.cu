@@ -77,7 +77,8 @@ frnn_bwd_kernel(const BwdParams p, const __grid_constant__ CUtensorMap cache_map
   while (tmem_cols < static_cast<uint32_t>(a_col0 + MTB * (ROWS / 2))) tmem_cols <<= 1;
 
   // shared memory carve-up
-  const int part_bytes = C * BV * U * 4;  // one parity buffer
+  constexpr int BP = BV + 4;  // padded batch stride of the partial rows (keeps 16-byte stores aligned, spreads banks)
+  const int part_bytes = C * U * BP * 4;  // one parity buffer: [source CTA][unit][batch]
   uint8_t* const dgbuf = smem;
   float* const part = reinterpret_cast<float*>(smem + Cfg::DGBUF_BYTES);
   float* const dbuf = reinterpret_cast<float*>(smem + Cfg::DGBUF_BYTES + 2 * part_bytes);
@@ -153,7 +154,8 @@ frnn_bwd_kernel(const BwdParams p, const __grid_constant__ CUtensorMap cache_map
 #pragma unroll
     for (int q = 0; q < S; ++q) ld_f32_vec<IPT>(p.d_carry + q * BND + item_bn, dcar[q]);
   }
-  const uint32_t part_tx = static_cast<uint32_t>(C) * bv * U * 4u;
+  const int bvq = (bv + 3) & ~3;  // batch columns actually sent (whole 16-byte packets)
+  const uint32_t part_tx = static_cast<uint32_t>(C) * bvq * U * 4u;
   if (tid == 0) {
     mbar_arrive_expect_tx(smem_u32(&s_part_bar[1]), part_tx);                 // iteration 1 (or final if T == 1)
     if (T >= 2) mbar_arrive_expect_tx(smem_u32(&s_part_bar[0]), part_tx);     // iteration 2
@@ -177,7 +179,7 @@ frnn_bwd_kernel(const BwdParams p, const __grid_constant__ CUtensorMap cache_map
       long long pw = 0, pi = 0;
       for (int it = 0; it < T; ++it) {
         const long long m0 = prof ? clock64() : 0;
-        if (!mbar_wait_bounded<false>(smem_u32(&s_dg_bar), it & 1, limit, abort_flag)) {
+        if (!mbar_wait_bounded<false, true>(smem_u32(&s_dg_bar), it & 1, limit, abort_flag)) {
           report(p.err, kErrWaitDg, it);
           break;
         }
@@ -265,18 +267,16 @@ frnn_bwd_kernel(const BwdParams p, const __grid_constant__ CUtensorMap cache_map
       if (it >= 1) {
         // partial dh for this step from every CTA of the cluster
         const int pb = it & 1;
-        if (!mbar_wait_bounded<true>(smem_u32(&s_part_bar[pb]), ((it - 1) >> 1) & 1, limit, abort_flag)) {
+        if (!mbar_wait_bounded<true, true>(smem_u32(&s_part_bar[pb]), ((it - 1) >> 1) & 1, limit, abort_flag)) {
           report(p.err, kErrWaitPart, it);
           break;
         }
         if (tid == 0 && it + 2 <= T) mbar_arrive_expect_tx(smem_u32(&s_part_bar[pb]), part_tx);
         if (active) {
-          const float* pbuf = part + static_cast<size_t>(pb) * (part_bytes / 4) + ib * U + ul;
+          const float* pbuf = part + static_cast<size_t>(pb) * (part_bytes / 4) + ul * BP + ib;
           for (int src = 0; src < C; ++src) {
-            float v[IPT];
-            ld_f32_vec<IPT>(pbuf + src * BV * U, v);
 #pragma unroll
-            for (int j = 0; j < IPT; ++j) ds[0][j] += v[j];
+            for (int j = 0; j < IPT; ++j) ds[0][j] += pbuf[src * U * BP + j * BP];
           }
         }
       }
@@ -289,8 +289,9 @@ frnn_bwd_kernel(const BwdParams p, const __grid_constant__ CUtensorMap cache_map
         break;
       }
       uint32_t dgp[CT::GR][IPT / 2];
+      float dgw[CT::GW][IPT];
       if (active) {
-        float dgr[CT::GR][IPT], dgw[CT::GW][IPT];
+        float dgr[CT::GR][IPT];
         const bool take_i = CELL == kSLSTM && t == 0 && p.slstm_zero_first != 0;
 #pragma unroll
         for (int j = 0; j < IPT; ++j) {
@@ -321,6 +322,12 @@ frnn_bwd_kernel(const BwdParams p, const __grid_constant__ CUtensorMap cache_map
           else if constexpr (IPT == 4) *reinterpret_cast<uint2*>(dst) = make_uint2(dgp[g][0], dgp[g][1]);
           else *reinterpret_cast<uint4*>(dst) = make_uint4(dgp[g][0], dgp[g][1], dgp[g][2], dgp[g][3]);
         }
+      }
+      fence_proxy_async_smem();
+      tc_fence_before_sync();
+      mbar_arrive(smem_u32(&s_dg_bar));
+      const long long c3 = prof ? clock64() : 0;
+      if (active) {
         // streams to global memory
         const size_t row = (static_cast<size_t>(b0 + ib) * T + t);
         __nv_bfloat16* dgr_g = p.dgr + (row * CT::GR * N + n) * D + d0;
@@ -341,10 +348,6 @@ frnn_bwd_kernel(const BwdParams p, const __grid_constant__ CUtensorMap cache_map
           for (int g = 0; g < CT::GW; ++g) st_f32_vec<IPT>(dwx_g + g * ND, dgw[g]);
         }
       }
-      fence_proxy_async();
-      tc_fence_before_sync();
-      mbar_arrive(smem_u32(&s_dg_bar));
-      const long long c3 = prof ? clock64() : 0;
       if (!mbar_wait_bounded<false>(smem_u32(&s_mma_bar), it & 1, limit, abort_flag)) {
         report(p.err, kErrWaitMma, it);
         break;
@@ -353,7 +356,7 @@ frnn_bwd_kernel(const BwdParams p, const __grid_constant__ CUtensorMap cache_map
       const long long c4 = prof ? clock64() : 0;
       // scatter partial dh_{t-1} rows to the CTAs that own those units
       const int nb = (it + 1) & 1;
-      const uint32_t part_base = smem_u32(part) + static_cast<uint32_t>(nb) * part_bytes + static_cast<uint32_t>(rank) * BV * U * 4;
+      const uint32_t part_base = smem_u32(part) + static_cast<uint32_t>(nb) * part_bytes + static_cast<uint32_t>(rank) * U * BP * 4;
       const uint32_t bar_local = smem_u32(&s_part_bar[nb]);
       for (int j = 0; j < MTB; ++j) {
         uint32_t r[BV / 8][8];
@@ -363,13 +366,13 @@ frnn_bwd_kernel(const BwdParams p, const __grid_constant__ CUtensorMap cache_map
         const int pp = j * 128 + tid;
         if (pp < D) {
           const int dest = pp / U, pl = pp % U;
-          const uint32_t ra = map_to_cta(part_base + pl * 4, dest);
+          const uint32_t ra = map_to_cta(part_base + pl * BP * 4, dest);
           const uint32_t rb = map_to_cta(bar_local, dest);
 #pragma unroll
           for (int c = 0; c < BV / 8; ++c)
 #pragma unroll
-            for (int q = 0; q < 8; ++q)
-              if (8 * c + q < bv) st_async_b32(ra + (8 * c + q) * U * 4, r[c][q], rb);
+            for (int q = 0; q < 8; q += 4)
+              if (8 * c + q < bvq) st_async_v4_b32(ra + (8 * c + q) * 4, r[c][q], r[c][q + 1], r[c][q + 2], r[c][q + 3], rb);
         }
       }
       tc_fence_before_sync();
@@ -409,7 +412,7 @@ int launch_bwd(const BwdParams& p, const float* cache, const float* history, con
                const float* d_history, cudaStream_t stream) {
   using Cfg = BwdCfg<CELL, BV, U, WX_BF16>;
   using CT = typename Cfg::CT;
-  const int part_bytes = p.C * BV * U * 4;
+  const int part_bytes = p.C * U * (BV + 4) * 4;
   const int smem = ((Cfg::DGBUF_BYTES + 2 * part_bytes + Cfg::DBUF_BYTES + 127) & ~127) + kStages * Cfg::STAGE_BYTES;
   const int MTB = (p.D + 127) / 128;
   if (((MTB * Cfg::BT + 31) / 32 * 32) + MTB * (Cfg::ROWS / 2) > 512) return -3;

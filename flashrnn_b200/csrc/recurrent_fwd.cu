@@ -57,10 +57,10 @@ frnn_fwd_kernel(const FwdParams p, const __grid_constant__ CUtensorMap wx_map) {
   extern __shared__ __align__(1024) uint8_t smem[];
   __shared__ __align__(8) uint64_t s_hbar[2];
   __shared__ __align__(8) uint64_t s_mma_bar;
-  __shared__ __align__(8) uint64_t s_epi_bar;
   __shared__ __align__(8) uint64_t s_wx_full[kWxStages];
   __shared__ __align__(8) uint64_t s_wx_empty[kWxStages];
   __shared__ uint32_t s_tmem_base;
+  __shared__ long long s_prof_clk[2];  // [0] last MMA commit, [1] last h push (phase timers only)
 
   const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
   const int D = p.D, N = p.N, T = p.T, B = p.B, C = p.C;
@@ -85,7 +85,6 @@ frnn_fwd_kernel(const FwdParams p, const __grid_constant__ CUtensorMap wx_map) {
     mbar_init(smem_u32(&s_hbar[0]), 1);
     mbar_init(smem_u32(&s_hbar[1]), 1);
     mbar_init(smem_u32(&s_mma_bar), 1);
-    mbar_init(smem_u32(&s_epi_bar), kEpiThreads);
     for (int s = 0; s < kWxStages; ++s) {
       mbar_init(smem_u32(&s_wx_full[s]), 1);
       mbar_init(smem_u32(&s_wx_empty[s]), kEpiThreads);
@@ -170,20 +169,22 @@ frnn_fwd_kernel(const FwdParams p, const __grid_constant__ CUtensorMap wx_map) {
   if (warp == 4) {
     if (lane == 0) {
       const uint32_t idesc = umma_idesc_bf16(128, BT, false, false);
-      long long pw = 0, pi = 0;
+      long long pw = 0, pi = 0, px = 0, pf = 0;
       for (int t = 0; t < T; ++t) {
         const int pb = t & 1;
         const long long m0 = prof ? clock64() : 0;
         if (t >= 1) {
-          if (!mbar_wait_bounded<true>(smem_u32(&s_hbar[pb]), ((t - 1) >> 1) & 1, limit, abort_flag)) {
+          if (!mbar_wait_bounded<true, true>(smem_u32(&s_hbar[pb]), ((t - 1) >> 1) & 1, limit, abort_flag)) {
             report(p.err, kErrWaitH, t);
             break;
           }
           if (t + 2 <= T - 1) mbar_arrive_expect_tx(smem_u32(&s_hbar[pb]), h_tx_bytes);
         }
-        fence_proxy_async();
+        const long long mw = prof ? clock64() : 0;
+        fence_proxy_async_smem();
         tc_fence_after_sync();
         const long long m1 = prof ? clock64() : 0;
+        if (prof) pf += m1 - mw;
         const uint32_t hb = smem_u32(hbuf + pb * hbuf_bytes);
         for (int j = 0; j < MT; ++j) {
           for (int kk = 0; kk < D / 16; ++kk) {
@@ -193,9 +194,14 @@ frnn_fwd_kernel(const FwdParams p, const __grid_constant__ CUtensorMap wx_map) {
           }
         }
         umma_commit(smem_u32(&s_mma_bar));
-        if (prof) { pw += m1 - m0; pi += clock64() - m1; }
+        if (prof) {
+          const long long m2 = clock64();
+          pw += m1 - m0; pi += m2 - m1;
+          if (t >= 1) px += m1 - *reinterpret_cast<volatile long long*>(&s_prof_clk[1]);
+          *reinterpret_cast<volatile long long*>(&s_prof_clk[0]) = m2;
+        }
       }
-      if (prof) { p.err[16] = static_cast<int>(pw); p.err[17] = static_cast<int>(pi); }
+      if (prof) { p.err[16] = static_cast<int>(pw); p.err[17] = static_cast<int>(pi); p.err[18] = static_cast<int>(px); p.err[19] = static_cast<int>(pf); }
     }
   } else if (warp == 5) {
     if (lane == 0) {
@@ -217,21 +223,32 @@ frnn_fwd_kernel(const FwdParams p, const __grid_constant__ CUtensorMap wx_map) {
     float* cache = p.cache == nullptr ? nullptr : p.cache + ((static_cast<size_t>(b0 + ib) * T * CT::GC) * N + n) * D + d0;
     __nv_bfloat16* hbf = p.hbf == nullptr ? nullptr : p.hbf + ((static_cast<size_t>(b0 + ib) * (T + 1) + 1) * N + n) * D + d0;
     const uint32_t h_off = kmajor_offset(BT, ib, d0);
-    // distance from this CTA's shared window to every peer's (constant for the whole kernel)
-    uint32_t peer_delta[16];
+    // Peers this lane pushes to (it shares the cluster with the other lanes of its packet group)
+    // and the distance from this CTA's shared window to theirs, constant for the whole kernel.
+    constexpr int LPP = 8 / IPT;  // lanes that together hold one 16-byte packet of h
+    constexpr int NPEER = 16 / LPP;
+    uint32_t peer_delta[NPEER];
     {
       const uint32_t base = smem_u32(smem);
 #pragma unroll
-      for (int d = 0; d < 16; ++d) peer_delta[d] = d < C ? map_to_cta(base, d) - base : 0u;
+      for (int i = 0; i < NPEER; ++i) {
+        const int d = i * LPP + (lane & (LPP - 1));
+        peer_delta[i] = d < C ? map_to_cta(base, d) - base : 0u;
+      }
     }
     const size_t ND = static_cast<size_t>(N) * D;
     long long pc[7] = {0, 0, 0, 0, 0, 0, 0};
+    long long pd = 0;
+    // After a wait has failed (`dead`), the warp keeps walking through the loop so that the
+    // named barrier below always sees all 128 threads; waits return at once because the abort
+    // flag is set, and nothing that is computed from then on matters.
+    bool dead = false;
     for (int t = 0; t < T; ++t) {
       const int s = t % kWxStages;
       const long long c0 = prof ? clock64() : 0;
-      if (!mbar_wait_bounded<false>(smem_u32(&s_wx_full[s]), (t / kWxStages) & 1, limit, abort_flag)) {
+      if (!dead && !mbar_wait_bounded<false>(smem_u32(&s_wx_full[s]), (t / kWxStages) & 1, limit, abort_flag)) {
         report(p.err, kErrWaitWx, t);
-        break;
+        dead = true;
       }
       const long long c1 = prof ? clock64() : 0;
       float wx[CT::GW][IPT];
@@ -245,12 +262,13 @@ frnn_fwd_kernel(const FwdParams p, const __grid_constant__ CUtensorMap wx_map) {
         }
       }
       mbar_arrive(smem_u32(&s_wx_empty[s]));
-      if (!mbar_wait_bounded<false>(smem_u32(&s_mma_bar), t & 1, limit, abort_flag)) {
+      if (!dead && !mbar_wait_bounded<false>(smem_u32(&s_mma_bar), t & 1, limit, abort_flag)) {
         report(p.err, kErrWaitMma, t);
-        break;
+        dead = true;
       }
       tc_fence_after_sync();
       const long long c2 = prof ? clock64() : 0;
+      if (prof) pd += c2 - *reinterpret_cast<volatile long long*>(&s_prof_clk[0]);
       // phase 1: accumulator rows (lane = gate row) -> gate buffer [batch][row]
       {
         uint32_t r[MT][BV / 8][8];
@@ -268,19 +286,18 @@ frnn_fwd_kernel(const FwdParams p, const __grid_constant__ CUtensorMap wx_map) {
       }
       tc_fence_before_sync();
       const long long c3 = prof ? clock64() : 0;
-      mbar_arrive(smem_u32(&s_epi_bar));
-      if (!mbar_wait_bounded<false>(smem_u32(&s_epi_bar), t & 1, limit, abort_flag)) {
-        report(p.err, kErrWaitEpi, t);
-        break;
-      }
+      asm volatile("bar.sync 1, 128;" ::: "memory");  // the four epilogue warps only
       const long long c4 = prof ? clock64() : 0;
       // phase 2: the cell, for IPT consecutive units of one batch row
       long long c5 = 0, c6 = 0;
+      float cv[CT::GC][IPT];
+      uint32_t hp[IPT / 2];
+#pragma unroll
+      for (int j = 0; j < IPT / 2; ++j) hp[j] = 0u;
       if (active) {
         float ry[CT::GR][IPT];
 #pragma unroll
         for (int g = 0; g < CT::GR; ++g) ld_f32_vec<IPT>(gbuf + ib * Cfg::GROW + g * U + ul, ry[g]);
-        float cv[CT::GC][IPT];
         const bool take_i = CELL == kSLSTM && t == 0 && p.slstm_zero_first != 0;
 #pragma unroll
         for (int j = 0; j < IPT; ++j) {
@@ -299,24 +316,42 @@ frnn_fwd_kernel(const FwdParams p, const __grid_constant__ CUtensorMap wx_map) {
 #pragma unroll
           for (int q = 0; q < CT::GC; ++q) cv[q][j] = cj[q];
         }
-        uint32_t hp[IPT / 2];
 #pragma unroll
         for (int j = 0; j < IPT; j += 2) hp[j / 2] = pack_bf16x2(st[0][j], st[0][j + 1]);
-        if (prof) c5 = clock64();
-        if (t + 1 < T) {
-          const uint32_t dst = smem_u32(hbuf + ((t + 1) & 1) * hbuf_bytes) + h_off;
-          const uint32_t bar = smem_u32(&s_hbar[(t + 1) & 1]);
+      }
+      if (prof) c5 = clock64();
+      // push round_bf16(h_t): LPP neighbouring lanes first gather one 16-byte packet (8 units of one
+      // batch row), then share the peers among themselves, so a thread issues C / LPP stores.
+      {
+        uint32_t pk[4];
+        if constexpr (LPP == 4) {
+          const uint32_t a = hp[0];
+          const uint32_t b1 = __shfl_xor_sync(0xffffffffu, a, 1);
+          const uint32_t lo = (lane & 1) ? b1 : a, hi = (lane & 1) ? a : b1;
+          const uint32_t lo2 = __shfl_xor_sync(0xffffffffu, lo, 2), hi2 = __shfl_xor_sync(0xffffffffu, hi, 2);
+          pk[0] = (lane & 2) ? lo2 : lo; pk[1] = (lane & 2) ? hi2 : hi;
+          pk[2] = (lane & 2) ? lo : lo2; pk[3] = (lane & 2) ? hi : hi2;
+        } else if constexpr (LPP == 2) {
+          const uint32_t o0 = __shfl_xor_sync(0xffffffffu, hp[0], 1), o1 = __shfl_xor_sync(0xffffffffu, hp[IPT / 2 - 1], 1);
+          pk[0] = (lane & 1) ? o0 : hp[0]; pk[1] = (lane & 1) ? o1 : hp[IPT / 2 - 1];
+          pk[2] = (lane & 1) ? hp[0] : o0; pk[3] = (lane & 1) ? hp[IPT / 2 - 1] : o1;
+        } else {
 #pragma unroll
-          for (int d = 0; d < 16; ++d) {
-            if (d < C) {
-              const uint32_t ra = dst + peer_delta[d], rb = bar + peer_delta[d];
-              if constexpr (IPT == 2) st_async_b32(ra, hp[0], rb);
-              else if constexpr (IPT == 4) st_async_v2_b32(ra, hp[0], hp[1], rb);
-              else st_async_v4_b32(ra, hp[0], hp[1], hp[2], hp[3], rb);
-            }
+          for (int j = 0; j < 4; ++j) pk[j] = hp[j % (IPT / 2)];
+        }
+        if (active && t + 1 < T) {
+          const uint32_t dst = smem_u32(hbuf + ((t + 1) & 1) * hbuf_bytes) + (h_off & ~15u);
+          const uint32_t bar = smem_u32(&s_hbar[(t + 1) & 1]);
+          const int first = lane & (LPP - 1);
+#pragma unroll
+          for (int i = 0; i < NPEER; ++i) {
+            if (i * LPP + first < C)
+              st_async_v4_b32(dst + peer_delta[i], pk[0], pk[1], pk[2], pk[3], bar + peer_delta[i]);
           }
         }
-        if (prof) c6 = clock64();
+      }
+      if (prof) { c6 = clock64(); *reinterpret_cast<volatile long long*>(&s_prof_clk[1]) = c6; }
+      if (active) {
 #pragma unroll
         for (int q = 0; q < CT::S; ++q) st_f32_vec<IPT>(hist + q * sBTND + t * ND, st[q]);
         if (cache != nullptr && CELL != kElman) {
@@ -336,6 +371,7 @@ frnn_fwd_kernel(const FwdParams p, const __grid_constant__ CUtensorMap wx_map) {
     if (prof) {
 #pragma unroll
       for (int q = 0; q < 7; ++q) p.err[8 + q] = static_cast<int>(pc[q]);
+      p.err[15] = static_cast<int>(pd);
     }
     if (active) {
 #pragma unroll

@@ -89,18 +89,50 @@ __device__ __forceinline__ bool mbar_try_wait_cluster(uint32_t bar, uint32_t par
   return ok != 0;
 }
 
+// Variants without the parking hint: the waiter polls, which costs issue slots but reacts fastest.
+__device__ __forceinline__ bool mbar_try_wait_spin(uint32_t bar, uint32_t parity) {
+  uint32_t ok;
+  asm volatile(
+      "{\n"
+      " .reg .pred p;\n"
+      " mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n"
+      " selp.u32 %0, 1, 0, p;\n"
+      "}\n"
+      : "=r"(ok)
+      : "r"(bar), "r"(parity)
+      : "memory");
+  return ok != 0;
+}
+__device__ __forceinline__ bool mbar_try_wait_cluster_spin(uint32_t bar, uint32_t parity) {
+  uint32_t ok;
+  asm volatile(
+      "{\n"
+      " .reg .pred p;\n"
+      " mbarrier.try_wait.parity.acquire.cluster.shared::cta.b64 p, [%1], %2;\n"
+      " selp.u32 %0, 1, 0, p;\n"
+      "}\n"
+      : "=r"(ok)
+      : "r"(bar), "r"(parity)
+      : "memory");
+  return ok != 0;
+}
+
 // Bounded wait. `abort_flag` (global memory, may be null) is polled so that once any CTA of the
 // grid has given up, every other waiter leaves quickly too. Returns false on timeout / abort.
-template <bool kClusterScope>
+template <bool kClusterScope, bool kSpin = false>
 __device__ __forceinline__ bool mbar_wait_bounded(uint32_t bar, uint32_t parity, uint64_t limit_ns,
                                                   const volatile int* abort_flag) {
+  auto poll = [&]() -> bool {
+    if constexpr (kSpin) return kClusterScope ? mbar_try_wait_cluster_spin(bar, parity) : mbar_try_wait_spin(bar, parity);
+    else return kClusterScope ? mbar_try_wait_cluster(bar, parity) : mbar_try_wait(bar, parity);
+  };
   for (int fast = 0; fast < 64; ++fast) {
-    if (kClusterScope ? mbar_try_wait_cluster(bar, parity) : mbar_try_wait(bar, parity)) return true;
+    if (poll()) return true;
   }
   const uint64_t t0 = global_timer_ns();
   uint32_t spins = 0;
   while (true) {
-    if (kClusterScope ? mbar_try_wait_cluster(bar, parity) : mbar_try_wait(bar, parity)) return true;
+    if (poll()) return true;
     if ((++spins & 255u) == 0u) {
       if (abort_flag != nullptr && *abort_flag != 0) return false;
       if (global_timer_ns() - t0 > limit_ns) return false;

@@ -93,7 +93,7 @@ __global__ void __launch_bounds__(kThreads, 1) wgrad_kernel(const WgradParams p)
       }
       *reinterpret_cast<uint4*>(sB + pg * 1024 + (k >> 3) * 128 + (k & 7) * 16) = val;
     }
-    fence_proxy_async();
+    fence_proxy_async_smem();
     __syncthreads();
     if (tid == 0) {
       tc_fence_after_sync();
