@@ -39,6 +39,9 @@ FLOP_FWD = 2 * GR * D * D * N * B * T          # R*h contraction of the forward 
 FLOP_BWD = 2 * GR * D * D * N * B * T          # R^T*dg contraction of the backward kernel
 FLOP_WGRAD = 2 * GR * D * D * N * B * T        # dR contraction
 CPU_SAMPLE_T = 128                              # bounded CPU sample: same B, N, D, first 128 steps
+# dram__bytes_read.sum + dram__bytes_write.sum per launch on this workload, from the ncu capture summarised in
+# profiles/recurrence_kernels_cfg2_lstm_bf16_B8_T1024_N3_D256.md
+NCU_TRAFFIC_BYTES = {"fwd": 52.1e6 + 107.9e6, "bwd": 203.1e6 + 75.7e6, "wgrad": 63.0e6 + 2.2e6}
 
 
 def _peaks():
@@ -258,7 +261,7 @@ def main():
             "kernels_ms": breakdown,
             "roofline": {"bound": "tensor", "kernel": f"frnn_{dom}_kernel", "achieved": achieved, "peak": bf16_peak,
                          "unit": "TFLOP/s", "frac": achieved / bf16_peak, "peak_source": peak_kind,
-                         "traffic": None,
+                         "traffic": NCU_TRAFFIC_BYTES[dom],
                          "note": "step-latency bound: T dependent steps; see DESIGN.md for the per-step budget"},
             "clocks": clocks.summary(),
         }
