@@ -52,7 +52,7 @@ bool cell_counts(int cell, CellCounts* c) {
 }  // namespace
 
 int make_tensor_map(CUtensorMap* map, const void* base, int elem_bytes, int rank, const uint64_t* dims,
-                    const uint32_t* box) {
+                    const uint32_t* box, bool swizzle128) {
   EncodeTiledFn fn = encode_tiled_fn();
   if (fn == nullptr) return -4;
   cuuint64_t gdims[5];
@@ -68,7 +68,8 @@ int make_tensor_map(CUtensorMap* map, const void* base, int elem_bytes, int rank
   }
   const CUtensorMapDataType dt = elem_bytes == 4 ? CU_TENSOR_MAP_DATA_TYPE_FLOAT32 : CU_TENSOR_MAP_DATA_TYPE_BFLOAT16;
   const CUresult r = fn(map, dt, static_cast<cuuint32_t>(rank), const_cast<void*>(base), gdims, gstrides, gbox, estr,
-                        CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_NONE, CU_TENSOR_MAP_L2_PROMOTION_L2_128B,
+                        CU_TENSOR_MAP_INTERLEAVE_NONE, swizzle128 ? CU_TENSOR_MAP_SWIZZLE_128B : CU_TENSOR_MAP_SWIZZLE_NONE,
+                        CU_TENSOR_MAP_L2_PROMOTION_L2_128B,
                         CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
   return r == CUDA_SUCCESS ? 0 : -4;
 }

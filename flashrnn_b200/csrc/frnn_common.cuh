@@ -122,6 +122,6 @@ __host__ __device__ __forceinline__ uint32_t kmajor_offset(int rows, int row, in
 
 // Host: build a tiled tensor map (no swizzle, no interleave). dims/box innermost first.
 int make_tensor_map(CUtensorMap* map, const void* base, int elem_bytes, int rank, const uint64_t* dims,
-                    const uint32_t* box);
+                    const uint32_t* box, bool swizzle128 = false);
 
 }  // namespace frnn

@@ -272,6 +272,20 @@ __device__ __forceinline__ uint64_t umma_smem_desc(uint32_t smem_addr, uint32_t 
   return d;         // layout type 0 = no swizzle, base offset 0
 }
 
+// Descriptor for MN-major operand tiles written by TMA with the 128-byte swizzle: rows of 64
+// elements (128 B) along M/N, 8 such rows (one per k) form a 1024-byte swizzle atom;
+// `mn_group_stride` = bytes between 64-element groups along M/N, k-groups are 1024 B apart.
+// The tile base must be 1024-byte aligned.
+__device__ __forceinline__ uint64_t umma_smem_desc_mn_sw128(uint32_t smem_addr, uint32_t mn_group_stride) {
+  uint64_t d = 0;
+  d |= static_cast<uint64_t>((smem_addr & 0x3FFFFu) >> 4);
+  d |= static_cast<uint64_t>((mn_group_stride >> 4) & 0x3FFFu) << 16;  // leading byte offset
+  d |= static_cast<uint64_t>((1024u >> 4) & 0x3FFFu) << 32;            // stride byte offset
+  d |= 1ull << 46;
+  d |= 2ull << 61;  // SWIZZLE_128B
+  return d;
+}
+
 // Instruction descriptor: bf16 x bf16 -> fp32, dense. `a_mn` / `b_mn` select MN-major operands.
 __host__ __device__ constexpr uint32_t umma_idesc_bf16(int m, int n, bool a_mn, bool b_mn) {
   return (1u << 4)      // accumulator format F32

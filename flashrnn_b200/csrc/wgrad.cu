@@ -138,6 +138,139 @@ __global__ void __launch_bounds__(kThreads, 1) wgrad_kernel(const WgradParams p)
   if (warp == 0) tmem_dealloc(tbase, tmem_cols);
 }
 
+// ---------------------------------------------------------------------------------------------
+// Pipelined variant for D % 64 == 0: operands arrive by TMA (128-byte swizzle, 64 x 64 boxes)
+// through a 4-stage ring; warp 0 = TMA producer, warp 1 = UMMA issuer, warps 2-5 = epilogue.
+// A stage holds 64 (b,t) rows: A = dg^T [128 m x 64 k] as two boxes, B = h~ [NP p x 64 k] as
+// NP/64 boxes. A chunk never straddles a batch row; rows past T read as zeros on the dg side.
+// ---------------------------------------------------------------------------------------------
+constexpr int kTmaThreads = 192;
+constexpr int kTmaStages = 4;
+
+__global__ void __launch_bounds__(kTmaThreads, 1)
+wgrad_tma_kernel(const WgradParams p, const __grid_constant__ CUtensorMap dgr_map,
+                 const __grid_constant__ CUtensorMap hbf_map) {
+  extern __shared__ uint8_t smem_raw[];
+  __shared__ __align__(8) uint64_t s_full[kTmaStages];
+  __shared__ __align__(8) uint64_t s_empty[kTmaStages];
+  __shared__ __align__(8) uint64_t s_acc;
+  __shared__ uint32_t s_tmem_base;
+  const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
+  const int D = p.D, T = p.T, GR = p.GR, NP = p.NP;
+  const int npt = D / NP;
+  const int mtile = blockIdx.x / npt, ptile = blockIdx.x % npt;
+  const int n = blockIdx.y, split = blockIdx.z;
+  const int m0 = mtile * 128, p0 = ptile * NP;
+  const int M = GR * D;
+  const int cpb = (T + kKC - 1) / kKC;  // chunks per batch row
+  const int total_chunks = p.B * cpb;
+  const int c_begin = split * p.chunks_per_split;
+  const int c_end = min(c_begin + p.chunks_per_split, total_chunks);
+  const int n_chunks = max(c_end - c_begin, 0);
+  const uint32_t stage_bytes = 16384u + static_cast<uint32_t>(NP) * 128u;
+  const uint32_t base = (smem_u32(smem_raw) + 1023u) & ~1023u;
+  uint32_t tmem_cols = 32;
+  while (tmem_cols < static_cast<uint32_t>(NP)) tmem_cols <<= 1;
+  const volatile int* abort_flag = p.err;
+  constexpr uint64_t kLimit = 2000000000ull;
+
+  if (tid == 0) {
+    for (int s = 0; s < kTmaStages; ++s) {
+      mbar_init(smem_u32(&s_full[s]), 1);
+      mbar_init(smem_u32(&s_empty[s]), 1);
+    }
+    mbar_init(smem_u32(&s_acc), 1);
+    fence_mbar_init();
+  }
+  if (warp == 1) {
+    tmem_alloc(smem_u32(&s_tmem_base), tmem_cols);
+    tmem_relinquish_alloc();
+  }
+  tc_fence_before_sync();
+  __syncthreads();
+  tc_fence_after_sync();
+  const uint32_t tbase = s_tmem_base;
+  bool ok = true;
+
+  if (warp == 0) {
+    if (lane == 0) {
+      tma_prefetch_desc(&dgr_map);
+      tma_prefetch_desc(&hbf_map);
+      for (int i = 0; i < n_chunks; ++i) {
+        const int s = i % kTmaStages, c = c_begin + i;
+        if (i >= kTmaStages &&
+            !mbar_wait_bounded<false>(smem_u32(&s_empty[s]), ((i / kTmaStages) - 1) & 1, kLimit, abort_flag)) {
+          atomicCAS(p.err, 0, kErrWaitEmpty);
+          break;
+        }
+        const int b = c / cpb, t0 = (c % cpb) * kKC;
+        const uint32_t bar = smem_u32(&s_full[s]);
+        const uint32_t sa = base + s * stage_bytes, sb = sa + 16384u;
+        mbar_arrive_expect_tx(bar, stage_bytes);
+        for (int h = 0; h < 2; ++h) {
+          const int m = m0 + 64 * h;
+          tma_load_5d(sa + h * 8192u, &dgr_map, bar, m % D, n, m / D, t0, b);
+        }
+        for (int j = 0; j < NP / 64; ++j) tma_load_4d(sb + j * 8192u, &hbf_map, bar, p0 + 64 * j, n, t0, b);
+      }
+    }
+  } else if (warp == 1) {
+    if (lane == 0) {
+      const uint32_t idesc = umma_idesc_bf16(128, NP, true, true);
+      for (int i = 0; i < n_chunks; ++i) {
+        const int s = i % kTmaStages;
+        if (!mbar_wait_bounded<false>(smem_u32(&s_full[s]), (i / kTmaStages) & 1, kLimit, abort_flag)) {
+          atomicCAS(p.err, 0, kErrWaitWx);
+          ok = false;
+          break;
+        }
+        tc_fence_after_sync();
+        const uint32_t sa = base + s * stage_bytes, sb = sa + 16384u;
+#pragma unroll
+        for (int kk = 0; kk < kKC / 16; ++kk) {
+          const uint64_t ad = umma_smem_desc_mn_sw128(sa + kk * 2048u, 8192u);
+          const uint64_t bd = umma_smem_desc_mn_sw128(sb + kk * 2048u, 8192u);
+          umma_bf16_ss(tbase, ad, bd, idesc, (i > 0 || kk > 0) ? 1u : 0u);
+        }
+        umma_commit(smem_u32(&s_empty[s]));  // the stage is free once these MMAs have read it
+      }
+      if (ok) umma_commit(smem_u32(&s_acc));
+    }
+  } else {
+    const int q = warp & 3;  // TMEM lane quarter this warp may read
+    const int m = m0 + 32 * q + lane;
+    bool have = n_chunks > 0;
+    if (have && !mbar_wait_bounded<false>(smem_u32(&s_acc), 0, kLimit, abort_flag)) {
+      atomicCAS(p.err, 0, kErrWaitMma);
+      have = false;
+    }
+    tc_fence_after_sync();
+    float* dst = nullptr;
+    if (m < M) {
+      const int g = m / D, o = m % D;
+      dst = p.out + static_cast<size_t>(split) * GR * p.N * D * D + ((static_cast<size_t>(g) * p.N + n) * D + o) * D + p0;
+    }
+    for (int c8 = 0; c8 < NP; c8 += 8) {
+      uint32_t r[8] = {0u, 0u, 0u, 0u, 0u, 0u, 0u, 0u};
+      if (have) {
+        tmem_ld_x8(tmem_addr(tbase, 32 * q, c8), r);
+        tmem_ld_wait();
+      }
+      if (dst != nullptr) {
+        *reinterpret_cast<float4*>(dst + c8) = make_float4(__uint_as_float(r[0]), __uint_as_float(r[1]), __uint_as_float(r[2]), __uint_as_float(r[3]));
+        *reinterpret_cast<float4*>(dst + c8 + 4) = make_float4(__uint_as_float(r[4]), __uint_as_float(r[5]), __uint_as_float(r[6]), __uint_as_float(r[7]));
+      }
+    }
+  }
+  if (*abort_flag != 0) {
+    const uint64_t t0 = global_timer_ns();
+    while (global_timer_ns() - t0 < 200000ull) __nanosleep(1000);
+  }
+  tc_fence_before_sync();
+  __syncthreads();
+  if (warp == 1) tmem_dealloc(tbase, tmem_cols);
+}
+
 __global__ void reduce_parts_kernel(const float* __restrict__ parts, float* __restrict__ out, long long n, int nparts) {
   const long long i = (static_cast<long long>(blockIdx.x) * blockDim.x + threadIdx.x) * 4;
   if (i >= n) return;
@@ -151,13 +284,18 @@ __global__ void reduce_parts_kernel(const float* __restrict__ parts, float* __re
 
 }  // namespace
 
+// The TMA kernel needs whole 64-element boxes along both output dimensions.
+static bool wgrad_uses_tma(int D, int np) { return D % 64 == 0 && np % 64 == 0; }
+
 int wgrad_plan(int gr, int B, int T, int N, int D, int* np_out, int* ksplit_out, int* cps_out) {
   const int npt = (D + 255) / 256;
   if (D % (16 * npt) != 0) return -2;
   const int np = D / npt;
   const int mtiles = (gr * D + 127) / 128;
   const long long tiles = static_cast<long long>(mtiles) * npt * N;
-  const long long chunks = (static_cast<long long>(B) * T + kKC - 1) / kKC;
+  const long long chunks = wgrad_uses_tma(D, np)
+                               ? static_cast<long long>(B) * ((T + kKC - 1) / kKC)   // per batch row
+                               : (static_cast<long long>(B) * T + kKC - 1) / kKC;
   long long ks = 148 / tiles;
   if (ks < 1) ks = 1;
   if (ks > 32) ks = 32;
@@ -181,12 +319,29 @@ int wgrad_launch(int gr, int gb, const __nv_bfloat16* dgr, const __nv_bfloat16* 
   p.err = err;
   p.B = B; p.T = T; p.N = N; p.D = D; p.GR = gr;
   p.NP = np; p.ksplit = ksplit; p.chunks_per_split = cps;
-  const int smem = 16 * 1024 + (np / 8) * 1024;
-  cudaError_t e = cudaFuncSetAttribute(wgrad_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, smem);
-  if (e != cudaSuccess) return static_cast<int>(e);
   const int mtiles = (gr * D + 127) / 128;
   dim3 grid(static_cast<unsigned>(mtiles * (D / np)), static_cast<unsigned>(N), static_cast<unsigned>(ksplit));
-  wgrad_kernel<<<grid, kThreads, smem, s>>>(p);
+  cudaError_t e;
+  if (wgrad_uses_tma(D, np)) {
+    CUtensorMap dgr_map, hbf_map;
+    const uint64_t ddims[5] = {static_cast<uint64_t>(D), static_cast<uint64_t>(N), static_cast<uint64_t>(gr),
+                               static_cast<uint64_t>(T), static_cast<uint64_t>(B)};
+    const uint32_t dbox[5] = {64u, 1u, 1u, static_cast<uint32_t>(kKC), 1u};
+    const uint64_t hdims[4] = {static_cast<uint64_t>(D), static_cast<uint64_t>(N), static_cast<uint64_t>(T + 1),
+                               static_cast<uint64_t>(B)};
+    const uint32_t hbox[4] = {64u, 1u, static_cast<uint32_t>(kKC), 1u};
+    if (make_tensor_map(&dgr_map, dgr, 2, 5, ddims, dbox, true) != 0) return -4;
+    if (make_tensor_map(&hbf_map, hbf, 2, 4, hdims, hbox, true) != 0) return -4;
+    const int smem = kTmaStages * (16384 + np * 128) + 1024;
+    e = cudaFuncSetAttribute(wgrad_tma_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, smem);
+    if (e != cudaSuccess) return static_cast<int>(e);
+    wgrad_tma_kernel<<<grid, kTmaThreads, smem, s>>>(p, dgr_map, hbf_map);
+  } else {
+    const int smem = 16 * 1024 + (np / 8) * 1024;
+    e = cudaFuncSetAttribute(wgrad_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, smem);
+    if (e != cudaSuccess) return static_cast<int>(e);
+    wgrad_kernel<<<grid, kThreads, smem, s>>>(p);
+  }
   e = cudaGetLastError();
   if (e != cudaSuccess) return static_cast<int>(e);
   const long long nR = static_cast<long long>(gr) * N * D * D;
