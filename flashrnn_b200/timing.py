@@ -1,0 +1,122 @@
+"""Per-kernel timing of the recurrence on arbitrary shapes (CUDA events, through the C ABI).
+
+    python -m flashrnn_b200.timing                 # the benchmark configurations that fit one GPU
+    python -m flashrnn_b200.timing lstm 16 1024 3 256
+
+The head-dimension sweep mirrors the reference's published one
+(flashrnn/speed_experiments/kernel_speed_benchmark.py:104-127: N*D = 768, B = 16, T = 1024).
+Prints one markdown table row per shape: forward, backward and dR/db times, fwd+bwd (B*T)/s and the
+in-kernel phase timers of CTA 0.
+"""
+
+from __future__ import annotations
+
+import sys
+
+import torch
+
+from . import _lib
+from .workloads import HEAD_DIM_SWEEP, SIZES, make_inputs
+
+
+def time_shape(cell: str, B: int, T: int, N: int, D: int, reps: int = 5, device: str = "cuda:0") -> dict:
+    lib = _lib.load()
+    dev = torch.device(device)
+    plan = _lib.plan(cell, B, T, N, D)
+    if not plan.supported:
+        return {"supported": False}
+    gr, gw, gb, S = SIZES[cell]
+    f32, bf = torch.float32, torch.bfloat16
+    wx, R, b, init = make_inputs(cell, B, T, N, D, 3, zero_initial=(cell == "slstm"))
+    wx, R = wx.to(dev).to(bf).contiguous(), R.to(dev).to(bf).contiguous()
+    b, init = b.to(dev), init.to(dev)
+    hist = torch.empty((S, B, T, N, D), dtype=f32, device=dev)
+    carry = torch.empty((S, B, 1, N, D), dtype=f32, device=dev)
+    cache = torch.empty(max(plan.cache_bytes // 4, 1), dtype=f32, device=dev)
+    hbf = torch.empty(plan.hbf_bytes // 2, dtype=bf, device=dev)
+    d_hist = torch.zeros_like(hist)
+    d_hist[0] = 1.0
+    d_carry = torch.zeros_like(carry)
+    dwx = torch.empty_like(wx)
+    dgr = torch.empty(plan.dgr_bytes // 2, dtype=bf, device=dev)
+    d_init = torch.empty_like(carry)
+    db_part = torch.empty(plan.dbpart_bytes // 4, dtype=f32, device=dev)
+    dR = torch.empty((gr, N, D, D), dtype=f32, device=dev)
+    db = torch.empty((gb, N, D), dtype=f32, device=dev)
+    work = torch.empty(max(plan.wgrad_work_bytes // 4, 1), dtype=f32, device=dev)
+    err = torch.zeros(32, dtype=torch.int32, device=dev)
+    stream = torch.cuda.current_stream(dev).cuda_stream
+    cid = _lib.CELLS[cell]
+    zero_first = int(cell == "slstm")
+    cache_ptr = cache.data_ptr() if plan.cache_bytes else None
+
+    def fwd():
+        _lib.check(lib.frnn_b200_forward(cid, wx.data_ptr(), 1, R.data_ptr(), b.data_ptr(), init.data_ptr(),
+                                         hist.data_ptr(), carry.data_ptr(), cache_ptr, hbf.data_ptr(), B, T, N, D,
+                                         zero_first, 0, err.data_ptr(), stream), "forward")
+
+    def bwd():
+        _lib.check(lib.frnn_b200_backward(cid, cache_ptr, hist.data_ptr(), init.data_ptr(), R.data_ptr(),
+                                          d_hist.data_ptr(), d_carry.data_ptr(), dwx.data_ptr(), 1, dgr.data_ptr(),
+                                          d_init.data_ptr(), db_part.data_ptr(), B, T, N, D, zero_first, 0,
+                                          err.data_ptr(), stream), "backward")
+
+    def wgrad():
+        _lib.check(lib.frnn_b200_wgrad(cid, dgr.data_ptr(), hbf.data_ptr(), db_part.data_ptr(), dR.data_ptr(),
+                                       db.data_ptr(), work.data_ptr(), B, T, N, D, err.data_ptr(), stream), "wgrad")
+
+    out = {"supported": True, "cluster": plan.cluster, "ctas": plan.grid_ctas}
+    for name, fn in (("fwd", fwd), ("bwd", bwd), ("wgrad", wgrad)):
+        fn()
+        torch.cuda.synchronize()
+        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        e0.record()
+        for _ in range(reps):
+            fn()
+        e1.record()
+        e1.synchronize()
+        out[name] = e0.elapsed_time(e1) / reps
+    for name, fn in (("fwd", fwd), ("bwd", bwd)):
+        err.zero_()
+        err[3] = 1
+        fn()
+        torch.cuda.synchronize()
+        v = err.tolist()
+        out[name + "_phases"] = [round(v[8 + i] / T) for i in range(8)] + [round(v[16] / T), round(v[17] / T)]
+    err.zero_()
+    if int(err[0].item()) != 0:
+        raise RuntimeError(f"device-side error {err.tolist()}")
+    return out
+
+
+def row(cell, B, T, N, D, r) -> str:
+    if not r["supported"]:
+        return f"| {cell} | {B} | {T} | {N} | {D} | not supported by the cluster kernels (D > 512) | | | | | |"
+    tot = r["fwd"] + r["bwd"] + r["wgrad"]
+    return (f"| {cell} | {B} | {T} | {N} | {D} | {r['cluster']} / {r['ctas']} | {r['fwd']:.3f} | {r['bwd']:.3f} | "
+            f"{r['wgrad']:.3f} | {B * T / tot * 1e3 / 1e6:.2f} | {r['fwd'] * 1e3 / T:.2f} / {r['bwd'] * 1e3 / T:.2f} |")
+
+
+HEADER = ("| cell | B | T | N | D | cluster / CTAs | fwd ms | bwd ms | dR+db ms | fwd+bwd M(B*T)/s | µs/step fwd / bwd |\n"
+          "|---|---|---|---|---|---|---|---|---|---|---|")
+
+
+def main(argv) -> None:
+    if len(argv) == 5:
+        cell, B, T, N, D = argv[0], *map(int, argv[1:])
+        r = time_shape(cell, B, T, N, D)
+        print(HEADER)
+        print(row(cell, B, T, N, D, r))
+        print(r)
+        return
+    shapes = [("lstm", 8, 256, 1, 64), ("lstm", 8, 1024, 3, 256), ("slstm", 16, 2048, 4, 128)]
+    for cell in ("lstm", "gru", "elman"):
+        shapes += [(cell, 16, 1024, n, d) for d, n in HEAD_DIM_SWEEP]
+    shapes += [("lstm", 32, 2048, 4, 128)]  # one GPU's shard of N32 D128 B256 T2048 split over 8 GPUs by heads and batch
+    print(HEADER)
+    for s in shapes:
+        print(row(*s, time_shape(*s)), flush=True)
+
+
+if __name__ == "__main__":
+    main(sys.argv[1:])
