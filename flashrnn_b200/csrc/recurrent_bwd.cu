@@ -85,6 +85,8 @@ frnn_bwd_kernel(const BwdParams p, const __grid_constant__ CUtensorMap cache_map
   uint8_t* const stages = smem + ((Cfg::DGBUF_BYTES + 2 * part_bytes + Cfg::DBUF_BYTES + 127) & ~127);
   const volatile int* abort_flag = p.err;
   const uint64_t limit = p.wait_limit_ns;
+  // test hook: with err[4] = 1 no CTA scatters partial dh from iteration err[5] on, so the next wait runs out
+  const int mute_from = p.err[4] != 0 ? p.err[5] : 0x7fffffff;
   const bool prof = p.err[3] != 0 && blockIdx.x == 0 && lane == 0 && (warp == 0 || warp == 4);
 
   if (tid == 0) {
@@ -227,6 +229,9 @@ frnn_bwd_kernel(const BwdParams p, const __grid_constant__ CUtensorMap cache_map
     const int sbu = p.box_b * U;
     const uint32_t dg_off = kmajor_offset(BT, ib, ul);
     long long pc[5] = {0, 0, 0, 0, 0};
+    // Once a wait has failed (`dead`) the warp keeps walking through the loop without waiting, so
+    // that the warp-wide tcgen05.ld below is always executed by all of its lanes.
+    bool dead = false;
     for (int it = 0; it <= T; ++it) {
       const int t = T - 1 - it;
       const long long c0 = prof ? clock64() : 0;
@@ -238,9 +243,9 @@ frnn_bwd_kernel(const BwdParams p, const __grid_constant__ CUtensorMap cache_map
       float cache[CT::GC][IPT], sn[S][IPT], sp[S][IPT];
       if (it < T) {
         const int s = it % kStages;
-        if (!mbar_wait_bounded<false>(smem_u32(&s_full[s]), (it / kStages) & 1, limit, abort_flag)) {
+        if (!dead && !mbar_wait_bounded<false>(smem_u32(&s_full[s]), (it / kStages) & 1, limit, abort_flag)) {
           report(p.err, kErrWaitWx, it);
-          break;
+          dead = true;
         }
         if (active) {
           const float* sb = reinterpret_cast<const float*>(stages + s * Cfg::STAGE_BYTES);
@@ -267,11 +272,12 @@ frnn_bwd_kernel(const BwdParams p, const __grid_constant__ CUtensorMap cache_map
       if (it >= 1) {
         // partial dh for this step from every CTA of the cluster
         const int pb = it & 1;
-        if (!mbar_wait_bounded<true, true>(smem_u32(&s_part_bar[pb]), ((it - 1) >> 1) & 1, limit, abort_flag)) {
+        if (!dead && !mbar_wait_bounded<true, true>(smem_u32(&s_part_bar[pb]), ((it - 1) >> 1) & 1, limit, abort_flag)) {
           report(p.err, kErrWaitPart, it);
-          break;
+          dead = true;
         }
-        if (tid == 0 && it + 2 <= T) mbar_arrive_expect_tx(smem_u32(&s_part_bar[pb]), part_tx);
+        // re-arm only a barrier whose phase has really completed (arriving twice in one phase is invalid)
+        if (tid == 0 && !dead && it + 2 <= T) mbar_arrive_expect_tx(smem_u32(&s_part_bar[pb]), part_tx);
         if (active) {
           const float* pbuf = part + static_cast<size_t>(pb) * (part_bytes / 4) + ul * BP + ib;
           for (int src = 0; src < C; ++src) {
@@ -348,9 +354,9 @@ frnn_bwd_kernel(const BwdParams p, const __grid_constant__ CUtensorMap cache_map
           for (int g = 0; g < CT::GW; ++g) st_f32_vec<IPT>(dwx_g + g * ND, dgw[g]);
         }
       }
-      if (!mbar_wait_bounded<false>(smem_u32(&s_mma_bar), it & 1, limit, abort_flag)) {
+      if (!dead && !mbar_wait_bounded<false>(smem_u32(&s_mma_bar), it & 1, limit, abort_flag)) {
         report(p.err, kErrWaitMma, it);
-        break;
+        dead = true;
       }
       tc_fence_after_sync();
       const long long c4 = prof ? clock64() : 0;
@@ -364,7 +370,7 @@ frnn_bwd_kernel(const BwdParams p, const __grid_constant__ CUtensorMap cache_map
         for (int c = 0; c < BV / 8; ++c) tmem_ld_x8(tmem_addr(tbase, 32 * warp, j * BT + 8 * c), r[c]);
         tmem_ld_wait();
         const int pp = j * 128 + tid;
-        if (pp < D) {
+        if (pp < D && !dead && it < mute_from) {
           const int dest = pp / U, pl = pp % U;
           const uint32_t ra = map_to_cta(part_base + pl * BP * 4, dest);
           const uint32_t rb = map_to_cta(bar_local, dest);

@@ -75,6 +75,8 @@ frnn_fwd_kernel(const FwdParams p, const __grid_constant__ CUtensorMap wx_map) {
   uint8_t* const wxs = smem + ((2 * hbuf_bytes + Cfg::GBUF_BYTES + 127) & ~127);
   const volatile int* abort_flag = p.err;
   const uint64_t limit = p.wait_limit_ns;
+  // test hook: with err[4] = 1 no CTA publishes h from step err[5] on, so the next operand wait runs out
+  const int mute_from = p.err[4] != 0 ? p.err[5] : 0x7fffffff;
   const bool prof = p.err[3] != 0 && blockIdx.x == 0 && lane == 0 && (warp == 0 || warp == 4);
   const int a_cols = MT * (D / 2);
   uint32_t tmem_cols = 32;
@@ -339,7 +341,7 @@ frnn_fwd_kernel(const FwdParams p, const __grid_constant__ CUtensorMap wx_map) {
 #pragma unroll
           for (int j = 0; j < 4; ++j) pk[j] = hp[j % (IPT / 2)];
         }
-        if (active && t + 1 < T) {
+        if (active && !dead && t + 1 < T && t < mute_from) {
           const uint32_t dst = smem_u32(hbuf + ((t + 1) & 1) * hbuf_bytes) + (h_off & ~15u);
           const uint32_t bar = smem_u32(&s_hbar[(t + 1) & 1]);
           const int first = lane & (LPP - 1);

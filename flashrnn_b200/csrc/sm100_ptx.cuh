@@ -386,4 +386,41 @@ __device__ __forceinline__ void mbar_expect_tx(uint32_t bar, uint32_t bytes) {
   asm volatile("mbarrier.expect_tx.relaxed.cta.shared::cta.b64 [%0], %1;" ::"r"(bar), "r"(bytes) : "memory");
 }
 
+// ----------------------------------------------------------------------------------------------
+// exchange through global memory (groups of CTAs larger than a cluster)
+// ----------------------------------------------------------------------------------------------
+__device__ __forceinline__ uint32_t ld_acquire_gpu_u32(const uint32_t* p) {
+  uint32_t v;
+  asm volatile("ld.acquire.gpu.global.u32 %0, [%1];" : "=r"(v) : "l"(p) : "memory");
+  return v;
+}
+__device__ __forceinline__ void red_release_gpu_add_u32(uint32_t* p, uint32_t v) {
+  asm volatile("red.release.gpu.global.add.u32 [%0], %1;" ::"l"(p), "r"(v) : "memory");
+}
+__device__ __forceinline__ void fence_proxy_async_global() {
+  asm volatile("fence.proxy.async.global;" ::: "memory");
+}
+// 1-D bulk copy global -> this CTA's shared memory; size and both addresses multiples of 16 bytes.
+__device__ __forceinline__ void bulk_load_1d(uint32_t dst, const void* src, uint32_t bytes, uint32_t bar) {
+  asm volatile("cp.async.bulk.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1], %2, [%3];" ::"r"(dst),
+               "l"(reinterpret_cast<uint64_t>(src)), "r"(bytes), "r"(bar)
+               : "memory");
+}
+// Bounded wait until *counter >= target (acquire, gpu scope).
+__device__ __forceinline__ bool counter_wait_bounded(const uint32_t* counter, uint32_t target, uint64_t limit_ns,
+                                                     const volatile int* abort_flag) {
+  for (int fast = 0; fast < 64; ++fast) {
+    if (ld_acquire_gpu_u32(counter) >= target) return true;
+  }
+  const uint64_t t0 = global_timer_ns();
+  uint32_t spins = 0;
+  while (true) {
+    if (ld_acquire_gpu_u32(counter) >= target) return true;
+    if ((++spins & 63u) == 0u) {
+      if (abort_flag != nullptr && *abort_flag != 0) return false;
+      if (global_timer_ns() - t0 > limit_ns) return false;
+    }
+  }
+}
+
 }  // namespace frnn
