@@ -300,12 +300,12 @@ def kernel_breakdown(_lib, dev, d_wx, d_R, d_b, d_init, flush, reps):
     def fwd():
         _lib.check(lib.frnn_b200_forward(cid, d_wx.data_ptr(), 1, d_R.data_ptr(), d_b.data_ptr(), d_init.data_ptr(),
                                          history.data_ptr(), carry.data_ptr(), cache.data_ptr(), hbf.data_ptr(),
-                                         B, T, N, D, 0, 0, err.data_ptr(), stream), "forward")
+                                         None, B, T, N, D, 0, 0, err.data_ptr(), stream), "forward")
 
     def bwd():
         _lib.check(lib.frnn_b200_backward(cid, cache.data_ptr(), history.data_ptr(), d_init.data_ptr(),
                                           d_R.data_ptr(), d_history.data_ptr(), d_carry.data_ptr(), dwx.data_ptr(), 1,
-                                          dgr.data_ptr(), d_initial.data_ptr(), db_part.data_ptr(), B, T, N, D, 0, 0,
+                                          dgr.data_ptr(), d_initial.data_ptr(), db_part.data_ptr(), None, B, T, N, D, 0, 0,
                                           err.data_ptr(), stream), "backward")
 
     def wgrad():

@@ -39,7 +39,7 @@ class Plan(ctypes.Structure):
         ("unit", c_int), ("cluster", c_int), ("batch_tile", c_int), ("n_btiles", c_int), ("grid_ctas", c_int),
         ("supported", c_int),
         ("cache_bytes", c_int64), ("hbf_bytes", c_int64), ("dgr_bytes", c_int64), ("dbpart_bytes", c_int64),
-        ("wgrad_work_bytes", c_int64), ("wgrad_ksplit", c_int),
+        ("wgrad_work_bytes", c_int64), ("wgrad_ksplit", c_int), ("exchange", c_int), ("xchg_bytes", c_int64),
     ]
 
 
@@ -48,10 +48,11 @@ SIGNATURES = {
     "frnn_b200_version": (c_int, []),
     "frnn_b200_plan": (c_int, [c_int, c_int, c_int, c_int, c_int, POINTER(Plan)]),
     "frnn_b200_forward": (c_int, [c_int, c_void_p, c_int, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p,
-                                  c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_int, c_int, c_void_p, c_void_p]),
+                                  c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_int, c_int, c_void_p,
+                                  c_void_p]),
     "frnn_b200_backward": (c_int, [c_int, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p,
-                                   c_int, c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_int, c_int,
-                                   c_void_p, c_void_p]),
+                                   c_int, c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_int,
+                                   c_int, c_void_p, c_void_p]),
     "frnn_b200_wgrad": (c_int, [c_int, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_int,
                                 c_int, c_int, c_void_p, c_void_p]),
     "frnn_b200_wgrad_noalloc": (c_int, [c_int, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_int, c_int,

@@ -98,7 +98,14 @@ extern "C" int frnn_b200_plan(int cell, int B, int T, int N, int D, frnn_b200_pl
   const int fwd_cols = ((mt * bt + 31) / 32 * 32) + mt * (D / 2);
   const int mtb = (D + 127) / 128;
   const int bwd_cols = ((mtb * bt + 31) / 32 * 32) + mtb * (rows / 2);
-  out->supported = (D % 16 == 0) && out->cluster <= 16 && fwd_cols <= 512 && bwd_cols <= 512;
+  out->exchange = out->cluster > 16 ? 1 : 0;  // wider than a cluster: exchange through global memory
+  out->supported = (D % 16 == 0) && fwd_cols <= 512 && bwd_cols <= 512 && (out->exchange == 0 || out->unit == 32);
+  if (out->exchange) {
+    const int64_t groups = static_cast<int64_t>(N) * out->n_btiles;
+    const int64_t fwd_b = 2ll * 16 * D * 2;                                          // two parity operand buffers
+    const int64_t bwd_b = 2ll * out->cluster * out->cluster * 32 * (out->batch_tile + 4) * 4;  // partial-dh blocks
+    out->xchg_bytes = 4096 + groups * 512 + groups * (fwd_b > bwd_b ? fwd_b : bwd_b);
+  }
   const int64_t btnd = static_cast<int64_t>(B) * T * N * D;
   out->cache_bytes = btnd * c.gc * 4;
   out->hbf_bytes = static_cast<int64_t>(B) * (T + 1) * N * D * 2;
@@ -115,9 +122,9 @@ extern "C" int frnn_b200_plan(int cell, int B, int T, int N, int D, frnn_b200_pl
 }
 
 extern "C" int frnn_b200_forward(int cell, const void* wx, int wx_bf16, const void* r_bf16, const float* bias,
-                                 const float* initial, float* history, float* carry, float* cache, void* hbf, int B,
-                                 int T, int N, int D, int slstm_zero_first, int wait_limit_ms, int* err,
-                                 void* stream) {
+                                 const float* initial, float* history, float* carry, float* cache, void* hbf,
+                                 void* xchg, int B, int T, int N, int D, int slstm_zero_first, int wait_limit_ms,
+                                 int* err, void* stream) {
   frnn_b200_plan_t plan;
   const int rc = frnn_b200_plan(cell, B, T, N, D, &plan);
   if (rc != 0) return rc;
@@ -137,13 +144,21 @@ extern "C" int frnn_b200_forward(int cell, const void* wx, int wx_bf16, const vo
   p.wx_box_b = plan.batch_tile;  // rows past B are filled with zeros by TMA
   p.slstm_zero_first = slstm_zero_first;
   p.wait_limit_ns = (wait_limit_ms > 0 ? static_cast<unsigned long long>(wait_limit_ms) : 2000ull) * 1000000ull;
+  if (plan.exchange) {
+    if (!xchg) return -5;
+    const size_t counters = static_cast<size_t>(N) * plan.n_btiles * 512;
+    const cudaError_t me = cudaMemsetAsync(xchg, 0, static_cast<size_t>(plan.xchg_bytes), static_cast<cudaStream_t>(stream));
+    if (me != cudaSuccess) return static_cast<int>(me);
+    p.xg_counters = static_cast<uint32_t*>(xchg);
+    p.xg_data = static_cast<uint8_t*>(xchg) + ((counters + 4095) & ~static_cast<size_t>(4095));
+  }
   return forward_dispatch(cell, p, wx, wx_bf16, plan.batch_tile, plan.unit, static_cast<cudaStream_t>(stream));
 }
 
 extern "C" int frnn_b200_backward(int cell, const float* cache, const float* history, const float* initial,
                                   const void* r_bf16, const float* d_history, const float* d_carry, void* dwx,
-                                  int wx_bf16, void* dgr, float* d_initial, float* db_part, int B, int T, int N, int D,
-                                  int slstm_zero_first, int wait_limit_ms, int* err, void* stream) {
+                                  int wx_bf16, void* dgr, float* d_initial, float* db_part, void* xchg, int B, int T,
+                                  int N, int D, int slstm_zero_first, int wait_limit_ms, int* err, void* stream) {
   frnn_b200_plan_t plan;
   const int rc = frnn_b200_plan(cell, B, T, N, D, &plan);
   if (rc != 0) return rc;
@@ -164,6 +179,14 @@ extern "C" int frnn_b200_backward(int cell, const float* cache, const float* his
   p.box_b = plan.batch_tile;  // rows past B are filled with zeros by TMA
   p.slstm_zero_first = slstm_zero_first;
   p.wait_limit_ns = (wait_limit_ms > 0 ? static_cast<unsigned long long>(wait_limit_ms) : 2000ull) * 1000000ull;
+  if (plan.exchange) {
+    if (!xchg) return -5;
+    const size_t counters = static_cast<size_t>(N) * plan.n_btiles * 512;
+    const cudaError_t me = cudaMemsetAsync(xchg, 0, static_cast<size_t>(plan.xchg_bytes), static_cast<cudaStream_t>(stream));
+    if (me != cudaSuccess) return static_cast<int>(me);
+    p.xg_counters = static_cast<uint32_t*>(xchg);
+    p.xg_data = static_cast<uint8_t*>(xchg) + ((counters + 4095) & ~static_cast<size_t>(4095));
+  }
   return backward_dispatch(cell, p, cache, history, initial, d_history, wx_bf16, plan.batch_tile, plan.unit,
                            static_cast<cudaStream_t>(stream));
 }

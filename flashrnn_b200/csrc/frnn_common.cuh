@@ -50,6 +50,10 @@ struct FwdParams {
   int wx_box_b;            // batch extent of the Wx TMA box
   int slstm_zero_first;
   unsigned long long wait_limit_ns;
+  // Exchange through global memory (groups wider than a cluster), null for cluster exchange:
+  // per group two parity copies of the operand buffer, and two arrival counters 256 B apart.
+  uint8_t* xg_data;
+  uint32_t* xg_counters;
 };
 
 struct BwdParams {
@@ -65,6 +69,10 @@ struct BwdParams {
   int box_b;
   int slstm_zero_first;
   unsigned long long wait_limit_ns;
+  // Exchange through global memory, null for cluster exchange: per group two parity copies of
+  // the partial-dh blocks [dest CTA][source CTA][unit][padded batch] and two arrival counters.
+  uint8_t* xg_data;
+  uint32_t* xg_counters;
 };
 
 template <int N>

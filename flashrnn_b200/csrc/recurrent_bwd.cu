@@ -65,7 +65,7 @@ frnn_bwd_kernel(const BwdParams p, const __grid_constant__ CUtensorMap cache_map
 
   const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
   const int D = p.D, N = p.N, T = p.T, B = p.B, C = p.C;
-  const int rank = static_cast<int>(cluster_cta_rank());
+  const int rank = static_cast<int>(blockIdx.x % C);  // == rank inside the cluster when there is one
   const int gid = blockIdx.x / C;
   const int n = gid % N;
   const int btile = gid / N;
@@ -79,10 +79,15 @@ frnn_bwd_kernel(const BwdParams p, const __grid_constant__ CUtensorMap cache_map
   // shared memory carve-up
   constexpr int BP = BV + 4;  // padded batch stride of the partial rows (keeps 16-byte stores aligned, spreads banks)
   const int part_bytes = C * U * BP * 4;  // one parity buffer: [source CTA][unit][batch]
+  const bool xg = p.xg_data != nullptr;   // exchange partial dh through global memory instead of DSMEM
+  const int part_bufs = xg ? 1 : 2;       // the global copy is double-buffered, its staging area is not
   uint8_t* const dgbuf = smem;
   float* const part = reinterpret_cast<float*>(smem + Cfg::DGBUF_BYTES);
-  float* const dbuf = reinterpret_cast<float*>(smem + Cfg::DGBUF_BYTES + 2 * part_bytes);
-  uint8_t* const stages = smem + ((Cfg::DGBUF_BYTES + 2 * part_bytes + Cfg::DBUF_BYTES + 127) & ~127);
+  float* const dbuf = reinterpret_cast<float*>(smem + Cfg::DGBUF_BYTES + part_bufs * part_bytes);
+  uint8_t* const stages = smem + ((Cfg::DGBUF_BYTES + part_bufs * part_bytes + Cfg::DBUF_BYTES + 127) & ~127);
+  // global layout per group: [parity][dest CTA][source CTA][unit][padded batch] fp32
+  uint8_t* const xg_p = xg ? p.xg_data + static_cast<size_t>(gid) * 2 * C * part_bytes : nullptr;
+  uint32_t* const xg_cnt = xg ? p.xg_counters + static_cast<size_t>(gid) * 128 : nullptr;
   const volatile int* abort_flag = p.err;
   const uint64_t limit = p.wait_limit_ns;
   // test hook: with err[4] = 1 no CTA scatters partial dh from iteration err[5] on, so the next wait runs out
@@ -158,7 +163,7 @@ frnn_bwd_kernel(const BwdParams p, const __grid_constant__ CUtensorMap cache_map
   }
   const int bvq = (bv + 3) & ~3;  // batch columns actually sent (whole 16-byte packets)
   const uint32_t part_tx = static_cast<uint32_t>(C) * bvq * U * 4u;
-  if (tid == 0) {
+  if (tid == 0 && !xg) {
     mbar_arrive_expect_tx(smem_u32(&s_part_bar[1]), part_tx);                 // iteration 1 (or final if T == 1)
     if (T >= 2) mbar_arrive_expect_tx(smem_u32(&s_part_bar[0]), part_tx);     // iteration 2
   }
@@ -272,14 +277,26 @@ frnn_bwd_kernel(const BwdParams p, const __grid_constant__ CUtensorMap cache_map
       if (it >= 1) {
         // partial dh for this step from every CTA of the cluster
         const int pb = it & 1;
+        if (xg && tid == 0 && !dead) {
+          // all CTAs of the group have scattered: fetch this CTA's block [source][unit][batch]
+          const uint32_t target = static_cast<uint32_t>(C) * static_cast<uint32_t>(((it - 1) >> 1) + 1);
+          if (counter_wait_bounded(xg_cnt + pb * 64, target, limit, abort_flag)) {
+            fence_proxy_async_global();
+            mbar_arrive_expect_tx(smem_u32(&s_part_bar[pb]), static_cast<uint32_t>(part_bytes));
+            bulk_load_1d(smem_u32(part), xg_p + (static_cast<size_t>(pb) * C + rank) * part_bytes,
+                         static_cast<uint32_t>(part_bytes), smem_u32(&s_part_bar[pb]));
+          } else {
+            report(p.err, kErrWaitPart, it);
+          }
+        }
         if (!dead && !mbar_wait_bounded<true, true>(smem_u32(&s_part_bar[pb]), ((it - 1) >> 1) & 1, limit, abort_flag)) {
           report(p.err, kErrWaitPart, it);
           dead = true;
         }
         // re-arm only a barrier whose phase has really completed (arriving twice in one phase is invalid)
-        if (tid == 0 && !dead && it + 2 <= T) mbar_arrive_expect_tx(smem_u32(&s_part_bar[pb]), part_tx);
+        if (tid == 0 && !dead && !xg && it + 2 <= T) mbar_arrive_expect_tx(smem_u32(&s_part_bar[pb]), part_tx);
         if (active) {
-          const float* pbuf = part + static_cast<size_t>(pb) * (part_bytes / 4) + ul * BP + ib;
+          const float* pbuf = part + static_cast<size_t>(xg ? 0 : pb) * (part_bytes / 4) + ul * BP + ib;
           for (int src = 0; src < C; ++src) {
 #pragma unroll
             for (int j = 0; j < IPT; ++j) ds[0][j] += pbuf[src * U * BP + j * BP];
@@ -372,13 +389,31 @@ frnn_bwd_kernel(const BwdParams p, const __grid_constant__ CUtensorMap cache_map
         const int pp = j * 128 + tid;
         if (pp < D && !dead && it < mute_from) {
           const int dest = pp / U, pl = pp % U;
-          const uint32_t ra = map_to_cta(part_base + pl * BP * 4, dest);
-          const uint32_t rb = map_to_cta(bar_local, dest);
+          if (!xg) {
+            const uint32_t ra = map_to_cta(part_base + pl * BP * 4, dest);
+            const uint32_t rb = map_to_cta(bar_local, dest);
 #pragma unroll
-          for (int c = 0; c < BV / 8; ++c)
+            for (int c = 0; c < BV / 8; ++c)
 #pragma unroll
-            for (int q = 0; q < 8; q += 4)
-              if (8 * c + q < bvq) st_async_v4_b32(ra + (8 * c + q) * 4, r[c][q], r[c][q + 1], r[c][q + 2], r[c][q + 3], rb);
+              for (int q = 0; q < 8; q += 4)
+                if (8 * c + q < bvq) st_async_v4_b32(ra + (8 * c + q) * 4, r[c][q], r[c][q + 1], r[c][q + 2], r[c][q + 3], rb);
+          } else {
+            uint8_t* dst = xg_p + ((static_cast<size_t>(nb) * C + dest) * C + rank) * (U * BP * 4) + pl * BP * 4;
+#pragma unroll
+            for (int c = 0; c < BV / 8; ++c)
+#pragma unroll
+              for (int q = 0; q < 8; q += 4)
+                if (8 * c + q < bvq)
+                  *reinterpret_cast<uint4*>(dst + (8 * c + q) * 4) = make_uint4(r[c][q], r[c][q + 1], r[c][q + 2], r[c][q + 3]);
+          }
+        }
+      }
+      if (xg) {
+        fence_proxy_async_global();
+        asm volatile("bar.sync 2, 128;" ::: "memory");
+        if (tid == 0 && !dead && it < mute_from) {
+          __threadfence();
+          red_release_gpu_add_u32(xg_cnt + nb * 64, 1u);
         }
       }
       tc_fence_before_sync();
@@ -419,7 +454,8 @@ int launch_bwd(const BwdParams& p, const float* cache, const float* history, con
   using Cfg = BwdCfg<CELL, BV, U, WX_BF16>;
   using CT = typename Cfg::CT;
   const int part_bytes = p.C * U * (BV + 4) * 4;
-  const int smem = ((Cfg::DGBUF_BYTES + 2 * part_bytes + Cfg::DBUF_BYTES + 127) & ~127) + kStages * Cfg::STAGE_BYTES;
+  const int part_bufs = p.xg_data != nullptr ? 1 : 2;
+  const int smem = ((Cfg::DGBUF_BYTES + part_bufs * part_bytes + Cfg::DBUF_BYTES + 127) & ~127) + kStages * Cfg::STAGE_BYTES;
   const int MTB = (p.D + 127) / 128;
   if (((MTB * Cfg::BT + 31) / 32 * 32) + MTB * (Cfg::ROWS / 2) > 512) return -3;
   if (smem > 227 * 1024) return -2;
@@ -444,7 +480,7 @@ int launch_bwd(const BwdParams& p, const float* cache, const float* history, con
   auto kern = frnn_bwd_kernel<CELL, BV, U, WX_BF16>;
   cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, smem);
   if (e != cudaSuccess) return static_cast<int>(e);
-  if (p.C > 8) {
+  if (p.C > 8 && p.xg_data == nullptr) {
     e = cudaFuncSetAttribute(kern, cudaFuncAttributeNonPortableClusterSizeAllowed, 1);
     if (e != cudaSuccess) return static_cast<int>(e);
   }
@@ -455,10 +491,16 @@ int launch_bwd(const BwdParams& p, const float* cache, const float* history, con
   cfg.dynamicSmemBytes = smem;
   cfg.stream = stream;
   cudaLaunchAttribute attr[1];
-  attr[0].id = cudaLaunchAttributeClusterDimension;
-  attr[0].val.clusterDim.x = static_cast<unsigned>(p.C);
-  attr[0].val.clusterDim.y = 1;
-  attr[0].val.clusterDim.z = 1;
+  if (p.xg_data == nullptr) {
+    attr[0].id = cudaLaunchAttributeClusterDimension;
+    attr[0].val.clusterDim.x = static_cast<unsigned>(p.C);
+    attr[0].val.clusterDim.y = 1;
+    attr[0].val.clusterDim.z = 1;
+  } else {
+    // the CTAs of a group wait on one another through global memory: all must be resident
+    attr[0].id = cudaLaunchAttributeCooperative;
+    attr[0].val.cooperative = 1;
+  }
   cfg.attrs = attr;
   cfg.numAttrs = 1;
   e = cudaLaunchKernelEx(&cfg, kern, p, cache_map, hist_map, init_map, dhist_map);

@@ -64,7 +64,7 @@ frnn_fwd_kernel(const FwdParams p, const __grid_constant__ CUtensorMap wx_map) {
 
   const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
   const int D = p.D, N = p.N, T = p.T, B = p.B, C = p.C;
-  const int rank = static_cast<int>(cluster_cta_rank());
+  const int rank = static_cast<int>(blockIdx.x % C);  // == rank inside the cluster when there is one
   const int gid = blockIdx.x / C;
   const int n = gid % N;
   const int b0 = (gid / N) * BV;
@@ -75,6 +75,9 @@ frnn_fwd_kernel(const FwdParams p, const __grid_constant__ CUtensorMap wx_map) {
   uint8_t* const wxs = smem + ((2 * hbuf_bytes + Cfg::GBUF_BYTES + 127) & ~127);
   const volatile int* abort_flag = p.err;
   const uint64_t limit = p.wait_limit_ns;
+  const bool xg = p.xg_data != nullptr;  // exchange h through global memory instead of DSMEM
+  uint8_t* const xg_h = xg ? p.xg_data + static_cast<size_t>(gid) * 2 * hbuf_bytes : nullptr;
+  uint32_t* const xg_cnt = xg ? p.xg_counters + static_cast<size_t>(gid) * 128 : nullptr;
   // test hook: with err[4] = 1 no CTA publishes h from step err[5] on, so the next operand wait runs out
   const int mute_from = p.err[4] != 0 ? p.err[5] : 0x7fffffff;
   const bool prof = p.err[3] != 0 && blockIdx.x == 0 && lane == 0 && (warp == 0 || warp == 4);
@@ -157,8 +160,8 @@ frnn_fwd_kernel(const FwdParams p, const __grid_constant__ CUtensorMap wx_map) {
   }
   const uint32_t h_tx_bytes = static_cast<uint32_t>(D) * bv * 2u;
   if (warp == 4 && lane == 0) {
-    if (T >= 2) mbar_arrive_expect_tx(smem_u32(&s_hbar[1]), h_tx_bytes);
-    if (T >= 3) mbar_arrive_expect_tx(smem_u32(&s_hbar[0]), h_tx_bytes);
+    if (!xg && T >= 2) mbar_arrive_expect_tx(smem_u32(&s_hbar[1]), h_tx_bytes);
+    if (!xg && T >= 3) mbar_arrive_expect_tx(smem_u32(&s_hbar[0]), h_tx_bytes);
     tma_prefetch_desc(&wx_map);
   }
   fence_proxy_async();
@@ -175,12 +178,27 @@ frnn_fwd_kernel(const FwdParams p, const __grid_constant__ CUtensorMap wx_map) {
       for (int t = 0; t < T; ++t) {
         const int pb = t & 1;
         const long long m0 = prof ? clock64() : 0;
-        if (t >= 1) {
+        if (t >= 1 && !xg) {
           if (!mbar_wait_bounded<true, true>(smem_u32(&s_hbar[pb]), ((t - 1) >> 1) & 1, limit, abort_flag)) {
             report(p.err, kErrWaitH, t);
             break;
           }
           if (t + 2 <= T - 1) mbar_arrive_expect_tx(smem_u32(&s_hbar[pb]), h_tx_bytes);
+        } else if (t >= 1) {
+          // every CTA of the group has published h_{t-1}: fetch the whole operand with one bulk copy
+          const uint32_t target = static_cast<uint32_t>(C) * static_cast<uint32_t>(((t - 1) >> 1) + 1);
+          if (!counter_wait_bounded(xg_cnt + pb * 64, target, limit, abort_flag)) {
+            report(p.err, kErrWaitH, t);
+            break;
+          }
+          fence_proxy_async_global();
+          mbar_arrive_expect_tx(smem_u32(&s_hbar[pb]), static_cast<uint32_t>(hbuf_bytes));
+          bulk_load_1d(smem_u32(hbuf + pb * hbuf_bytes), xg_h + static_cast<size_t>(pb) * hbuf_bytes,
+                       static_cast<uint32_t>(hbuf_bytes), smem_u32(&s_hbar[pb]));
+          if (!mbar_wait_bounded<false, true>(smem_u32(&s_hbar[pb]), ((t - 1) >> 1) & 1, limit, abort_flag)) {
+            report(p.err, kErrWaitH, t);
+            break;
+          }
         }
         const long long mw = prof ? clock64() : 0;
         fence_proxy_async_smem();
@@ -235,7 +253,7 @@ frnn_fwd_kernel(const FwdParams p, const __grid_constant__ CUtensorMap wx_map) {
 #pragma unroll
       for (int i = 0; i < NPEER; ++i) {
         const int d = i * LPP + (lane & (LPP - 1));
-        peer_delta[i] = d < C ? map_to_cta(base, d) - base : 0u;
+        peer_delta[i] = (!xg && d < C) ? map_to_cta(base, d) - base : 0u;
       }
     }
     const size_t ND = static_cast<size_t>(N) * D;
@@ -341,14 +359,30 @@ frnn_fwd_kernel(const FwdParams p, const __grid_constant__ CUtensorMap wx_map) {
 #pragma unroll
           for (int j = 0; j < 4; ++j) pk[j] = hp[j % (IPT / 2)];
         }
-        if (active && !dead && t + 1 < T && t < mute_from) {
-          const uint32_t dst = smem_u32(hbuf + ((t + 1) & 1) * hbuf_bytes) + (h_off & ~15u);
-          const uint32_t bar = smem_u32(&s_hbar[(t + 1) & 1]);
-          const int first = lane & (LPP - 1);
+        const bool publish = !dead && t + 1 < T && t < mute_from;
+        if (!xg) {
+          if (active && publish) {
+            const uint32_t dst = smem_u32(hbuf + ((t + 1) & 1) * hbuf_bytes) + (h_off & ~15u);
+            const uint32_t bar = smem_u32(&s_hbar[(t + 1) & 1]);
+            const int first = lane & (LPP - 1);
 #pragma unroll
-          for (int i = 0; i < NPEER; ++i) {
-            if (i * LPP + first < C)
-              st_async_v4_b32(dst + peer_delta[i], pk[0], pk[1], pk[2], pk[3], bar + peer_delta[i]);
+            for (int i = 0; i < NPEER; ++i) {
+              if (i * LPP + first < C)
+                st_async_v4_b32(dst + peer_delta[i], pk[0], pk[1], pk[2], pk[3], bar + peer_delta[i]);
+            }
+          }
+        } else {
+          // one lane of each packet group stores the packet into the group's global operand
+          // buffer; after all epilogue threads are through, one thread releases the arrival count
+          if (active && publish && (lane & (LPP - 1)) == 0) {
+            *reinterpret_cast<uint4*>(xg_h + static_cast<size_t>((t + 1) & 1) * hbuf_bytes + (h_off & ~15u)) =
+                make_uint4(pk[0], pk[1], pk[2], pk[3]);
+            fence_proxy_async_global();
+          }
+          asm volatile("bar.sync 2, 128;" ::: "memory");
+          if (tid == 0 && publish) {
+            __threadfence();
+            red_release_gpu_add_u32(xg_cnt + ((t + 1) & 1) * 64, 1u);
           }
         }
       }
@@ -408,7 +442,7 @@ int launch_fwd(const FwdParams& p, const void* wx, cudaStream_t stream) {
   auto kern = frnn_fwd_kernel<CELL, BV, U, WX_BF16>;
   cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, smem);
   if (e != cudaSuccess) return static_cast<int>(e);
-  if (p.C > 8) {
+  if (p.C > 8 && p.xg_data == nullptr) {
     e = cudaFuncSetAttribute(kern, cudaFuncAttributeNonPortableClusterSizeAllowed, 1);
     if (e != cudaSuccess) return static_cast<int>(e);
   }
@@ -419,10 +453,16 @@ int launch_fwd(const FwdParams& p, const void* wx, cudaStream_t stream) {
   cfg.dynamicSmemBytes = smem;
   cfg.stream = stream;
   cudaLaunchAttribute attr[1];
-  attr[0].id = cudaLaunchAttributeClusterDimension;
-  attr[0].val.clusterDim.x = static_cast<unsigned>(p.C);
-  attr[0].val.clusterDim.y = 1;
-  attr[0].val.clusterDim.z = 1;
+  if (p.xg_data == nullptr) {
+    attr[0].id = cudaLaunchAttributeClusterDimension;
+    attr[0].val.clusterDim.x = static_cast<unsigned>(p.C);
+    attr[0].val.clusterDim.y = 1;
+    attr[0].val.clusterDim.z = 1;
+  } else {
+    // the CTAs of a group wait on one another through global memory: all must be resident
+    attr[0].id = cudaLaunchAttributeCooperative;
+    attr[0].val.cooperative = 1;
+  }
   cfg.attrs = attr;
   cfg.numAttrs = 1;
   e = cudaLaunchKernelEx(&cfg, kern, p, map);

@@ -288,8 +288,10 @@ __global__ void reduce_parts_kernel(const float* __restrict__ parts, float* __re
 static bool wgrad_uses_tma(int D, int np) { return D % 64 == 0 && np % 64 == 0; }
 
 int wgrad_plan(int gr, int B, int T, int N, int D, int* np_out, int* ksplit_out, int* cps_out) {
-  const int npt = (D + 255) / 256;
-  if (D % (16 * npt) != 0) return -2;
+  // column tiles: the fewest equal parts of D that are at most 256 wide and a multiple of 16
+  if (D % 16 != 0) return -2;
+  int npt = (D + 255) / 256;
+  while (D % npt != 0 || (D / npt) % 16 != 0) ++npt;
   const int np = D / npt;
   const int mtiles = (gr * D + 127) / 128;
   const long long tiles = static_cast<long long>(mtiles) * npt * N;

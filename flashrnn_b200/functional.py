@@ -84,7 +84,7 @@ class _Recurrence(torch.autograd.Function):
         if not plan.supported:
             raise ValueError(
                 f"flashrnn_b200: cell={cell} D={D} is outside the sm_100a kernel family "
-                f"(needs D/{plan.unit} <= 16 CTAs per head and the R slice resident in tensor memory)"
+                f"(the R slice of a CTA must fit in tensor memory: D <= 768)"
             )
         history = torch.empty((S, B, T, N, D), dtype=torch.float32, device=dev)
         carry = torch.empty((S, B, 1, N, D), dtype=torch.float32, device=dev)
@@ -94,10 +94,11 @@ class _Recurrence(torch.autograd.Function):
             if plan.cache_bytes:
                 cache = torch.empty(plan.cache_bytes // 4, dtype=torch.float32, device=dev)
             hbf = torch.empty(plan.hbf_bytes // 2, dtype=torch.bfloat16, device=dev)
+        xchg = torch.empty(plan.xchg_bytes, dtype=torch.uint8, device=dev) if plan.xchg_bytes else None
         err = torch.zeros(32, dtype=torch.int32, device=dev)
         rc = lib.frnn_b200_forward(
             _lib.CELLS[cell], wx_c.data_ptr(), int(wx_c.dtype == torch.bfloat16), r_bf.data_ptr(), b32.data_ptr(),
-            init32.data_ptr(), history.data_ptr(), carry.data_ptr(), _ptr(cache), _ptr(hbf), B, T, N, D,
+            init32.data_ptr(), history.data_ptr(), carry.data_ptr(), _ptr(cache), _ptr(hbf), _ptr(xchg), B, T, N, D,
             int(zero_first), 0, err.data_ptr(), _stream(dev),
         )
         _lib.check(rc, "frnn_b200_forward")
@@ -135,12 +136,14 @@ class _Recurrence(torch.autograd.Function):
         work = None
         if plan.wgrad_work_bytes:
             work = torch.empty(plan.wgrad_work_bytes // 4, dtype=torch.float32, device=dev)
+        xchg = torch.empty(plan.xchg_bytes, dtype=torch.uint8, device=dev) if plan.xchg_bytes else None
         err = torch.zeros(32, dtype=torch.int32, device=dev)
         stream = _stream(dev)
         rc = lib.frnn_b200_backward(
             _lib.CELLS[cell], _ptr(cache) if cache.numel() else None, history.data_ptr(), init32.data_ptr(),
             r_bf.data_ptr(), d_history.data_ptr(), d_carry.data_ptr(), dwx.data_ptr(),
-            int(wx_dtype == torch.bfloat16), dgr.data_ptr(), d_initial.data_ptr(), db_part.data_ptr(), B, T, N, D,
+            int(wx_dtype == torch.bfloat16), dgr.data_ptr(), d_initial.data_ptr(), db_part.data_ptr(), _ptr(xchg),
+            B, T, N, D,
             int(ctx.zero_first), 0, err.data_ptr(), stream,
         )
         _lib.check(rc, "frnn_b200_backward")

@@ -44,6 +44,8 @@ def time_shape(cell: str, B: int, T: int, N: int, D: int, reps: int = 5, device:
     dR = torch.empty((gr, N, D, D), dtype=f32, device=dev)
     db = torch.empty((gb, N, D), dtype=f32, device=dev)
     work = torch.empty(max(plan.wgrad_work_bytes // 4, 1), dtype=f32, device=dev)
+    xchg = torch.empty(max(plan.xchg_bytes, 1), dtype=torch.uint8, device=dev)
+    xchg_ptr = xchg.data_ptr() if plan.xchg_bytes else None
     err = torch.zeros(32, dtype=torch.int32, device=dev)
     stream = torch.cuda.current_stream(dev).cuda_stream
     cid = _lib.CELLS[cell]
@@ -52,13 +54,13 @@ def time_shape(cell: str, B: int, T: int, N: int, D: int, reps: int = 5, device:
 
     def fwd():
         _lib.check(lib.frnn_b200_forward(cid, wx.data_ptr(), 1, R.data_ptr(), b.data_ptr(), init.data_ptr(),
-                                         hist.data_ptr(), carry.data_ptr(), cache_ptr, hbf.data_ptr(), B, T, N, D,
+                                         hist.data_ptr(), carry.data_ptr(), cache_ptr, hbf.data_ptr(), xchg_ptr, B, T, N, D,
                                          zero_first, 0, err.data_ptr(), stream), "forward")
 
     def bwd():
         _lib.check(lib.frnn_b200_backward(cid, cache_ptr, hist.data_ptr(), init.data_ptr(), R.data_ptr(),
                                           d_hist.data_ptr(), d_carry.data_ptr(), dwx.data_ptr(), 1, dgr.data_ptr(),
-                                          d_init.data_ptr(), db_part.data_ptr(), B, T, N, D, zero_first, 0,
+                                          d_init.data_ptr(), db_part.data_ptr(), xchg_ptr, B, T, N, D, zero_first, 0,
                                           err.data_ptr(), stream), "backward")
 
     def wgrad():
@@ -91,7 +93,7 @@ def time_shape(cell: str, B: int, T: int, N: int, D: int, reps: int = 5, device:
 
 def row(cell, B, T, N, D, r) -> str:
     if not r["supported"]:
-        return f"| {cell} | {B} | {T} | {N} | {D} | not supported by the cluster kernels (D > 512) | | | | | |"
+        return f"| {cell} | {B} | {T} | {N} | {D} | not supported (R slice exceeds tensor memory) | | | | | |"
     tot = r["fwd"] + r["bwd"] + r["wgrad"]
     return (f"| {cell} | {B} | {T} | {N} | {D} | {r['cluster']} / {r['ctas']} | {r['fwd']:.3f} | {r['bwd']:.3f} | "
             f"{r['wgrad']:.3f} | {B * T / tot * 1e3 / 1e6:.2f} | {r['fwd'] * 1e3 / T:.2f} / {r['bwd'] * 1e3 / T:.2f} |")

@@ -54,6 +54,9 @@ typedef struct frnn_b200_plan {
   int64_t dbpart_bytes;  /* float  [n_btiles,gates_b,N,D]  backward -> wgrad       */
   int64_t wgrad_work_bytes; /* float [wgrad_ksplit, gates_r,N,D,D] split-K partials, 0 if none */
   int wgrad_ksplit;
+  int exchange;          /* 0: CTAs of a group exchange through cluster shared memory;
+                            1: group wider than a cluster (D > 512): through global memory  */
+  int64_t xchg_bytes;    /* scratch for exchange = 1 (forward and backward), else 0       */
 } frnn_b200_plan_t;
 
 /* Library / ABI version (major*1000 + minor). */
@@ -71,12 +74,15 @@ int frnn_b200_plan(int cell, int B, int T, int N, int D, frnn_b200_plan_t* out);
  *   bias, initial : fp32
  *   history   : out fp32 [S,B,T,N,D];  carry: out fp32 [S,B,1,N,D]
  *   cache, hbf: scratch written for the backward pass, or NULL for inference
+ *   xchg      : scratch of plan.xchg_bytes when plan.exchange = 1 (cleared by the call), else NULL;
+ *               such shapes are launched cooperatively: N * n_btiles * cluster CTAs must be
+ *               resident at once (one per SM), otherwise the launch returns a CUDA error
  *   slstm_zero_first: 1 if every element of initial n is zero (reference.py:99)
  *   wait_limit_ms: bound for every in-kernel wait (0 = default 2000 ms)              */
 int frnn_b200_forward(int cell, const void* wx, int wx_bf16, const void* r_bf16, const float* bias,
                       const float* initial, float* history, float* carry, float* cache, void* hbf,
-                      int B, int T, int N, int D, int slstm_zero_first, int wait_limit_ms, int* err,
-                      void* stream);
+                      void* xchg, int B, int T, int N, int D, int slstm_zero_first, int wait_limit_ms,
+                      int* err, void* stream);
 
 /* Reverse-time recurrence (flashrnn/flashrnn/fused/flashrnn.cc:147-247 backward();
  * gradient structure of flashrnn/flashrnn/vanilla_fwbw/bw.py:20-98).
@@ -87,8 +93,9 @@ int frnn_b200_forward(int cell, const void* wx, int wx_bf16, const void* r_bf16,
  *   d_initial : out fp32 [S,B,1,N,D];  db_part: out scratch fp32 [n_btiles,GB,N,D]    */
 int frnn_b200_backward(int cell, const float* cache, const float* history, const float* initial,
                        const void* r_bf16, const float* d_history, const float* d_carry, void* dwx,
-                       int wx_bf16, void* dgr, float* d_initial, float* db_part, int B, int T, int N,
-                       int D, int slstm_zero_first, int wait_limit_ms, int* err, void* stream);
+                       int wx_bf16, void* dgr, float* d_initial, float* db_part, void* xchg, int B,
+                       int T, int N, int D, int slstm_zero_first, int wait_limit_ms, int* err,
+                       void* stream);
 
 /* dR[g,n,o,p] = sum_{b,t} dgr[b,t,g,n,o] * hbf[b,t,n,p] and db = sum over batch tiles of
  * db_part (the cuBLAS GEMM + gradientBiasAggregationKernel of

@@ -30,7 +30,9 @@ def test_plan_describes_the_headline_workload():
     assert p.cache_bytes == 8 * 1024 * 4 * 3 * 256 * 4 and p.hbf_bytes == 8 * 1025 * 3 * 256 * 2
     g = _lib.plan("gru", 16, 10, 2, 48)
     assert (g.gates_r, g.gates_b, g.unit, g.cluster, g.n_btiles) == (3, 4, 16, 3, 1)
-    assert not _lib.plan("lstm", 8, 8, 1, 768).supported      # needs the 2-D split kernel
+    wide = _lib.plan("lstm", 16, 8, 1, 768)                  # wider than a cluster: global-memory exchange
+    assert wide.supported and wide.exchange == 1 and wide.cluster == 24 and wide.xchg_bytes > 0
+    assert not _lib.plan("lstm", 8, 8, 1, 1024).supported     # the R slice no longer fits in tensor memory
     assert not _lib.plan("lstm", 8, 8, 1, 40).supported       # the ABI wants D % 16 == 0 (Python pads)
 
 

@@ -74,6 +74,10 @@ SHAPES = [
     ("gru", 6, 9, 3, 32, 30, False),
     ("elman", 16, 30, 2, 128, 31, False),
     ("elman", 1, 1, 1, 16, 32, False),     # single step, single row
+    ("lstm", 16, 12, 1, 768, 35, False),   # 24 CTAs per head: exchange through global memory
+    ("gru", 8, 7, 2, 576, 36, False),      # two such groups side by side
+    ("slstm", 4, 5, 1, 768, 37, True),
+    ("elman", 3, 9, 1, 640, 38, False),
     ("lstm", 1, 1, 1, 3, 33, False),       # the reference's smallest portable-gate shape
     ("gru", 3, 3, 2, 7, 34, False),
 ]

@@ -28,14 +28,14 @@ def _buffers(_lib, cell, B, T, N, D, dev):
 def _forward(lib, _lib, cell, B, T, N, D, t, err, limit_ms):
     return lib.frnn_b200_forward(_lib.CELLS[cell], t["wx"].data_ptr(), 0, t["R"].data_ptr(), t["b"].data_ptr(),
                                  t["init"].data_ptr(), t["hist"].data_ptr(), t["carry"].data_ptr(), t["cache"].data_ptr(),
-                                 t["hbf"].data_ptr(), B, T, N, D, 0, limit_ms, err.data_ptr(),
+                                 t["hbf"].data_ptr(), None, B, T, N, D, 0, limit_ms, err.data_ptr(),
                                  torch.cuda.current_stream().cuda_stream)
 
 
 def _backward(lib, _lib, cell, B, T, N, D, t, err, limit_ms):
     return lib.frnn_b200_backward(_lib.CELLS[cell], t["cache"].data_ptr(), t["hist"].data_ptr(), t["init"].data_ptr(),
                                   t["R"].data_ptr(), t["dH"].data_ptr(), t["dC"].data_ptr(), t["dwx"].data_ptr(), 0,
-                                  t["dgr"].data_ptr(), t["dinit"].data_ptr(), t["dbp"].data_ptr(), B, T, N, D, 0,
+                                  t["dgr"].data_ptr(), t["dinit"].data_ptr(), t["dbp"].data_ptr(), None, B, T, N, D, 0,
                                   limit_ms, err.data_ptr(), torch.cuda.current_stream().cuda_stream)
 
 
