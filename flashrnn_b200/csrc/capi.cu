@@ -36,6 +36,17 @@ EncodeTiledFn encode_tiled_fn() {
   return fn;
 }
 
+// SMs of the current device (148 on a B200; also the answer when no device is visible).
+int sm_count() {
+  int dev = 0, n = 0;
+  if (cudaGetDevice(&dev) != cudaSuccess || cudaDeviceGetAttribute(&n, cudaDevAttrMultiProcessorCount, dev) != cudaSuccess ||
+      n <= 0) {
+    cudaGetLastError();
+    return 148;
+  }
+  return n;
+}
+
 struct CellCounts {
   int gr, gw, gb, s, gc;
 };
@@ -89,7 +100,11 @@ extern "C" int frnn_b200_plan(int cell, int B, int T, int N, int D, frnn_b200_pl
   out->gates_r = c.gr; out->gates_w = c.gw; out->gates_b = c.gb; out->states = c.s; out->cache_gates = c.gc;
   out->unit = (D % 32 == 0) ? 32 : 16;
   out->cluster = D / out->unit;
-  out->batch_tile = B <= 8 ? 8 : 16;
+  // Batch tile: a step costs the same tensor-core time for 8 or 16 rows but twice the epilogue and
+  // exchange work, so 8-row tiles (more, independent groups) win as long as every group still
+  // gets its own SMs; beyond that 16-row tiles halve the number of groups.
+  out->batch_tile = 8;
+  if (B > 8 && static_cast<long long>(N) * ((B + 7) / 8) * out->cluster > sm_count()) out->batch_tile = 16;
   out->n_btiles = (B + out->batch_tile - 1) / out->batch_tile;
   out->grid_ctas = N * out->n_btiles * out->cluster;
   const int bt = 16;

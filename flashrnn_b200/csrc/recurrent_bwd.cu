@@ -58,7 +58,7 @@ frnn_bwd_kernel(const BwdParams p, const __grid_constant__ CUtensorMap cache_map
   extern __shared__ __align__(1024) uint8_t smem[];
   __shared__ __align__(8) uint64_t s_part_bar[2];
   __shared__ __align__(8) uint64_t s_dg_bar;
-  __shared__ __align__(8) uint64_t s_mma_bar;
+  __shared__ __align__(8) uint64_t s_mma_bar[8];  // one per 128-row tile of the partial dh (at most 6)
   __shared__ __align__(8) uint64_t s_full[kStages];
   __shared__ __align__(8) uint64_t s_empty[kStages];
   __shared__ uint32_t s_tmem_base;
@@ -98,7 +98,7 @@ frnn_bwd_kernel(const BwdParams p, const __grid_constant__ CUtensorMap cache_map
     mbar_init(smem_u32(&s_part_bar[0]), 1);
     mbar_init(smem_u32(&s_part_bar[1]), 1);
     mbar_init(smem_u32(&s_dg_bar), kEpiThreads);
-    mbar_init(smem_u32(&s_mma_bar), 1);
+    for (int j = 0; j < 8; ++j) mbar_init(smem_u32(&s_mma_bar[j]), 1);
     for (int s = 0; s < kStages; ++s) {
       mbar_init(smem_u32(&s_full[s]), 1);
       mbar_init(smem_u32(&s_empty[s]), kEpiThreads);
@@ -197,8 +197,10 @@ frnn_bwd_kernel(const BwdParams p, const __grid_constant__ CUtensorMap cache_map
             const uint64_t bdesc = umma_smem_desc(db_addr + kk * 2 * (BT * 16), BT * 16, 128);
             umma_bf16_ts(tbase + j * BT, tbase + a_col0 + j * (ROWS / 2) + kk * 8, bdesc, idesc, kk > 0 ? 1u : 0u);
           }
+          // each tile gets its own completion barrier: its rows are scattered while the next tiles
+          // are still on the tensor core
+          umma_commit(smem_u32(&s_mma_bar[j]));
         }
-        umma_commit(smem_u32(&s_mma_bar));
         if (prof) { pw += m1 - m0; pi += clock64() - m1; }
       }
       if (prof) { p.err[16] = static_cast<int>(pw); p.err[17] = static_cast<int>(pi); }
@@ -371,17 +373,18 @@ frnn_bwd_kernel(const BwdParams p, const __grid_constant__ CUtensorMap cache_map
           for (int g = 0; g < CT::GW; ++g) st_f32_vec<IPT>(dwx_g + g * ND, dgw[g]);
         }
       }
-      if (!dead && !mbar_wait_bounded<false>(smem_u32(&s_mma_bar), it & 1, limit, abort_flag)) {
-        report(p.err, kErrWaitMma, it);
-        dead = true;
-      }
-      tc_fence_after_sync();
-      const long long c4 = prof ? clock64() : 0;
+      long long c4 = 0;
       // scatter partial dh_{t-1} rows to the CTAs that own those units
       const int nb = (it + 1) & 1;
       const uint32_t part_base = smem_u32(part) + static_cast<uint32_t>(nb) * part_bytes + static_cast<uint32_t>(rank) * U * BP * 4;
       const uint32_t bar_local = smem_u32(&s_part_bar[nb]);
       for (int j = 0; j < MTB; ++j) {
+        if (!dead && !mbar_wait_bounded<false>(smem_u32(&s_mma_bar[j]), it & 1, limit, abort_flag)) {
+          report(p.err, kErrWaitMma, it);
+          dead = true;
+        }
+        tc_fence_after_sync();
+        if (prof && j == 0) c4 = clock64();
         uint32_t r[BV / 8][8];
 #pragma unroll
         for (int c = 0; c < BV / 8; ++c) tmem_ld_x8(tmem_addr(tbase, 32 * warp, j * BT + 8 * c), r[c]);

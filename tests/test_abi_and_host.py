@@ -29,7 +29,9 @@ def test_plan_describes_the_headline_workload():
     assert (p.unit, p.cluster, p.batch_tile, p.n_btiles, p.grid_ctas, p.supported) == (32, 8, 8, 1, 24, 1)
     assert p.cache_bytes == 8 * 1024 * 4 * 3 * 256 * 4 and p.hbf_bytes == 8 * 1025 * 3 * 256 * 2
     g = _lib.plan("gru", 16, 10, 2, 48)
-    assert (g.gates_r, g.gates_b, g.unit, g.cluster, g.n_btiles) == (3, 4, 16, 3, 1)
+    assert (g.gates_r, g.gates_b, g.unit, g.cluster, g.batch_tile, g.n_btiles) == (3, 4, 16, 3, 8, 2)
+    big = _lib.plan("lstm", 256, 16, 32, 128)                # more groups than SMs: 16-row batch tiles
+    assert (big.batch_tile, big.n_btiles, big.cluster) == (16, 16, 4)
     wide = _lib.plan("lstm", 16, 8, 1, 768)                  # wider than a cluster: global-memory exchange
     assert wide.supported and wide.exchange == 1 and wide.cluster == 24 and wide.xchg_bytes > 0
     assert not _lib.plan("lstm", 8, 8, 1, 1024).supported     # the R slice no longer fits in tensor memory
