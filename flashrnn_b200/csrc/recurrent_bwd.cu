@@ -64,6 +64,7 @@ frnn_bwd_kernel(const BwdParams p, const __grid_constant__ CUtensorMap cache_map
   __shared__ uint32_t s_tmem_base;
 
   const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
+  const long long t_entry = clock64();
   const int D = p.D, N = p.N, T = p.T, B = p.B, C = p.C;
   const int rank = static_cast<int>(blockIdx.x % C);  // == rank inside the cluster when there is one
   const int gid = blockIdx.x / C;
@@ -118,25 +119,32 @@ frnn_bwd_kernel(const BwdParams p, const __grid_constant__ CUtensorMap cache_map
 
   if (warp < 4) {
     // R_slice^T -> tensor memory: lane = input unit p, column c packs k = 2c, 2c+1 with
-    // k = g*U + u indexing the CTA's rows of R.
-    for (int j = 0; j < MTB; ++j) {
-      const int pp = j * 128 + tid;
-      const bool valid = pp < D;
-      for (int c0 = 0; c0 < ROWS / 2; c0 += 8) {
+    // k = g*U + u indexing the CTA's rows of R. Sixteen rows of R at a time are staged in shared
+    // memory with coalesced 16-byte loads (the TMA ring is still idle) and read back column-wise.
+    __nv_bfloat16* const rbuf = reinterpret_cast<__nv_bfloat16*>(stages);  // [16][D]
+    const int vec_per_row = D / 8;
+    for (int c0 = 0; c0 < ROWS / 2; c0 += 8) {
+      for (int v = tid; v < 16 * vec_per_row; v += kEpiThreads) {
+        const int k = 2 * c0 + v / vec_per_row, pv = v % vec_per_row;
+        const __nv_bfloat16* src = p.R + ((static_cast<size_t>(k / U) * N + n) * D + rank * U + (k % U)) * D + pv * 8;
+        reinterpret_cast<uint4*>(rbuf)[v] = __ldg(reinterpret_cast<const uint4*>(src));
+      }
+      asm volatile("bar.sync 1, 128;" ::: "memory");
+      for (int j = 0; j < MTB; ++j) {
+        const int pp = j * 128 + tid;
         uint32_t r[8];
 #pragma unroll
         for (int q = 0; q < 8; ++q) {
           uint32_t v = 0u;
-          if (valid) {
-            const int k0 = 2 * (c0 + q), k1 = k0 + 1;
-            const __nv_bfloat16 lo = p.R[((static_cast<size_t>(k0 / U) * N + n) * D + rank * U + (k0 % U)) * D + pp];
-            const __nv_bfloat16 hi = p.R[((static_cast<size_t>(k1 / U) * N + n) * D + rank * U + (k1 % U)) * D + pp];
-            v = static_cast<uint32_t>(__bfloat16_as_ushort(lo)) | (static_cast<uint32_t>(__bfloat16_as_ushort(hi)) << 16);
+          if (pp < D) {
+            v = static_cast<uint32_t>(__bfloat16_as_ushort(rbuf[(2 * q) * D + pp])) |
+                (static_cast<uint32_t>(__bfloat16_as_ushort(rbuf[(2 * q + 1) * D + pp])) << 16);
           }
           r[q] = v;
         }
         tmem_st_x8(tmem_addr(tbase, 32 * warp, a_col0 + j * (ROWS / 2) + c0), r);
       }
+      asm volatile("bar.sync 1, 128;" ::: "memory");
     }
     tmem_st_wait();
   }
@@ -179,6 +187,7 @@ frnn_bwd_kernel(const BwdParams p, const __grid_constant__ CUtensorMap cache_map
   cluster_sync_all();
   tc_fence_after_sync();
 
+  if (prof && warp == 0) p.err[20] = static_cast<int>(clock64() - t_entry);  // prologue cycles
   if (warp == 4) {
     if (lane == 0) {
       const uint32_t idesc = umma_idesc_bf16(128, BT, false, false);
@@ -236,6 +245,7 @@ frnn_bwd_kernel(const BwdParams p, const __grid_constant__ CUtensorMap cache_map
     const int sbu = p.box_b * U;
     const uint32_t dg_off = kmajor_offset(BT, ib, ul);
     long long pc[5] = {0, 0, 0, 0, 0};
+    long long pc5 = 0, pc6 = 0;
     // Once a wait has failed (`dead`) the warp keeps walking through the loop without waiting, so
     // that the warp-wide tcgen05.ld below is always executed by all of its lanes.
     bool dead = false;
@@ -254,6 +264,7 @@ frnn_bwd_kernel(const BwdParams p, const __grid_constant__ CUtensorMap cache_map
           report(p.err, kErrWaitWx, it);
           dead = true;
         }
+        if (prof) pc6 += clock64() - c0;
         if (active) {
           const float* sb = reinterpret_cast<const float*>(stages + s * Cfg::STAGE_BYTES);
 #pragma unroll
@@ -295,13 +306,20 @@ frnn_bwd_kernel(const BwdParams p, const __grid_constant__ CUtensorMap cache_map
           report(p.err, kErrWaitPart, it);
           dead = true;
         }
-        // re-arm only a barrier whose phase has really completed (arriving twice in one phase is invalid)
-        if (tid == 0 && !dead && !xg && it + 2 <= T) mbar_arrive_expect_tx(smem_u32(&s_part_bar[pb]), part_tx);
+        if (prof) pc5 += clock64() - c1;
         if (active) {
           const float* pbuf = part + static_cast<size_t>(xg ? 0 : pb) * (part_bytes / 4) + ul * BP + ib;
-          for (int src = 0; src < C; ++src) {
+          // fixed summation order; loads of eight sources are issued together before the adds
+          for (int s0 = 0; s0 < C; s0 += 8) {
+            float v[8][IPT];
 #pragma unroll
-            for (int j = 0; j < IPT; ++j) ds[0][j] += pbuf[src * U * BP + j * BP];
+            for (int k = 0; k < 8; ++k)
+#pragma unroll
+              for (int j = 0; j < IPT; ++j) v[k][j] = (s0 + k < C) ? pbuf[(s0 + k) * U * BP + j * BP] : 0.0f;
+#pragma unroll
+            for (int k = 0; k < 8; ++k)
+#pragma unroll
+              for (int j = 0; j < IPT; ++j) ds[0][j] += v[k][j];
           }
         }
       }
@@ -352,6 +370,11 @@ frnn_bwd_kernel(const BwdParams p, const __grid_constant__ CUtensorMap cache_map
       tc_fence_before_sync();
       mbar_arrive(smem_u32(&s_dg_bar));
       const long long c3 = prof ? clock64() : 0;
+      // Re-arm the partial-dh barrier of this parity for its next use (iteration it + 2), off the
+      // critical path; only a barrier whose phase has really completed may be armed again
+      // (arriving twice in one phase is invalid), hence not after a failed wait.
+      if (tid == 0 && it >= 1 && !dead && !xg && it + 2 <= T)
+        mbar_arrive_expect_tx(smem_u32(&s_part_bar[it & 1]), part_tx);
       if (active) {
         // streams to global memory
         const size_t row = (static_cast<size_t>(b0 + ib) * T + t);
@@ -427,6 +450,8 @@ frnn_bwd_kernel(const BwdParams p, const __grid_constant__ CUtensorMap cache_map
     if (prof) {
 #pragma unroll
       for (int q = 0; q < 5; ++q) p.err[8 + q] = static_cast<int>(pc[q]);
+      p.err[13] = static_cast<int>(pc5);
+      p.err[14] = static_cast<int>(pc6);
     }
   }
 
@@ -458,7 +483,9 @@ int launch_bwd(const BwdParams& p, const float* cache, const float* history, con
   using CT = typename Cfg::CT;
   const int part_bytes = p.C * U * (BV + 4) * 4;
   const int part_bufs = p.xg_data != nullptr ? 1 : 2;
-  const int smem = ((Cfg::DGBUF_BYTES + part_bufs * part_bytes + Cfg::DBUF_BYTES + 127) & ~127) + kStages * Cfg::STAGE_BYTES;
+  // the ring of TMA stages doubles as the staging area of the prologue's R load (16 rows of D bf16)
+  const int ring_bytes = kStages * Cfg::STAGE_BYTES > 16 * p.D * 2 ? kStages * Cfg::STAGE_BYTES : 16 * p.D * 2;
+  const int smem = ((Cfg::DGBUF_BYTES + part_bufs * part_bytes + Cfg::DBUF_BYTES + 127) & ~127) + ring_bytes;
   const int MTB = (p.D + 127) / 128;
   if (((MTB * Cfg::BT + 31) / 32 * 32) + MTB * (Cfg::ROWS / 2) > 512) return -3;
   if (smem > 227 * 1024) return -2;

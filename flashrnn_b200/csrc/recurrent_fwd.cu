@@ -63,6 +63,7 @@ frnn_fwd_kernel(const FwdParams p, const __grid_constant__ CUtensorMap wx_map) {
   __shared__ long long s_prof_clk[2];  // [0] last MMA commit, [1] last h push (phase timers only)
 
   const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
+  const long long t_entry = clock64();
   const int D = p.D, N = p.N, T = p.T, B = p.B, C = p.C;
   const int rank = static_cast<int>(blockIdx.x % C);  // == rank inside the cluster when there is one
   const int gid = blockIdx.x / C;
@@ -170,6 +171,7 @@ frnn_fwd_kernel(const FwdParams p, const __grid_constant__ CUtensorMap wx_map) {
   cluster_sync_all();
   tc_fence_after_sync();
 
+  if (prof && warp == 0) p.err[20] = static_cast<int>(clock64() - t_entry);  // prologue cycles
   // ---------------- main loops ----------------
   if (warp == 4) {
     if (lane == 0) {
@@ -183,7 +185,6 @@ frnn_fwd_kernel(const FwdParams p, const __grid_constant__ CUtensorMap wx_map) {
             report(p.err, kErrWaitH, t);
             break;
           }
-          if (t + 2 <= T - 1) mbar_arrive_expect_tx(smem_u32(&s_hbar[pb]), h_tx_bytes);
         } else if (t >= 1) {
           // every CTA of the group has published h_{t-1}: fetch the whole operand with one bulk copy
           const uint32_t target = static_cast<uint32_t>(C) * static_cast<uint32_t>(((t - 1) >> 1) + 1);
@@ -214,6 +215,9 @@ frnn_fwd_kernel(const FwdParams p, const __grid_constant__ CUtensorMap wx_map) {
           }
         }
         umma_commit(smem_u32(&s_mma_bar));
+        // arm this parity's operand barrier for its next use (step t + 2), after the issue so that it
+        // is off the critical path; its current phase has completed (we waited for it above)
+        if (!xg && t >= 1 && t + 2 <= T - 1) mbar_arrive_expect_tx(smem_u32(&s_hbar[pb]), h_tx_bytes);
         if (prof) {
           const long long m2 = clock64();
           pw += m1 - m0; pi += m2 - m1;

@@ -104,7 +104,7 @@ __global__ void __launch_bounds__(kThreads, 1) wgrad_kernel(const WgradParams p)
       }
       umma_commit(smem_u32(&s_bar));
     }
-    ok = mbar_wait_bounded<false>(smem_u32(&s_bar), issued & 1, 2000000000ull, p.err);
+    ok = mbar_wait_bounded<false, true>(smem_u32(&s_bar), issued & 1, 2000000000ull, p.err);
     ++issued;
     if (!ok) break;
   }
@@ -199,7 +199,7 @@ wgrad_tma_kernel(const WgradParams p, const __grid_constant__ CUtensorMap dgr_ma
       for (int i = 0; i < n_chunks; ++i) {
         const int s = i % kTmaStages, c = c_begin + i;
         if (i >= kTmaStages &&
-            !mbar_wait_bounded<false>(smem_u32(&s_empty[s]), ((i / kTmaStages) - 1) & 1, kLimit, abort_flag)) {
+            !mbar_wait_bounded<false, true>(smem_u32(&s_empty[s]), ((i / kTmaStages) - 1) & 1, kLimit, abort_flag)) {
           atomicCAS(p.err, 0, kErrWaitEmpty);
           break;
         }
@@ -219,7 +219,7 @@ wgrad_tma_kernel(const WgradParams p, const __grid_constant__ CUtensorMap dgr_ma
       const uint32_t idesc = umma_idesc_bf16(128, NP, true, true);
       for (int i = 0; i < n_chunks; ++i) {
         const int s = i % kTmaStages;
-        if (!mbar_wait_bounded<false>(smem_u32(&s_full[s]), (i / kTmaStages) & 1, kLimit, abort_flag)) {
+        if (!mbar_wait_bounded<false, true>(smem_u32(&s_full[s]), (i / kTmaStages) & 1, kLimit, abort_flag)) {
           atomicCAS(p.err, 0, kErrWaitWx);
           ok = false;
           break;
@@ -240,7 +240,7 @@ wgrad_tma_kernel(const WgradParams p, const __grid_constant__ CUtensorMap dgr_ma
     const int q = warp & 3;  // TMEM lane quarter this warp may read
     const int m = m0 + 32 * q + lane;
     bool have = n_chunks > 0;
-    if (have && !mbar_wait_bounded<false>(smem_u32(&s_acc), 0, kLimit, abort_flag)) {
+    if (have && !mbar_wait_bounded<false, true>(smem_u32(&s_acc), 0, kLimit, abort_flag)) {
       atomicCAS(p.err, 0, kErrWaitMma);
       have = false;
     }
