@@ -118,7 +118,7 @@ extern "C" int frnn_b200_plan(int cell, int B, int T, int N, int D, frnn_b200_pl
   if (out->exchange) {
     const int64_t groups = static_cast<int64_t>(N) * out->n_btiles;
     const int64_t fwd_b = 2ll * 16 * D * 2;                                          // two parity operand buffers
-    const int64_t bwd_b = 2ll * out->cluster * out->cluster * 32 * (out->batch_tile + 4) * 4;  // partial-dh blocks
+    const int64_t bwd_b = 2ll * out->cluster * out->cluster * 32 * out->batch_tile * 4;  // partial-dh blocks
     out->xchg_bytes = 4096 + groups * 512 + groups * (fwd_b > bwd_b ? fwd_b : bwd_b);
   }
   const int64_t btnd = static_cast<int64_t>(B) * T * N * D;

@@ -78,8 +78,7 @@ frnn_bwd_kernel(const BwdParams p, const __grid_constant__ CUtensorMap cache_map
   while (tmem_cols < static_cast<uint32_t>(a_col0 + MTB * (ROWS / 2))) tmem_cols <<= 1;
 
   // shared memory carve-up
-  constexpr int BP = BV + 4;  // padded batch stride of the partial rows (keeps 16-byte stores aligned, spreads banks)
-  const int part_bytes = C * U * BP * 4;  // one parity buffer: [source CTA][unit][batch]
+  const int part_bytes = C * BV * U * 4;  // one parity buffer: [source CTA][batch][unit] fp32
   const bool xg = p.xg_data != nullptr;   // exchange partial dh through global memory instead of DSMEM
   const int part_bufs = xg ? 1 : 2;       // the global copy is double-buffered, its staging area is not
   uint8_t* const dgbuf = smem;
@@ -169,8 +168,7 @@ frnn_bwd_kernel(const BwdParams p, const __grid_constant__ CUtensorMap cache_map
 #pragma unroll
     for (int q = 0; q < S; ++q) ld_f32_vec<IPT>(p.d_carry + q * BND + item_bn, dcar[q]);
   }
-  const int bvq = (bv + 3) & ~3;  // batch columns actually sent (whole 16-byte packets)
-  const uint32_t part_tx = static_cast<uint32_t>(C) * bvq * U * 4u;
+  const uint32_t part_tx = static_cast<uint32_t>(C) * bv * U * 4u;
   if (tid == 0 && !xg) {
     mbar_arrive_expect_tx(smem_u32(&s_part_bar[1]), part_tx);                 // iteration 1 (or final if T == 1)
     if (T >= 2) mbar_arrive_expect_tx(smem_u32(&s_part_bar[0]), part_tx);     // iteration 2
@@ -308,14 +306,19 @@ frnn_bwd_kernel(const BwdParams p, const __grid_constant__ CUtensorMap cache_map
         }
         if (prof) pc5 += clock64() - c1;
         if (active) {
-          const float* pbuf = part + static_cast<size_t>(xg ? 0 : pb) * (part_bytes / 4) + ul * BP + ib;
-          // fixed summation order; loads of eight sources are issued together before the adds
+          const float* pbuf = part + static_cast<size_t>(xg ? 0 : pb) * (part_bytes / 4) + ib * U + ul;
+          // fixed summation order; the loads of eight sources are issued together before the adds
           for (int s0 = 0; s0 < C; s0 += 8) {
             float v[8][IPT];
 #pragma unroll
-            for (int k = 0; k < 8; ++k)
+            for (int k = 0; k < 8; ++k) {
+              if (s0 + k < C) {
+                ld_f32_vec<IPT>(pbuf + (s0 + k) * BV * U, v[k]);
+              } else {
 #pragma unroll
-              for (int j = 0; j < IPT; ++j) v[k][j] = (s0 + k < C) ? pbuf[(s0 + k) * U * BP + j * BP] : 0.0f;
+                for (int j = 0; j < IPT; ++j) v[k][j] = 0.0f;
+              }
+            }
 #pragma unroll
             for (int k = 0; k < 8; ++k)
 #pragma unroll
@@ -399,7 +402,7 @@ frnn_bwd_kernel(const BwdParams p, const __grid_constant__ CUtensorMap cache_map
       long long c4 = 0;
       // scatter partial dh_{t-1} rows to the CTAs that own those units
       const int nb = (it + 1) & 1;
-      const uint32_t part_base = smem_u32(part) + static_cast<uint32_t>(nb) * part_bytes + static_cast<uint32_t>(rank) * U * BP * 4;
+      const uint32_t part_base = smem_u32(part) + static_cast<uint32_t>(nb) * part_bytes + static_cast<uint32_t>(rank) * BV * U * 4;
       const uint32_t bar_local = smem_u32(&s_part_bar[nb]);
       for (int j = 0; j < MTB; ++j) {
         if (!dead && !mbar_wait_bounded<false>(smem_u32(&s_mma_bar[j]), it & 1, limit, abort_flag)) {
@@ -412,25 +415,49 @@ frnn_bwd_kernel(const BwdParams p, const __grid_constant__ CUtensorMap cache_map
 #pragma unroll
         for (int c = 0; c < BV / 8; ++c) tmem_ld_x8(tmem_addr(tbase, 32 * warp, j * BT + 8 * c), r[c]);
         tmem_ld_wait();
-        const int pp = j * 128 + tid;
-        if (pp < D && !dead && it < mute_from) {
-          const int dest = pp / U, pl = pp % U;
+        // This lane holds one unit's row (all batch columns); the owner wants rows of one batch
+        // column over consecutive units. Four neighbouring lanes transpose 4 x 4 blocks with
+        // shuffles, after which lane i of the quad holds batch columns 8c + i and 8c + 4 + i of the
+        // quad's four units: two 16-byte packets per 8 columns.
+        const int qi = lane & 3;
+#pragma unroll
+        for (int c = 0; c < BV / 8; ++c) {
+#pragma unroll
+          for (int h = 0; h < 8; h += 4) {
+            uint32_t a = (qi & 1) ? r[c][h + 0] : r[c][h + 1], b = (qi & 1) ? r[c][h + 2] : r[c][h + 3];
+            a = __shfl_xor_sync(0xffffffffu, a, 1);
+            b = __shfl_xor_sync(0xffffffffu, b, 1);
+            if (qi & 1) { r[c][h + 0] = a; r[c][h + 2] = b; } else { r[c][h + 1] = a; r[c][h + 3] = b; }
+            a = (qi & 2) ? r[c][h + 0] : r[c][h + 2];
+            b = (qi & 2) ? r[c][h + 1] : r[c][h + 3];
+            a = __shfl_xor_sync(0xffffffffu, a, 2);
+            b = __shfl_xor_sync(0xffffffffu, b, 2);
+            if (qi & 2) { r[c][h + 0] = a; r[c][h + 1] = b; } else { r[c][h + 2] = a; r[c][h + 3] = b; }
+          }
+        }
+        const int pp0 = j * 128 + (tid & ~3);  // first unit of the quad
+        if (pp0 < D && !dead && it < mute_from) {
+          const int dest = pp0 / U, pl0 = pp0 % U;
           if (!xg) {
-            const uint32_t ra = map_to_cta(part_base + pl * BP * 4, dest);
+            const uint32_t ra = map_to_cta(part_base + pl0 * 4, dest);
             const uint32_t rb = map_to_cta(bar_local, dest);
 #pragma unroll
             for (int c = 0; c < BV / 8; ++c)
 #pragma unroll
-              for (int q = 0; q < 8; q += 4)
-                if (8 * c + q < bvq) st_async_v4_b32(ra + (8 * c + q) * 4, r[c][q], r[c][q + 1], r[c][q + 2], r[c][q + 3], rb);
+              for (int h = 0; h < 8; h += 4) {
+                const int bcol = 8 * c + h + qi;
+                if (bcol < bv) st_async_v4_b32(ra + bcol * U * 4, r[c][h], r[c][h + 1], r[c][h + 2], r[c][h + 3], rb);
+              }
           } else {
-            uint8_t* dst = xg_p + ((static_cast<size_t>(nb) * C + dest) * C + rank) * (U * BP * 4) + pl * BP * 4;
+            uint8_t* dst = xg_p + ((static_cast<size_t>(nb) * C + dest) * C + rank) * (BV * U * 4) + pl0 * 4;
 #pragma unroll
             for (int c = 0; c < BV / 8; ++c)
 #pragma unroll
-              for (int q = 0; q < 8; q += 4)
-                if (8 * c + q < bvq)
-                  *reinterpret_cast<uint4*>(dst + (8 * c + q) * 4) = make_uint4(r[c][q], r[c][q + 1], r[c][q + 2], r[c][q + 3]);
+              for (int h = 0; h < 8; h += 4) {
+                const int bcol = 8 * c + h + qi;
+                if (bcol < bv)
+                  *reinterpret_cast<uint4*>(dst + bcol * U * 4) = make_uint4(r[c][h], r[c][h + 1], r[c][h + 2], r[c][h + 3]);
+              }
           }
         }
       }
@@ -481,7 +508,7 @@ int launch_bwd(const BwdParams& p, const float* cache, const float* history, con
                const float* d_history, cudaStream_t stream) {
   using Cfg = BwdCfg<CELL, BV, U, WX_BF16>;
   using CT = typename Cfg::CT;
-  const int part_bytes = p.C * U * (BV + 4) * 4;
+  const int part_bytes = p.C * BV * U * 4;
   const int part_bufs = p.xg_data != nullptr ? 1 : 2;
   // the ring of TMA stages doubles as the staging area of the prologue's R load (16 rows of D bf16)
   const int ring_bytes = kStages * Cfg::STAGE_BYTES > 16 * p.D * 2 ? kStages * Cfg::STAGE_BYTES : 16 * p.D * 2;
