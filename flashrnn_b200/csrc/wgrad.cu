@@ -26,6 +26,7 @@ struct WgradParams {
   int NP;       // p columns per tile
   int ksplit;
   int chunks_per_split;
+  int pack;     // heads that share one 64-wide TMA box (narrow heads, D = 16 or 32), else 1
 };
 
 // Both operands are MN-major (the contraction index is the slow one in memory). Un-swizzled
@@ -157,11 +158,15 @@ wgrad_tma_kernel(const WgradParams p, const __grid_constant__ CUtensorMap dgr_ma
   __shared__ uint32_t s_tmem_base;
   const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
   const int D = p.D, T = p.T, GR = p.GR, NP = p.NP;
-  const int npt = D / NP;
+  const int npt = p.pack > 1 ? 1 : D / NP;
   const int mtile = blockIdx.x / npt, ptile = blockIdx.x % npt;
   const int n = blockIdx.y, split = blockIdx.z;
   const int m0 = mtile * 128, p0 = ptile * NP;
   const int M = GR * D;
+  // Narrow heads (pack > 1): one box spans `pack` neighbouring heads of one gate, so the 128 x 64
+  // tile holds pack x pack head blocks per gate of which only the diagonal ones are kept;
+  // blockIdx.x = gate pair, blockIdx.y = head group.
+  const int pack = p.pack;
   const int cpb = (T + kKC - 1) / kKC;  // chunks per batch row
   const int total_chunks = p.B * cpb;
   const int c_begin = split * p.chunks_per_split;
@@ -207,11 +212,17 @@ wgrad_tma_kernel(const WgradParams p, const __grid_constant__ CUtensorMap dgr_ma
         const uint32_t bar = smem_u32(&s_full[s]);
         const uint32_t sa = base + s * stage_bytes, sb = sa + 16384u;
         mbar_arrive_expect_tx(bar, stage_bytes);
-        for (int h = 0; h < 2; ++h) {
-          const int m = m0 + 64 * h;
-          tma_load_5d(sa + h * 8192u, &dgr_map, bar, m % D, n, m / D, t0, b);
+        if (pack == 1) {
+          for (int h = 0; h < 2; ++h) {
+            const int m = m0 + 64 * h;
+            tma_load_5d(sa + h * 8192u, &dgr_map, bar, m % D, n, m / D, t0, b);
+          }
+          for (int j = 0; j < NP / 64; ++j) tma_load_4d(sb + j * 8192u, &hbf_map, bar, p0 + 64 * j, n, t0, b);
+        } else {
+          // maps flatten (head, unit): x = 64 * head group; gates past GR read as zeros
+          for (int h = 0; h < 2; ++h) tma_load_4d(sa + h * 8192u, &dgr_map, bar, 64 * n, 2 * mtile + h, t0, b);
+          tma_load_3d(sb, &hbf_map, bar, 64 * n, t0, b);
         }
-        for (int j = 0; j < NP / 64; ++j) tma_load_4d(sb + j * 8192u, &hbf_map, bar, p0 + 64 * j, n, t0, b);
       }
     }
   } else if (warp == 1) {
@@ -245,20 +256,43 @@ wgrad_tma_kernel(const WgradParams p, const __grid_constant__ CUtensorMap dgr_ma
       have = false;
     }
     tc_fence_after_sync();
-    float* dst = nullptr;
-    if (m < M) {
-      const int g = m / D, o = m % D;
-      dst = p.out + static_cast<size_t>(split) * GR * p.N * D * D + ((static_cast<size_t>(g) * p.N + n) * D + o) * D + p0;
-    }
-    for (int c8 = 0; c8 < NP; c8 += 8) {
-      uint32_t r[8] = {0u, 0u, 0u, 0u, 0u, 0u, 0u, 0u};
-      if (have) {
-        tmem_ld_x8(tmem_addr(tbase, 32 * q, c8), r);
-        tmem_ld_wait();
+    if (pack == 1) {
+      float* dst = nullptr;
+      if (m < M) {
+        const int g = m / D, o = m % D;
+        dst = p.out + static_cast<size_t>(split) * GR * p.N * D * D + ((static_cast<size_t>(g) * p.N + n) * D + o) * D + p0;
       }
-      if (dst != nullptr) {
-        *reinterpret_cast<float4*>(dst + c8) = make_float4(__uint_as_float(r[0]), __uint_as_float(r[1]), __uint_as_float(r[2]), __uint_as_float(r[3]));
-        *reinterpret_cast<float4*>(dst + c8 + 4) = make_float4(__uint_as_float(r[4]), __uint_as_float(r[5]), __uint_as_float(r[6]), __uint_as_float(r[7]));
+      for (int c8 = 0; c8 < NP; c8 += 8) {
+        uint32_t r[8] = {0u, 0u, 0u, 0u, 0u, 0u, 0u, 0u};
+        if (have) {
+          tmem_ld_x8(tmem_addr(tbase, 32 * q, c8), r);
+          tmem_ld_wait();
+        }
+        if (dst != nullptr) {
+          *reinterpret_cast<float4*>(dst + c8) = make_float4(__uint_as_float(r[0]), __uint_as_float(r[1]), __uint_as_float(r[2]), __uint_as_float(r[3]));
+          *reinterpret_cast<float4*>(dst + c8 + 4) = make_float4(__uint_as_float(r[4]), __uint_as_float(r[5]), __uint_as_float(r[6]), __uint_as_float(r[7]));
+        }
+      }
+    } else {
+      // row = (gate of the pair, head of the group, unit); keep the columns of the same head
+      const int row = 32 * q + lane;
+      const int g = 2 * mtile + row / 64, hh = (row % 64) / D, o = row % D;
+      const int head = n * pack + hh;
+      float* dst = nullptr;
+      if (g < GR && head < p.N)
+        dst = p.out + static_cast<size_t>(split) * GR * p.N * D * D + ((static_cast<size_t>(g) * p.N + head) * D + o) * D;
+      for (int h2 = 0; h2 < pack; ++h2) {      // the TMEM address of a load is warp-uniform
+        for (int c8 = 0; c8 < D; c8 += 8) {
+          uint32_t r[8] = {0u, 0u, 0u, 0u, 0u, 0u, 0u, 0u};
+          if (have) {
+            tmem_ld_x8(tmem_addr(tbase, 32 * q, h2 * D + c8), r);
+            tmem_ld_wait();
+          }
+          if (dst != nullptr && h2 == hh) {
+            *reinterpret_cast<float4*>(dst + c8) = make_float4(__uint_as_float(r[0]), __uint_as_float(r[1]), __uint_as_float(r[2]), __uint_as_float(r[3]));
+            *reinterpret_cast<float4*>(dst + c8 + 4) = make_float4(__uint_as_float(r[4]), __uint_as_float(r[5]), __uint_as_float(r[6]), __uint_as_float(r[7]));
+          }
+        }
       }
     }
   }
@@ -284,18 +318,22 @@ __global__ void reduce_parts_kernel(const float* __restrict__ parts, float* __re
 
 }  // namespace
 
-// The TMA kernel needs whole 64-element boxes along both output dimensions.
+// The TMA kernel needs whole 64-element boxes along both output dimensions; heads of 16 or 32
+// units are packed 4 or 2 to a box.
 static bool wgrad_uses_tma(int D, int np) { return D % 64 == 0 && np % 64 == 0; }
+static int wgrad_pack(int D) { return (D == 16 || D == 32) ? 64 / D : 1; }
 
 int wgrad_plan(int gr, int B, int T, int N, int D, int* np_out, int* ksplit_out, int* cps_out) {
   // column tiles: the fewest equal parts of D that are at most 256 wide and a multiple of 16
   if (D % 16 != 0) return -2;
   int npt = (D + 255) / 256;
   while (D % npt != 0 || (D / npt) % 16 != 0) ++npt;
-  const int np = D / npt;
-  const int mtiles = (gr * D + 127) / 128;
-  const long long tiles = static_cast<long long>(mtiles) * npt * N;
-  const long long chunks = wgrad_uses_tma(D, np)
+  const int pack = wgrad_pack(D);
+  const int np = pack > 1 ? 64 : D / npt;
+  const int mtiles = pack > 1 ? (gr + 1) / 2 : (gr * D + 127) / 128;
+  const long long tiles = pack > 1 ? static_cast<long long>(mtiles) * ((N + pack - 1) / pack)
+                                   : static_cast<long long>(mtiles) * npt * N;
+  const long long chunks = (pack > 1 || wgrad_uses_tma(D, np))
                                ? static_cast<long long>(B) * ((T + kKC - 1) / kKC)   // per batch row
                                : (static_cast<long long>(B) * T + kKC - 1) / kKC;
   long long ks = 148 / tiles;
@@ -321,10 +359,26 @@ int wgrad_launch(int gr, int gb, const __nv_bfloat16* dgr, const __nv_bfloat16* 
   p.err = err;
   p.B = B; p.T = T; p.N = N; p.D = D; p.GR = gr;
   p.NP = np; p.ksplit = ksplit; p.chunks_per_split = cps;
-  const int mtiles = (gr * D + 127) / 128;
-  dim3 grid(static_cast<unsigned>(mtiles * (D / np)), static_cast<unsigned>(N), static_cast<unsigned>(ksplit));
+  const int pack = wgrad_pack(D);
+  p.pack = pack;
+  const int mtiles = pack > 1 ? (gr + 1) / 2 : (gr * D + 127) / 128;
+  dim3 grid(static_cast<unsigned>(pack > 1 ? mtiles : mtiles * (D / np)),
+            static_cast<unsigned>(pack > 1 ? (N + pack - 1) / pack : N), static_cast<unsigned>(ksplit));
   cudaError_t e;
-  if (wgrad_uses_tma(D, np)) {
+  if (pack > 1) {
+    CUtensorMap dgr_map, hbf_map;
+    const uint64_t ddims[4] = {static_cast<uint64_t>(N) * D, static_cast<uint64_t>(gr), static_cast<uint64_t>(T),
+                               static_cast<uint64_t>(B)};
+    const uint32_t dbox[4] = {64u, 1u, static_cast<uint32_t>(kKC), 1u};
+    const uint64_t hdims[3] = {static_cast<uint64_t>(N) * D, static_cast<uint64_t>(T + 1), static_cast<uint64_t>(B)};
+    const uint32_t hbox[3] = {64u, static_cast<uint32_t>(kKC), 1u};
+    if (make_tensor_map(&dgr_map, dgr, 2, 4, ddims, dbox, true) != 0) return -4;
+    if (make_tensor_map(&hbf_map, hbf, 2, 3, hdims, hbox, true) != 0) return -4;
+    const int smem = kTmaStages * (16384 + 64 * 128) + 1024;
+    e = cudaFuncSetAttribute(wgrad_tma_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, smem);
+    if (e != cudaSuccess) return static_cast<int>(e);
+    wgrad_tma_kernel<<<grid, kTmaThreads, smem, s>>>(p, dgr_map, hbf_map);
+  } else if (wgrad_uses_tma(D, np)) {
     CUtensorMap dgr_map, hbf_map;
     const uint64_t ddims[5] = {static_cast<uint64_t>(D), static_cast<uint64_t>(N), static_cast<uint64_t>(gr),
                                static_cast<uint64_t>(T), static_cast<uint64_t>(B)};

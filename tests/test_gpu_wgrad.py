@@ -10,6 +10,7 @@ CASES = [
     ("lstm", 8, 96, 2, 64), ("lstm", 3, 70, 1, 128), ("lstm", 8, 256, 3, 256), ("lstm", 2, 65, 1, 384),
     ("lstm", 2, 33, 1, 512), ("elman", 5, 130, 2, 64), ("gru", 16, 80, 1, 128), ("lstm", 4, 1, 2, 64),
     ("lstm", 3, 40, 2, 48), ("gru", 2, 17, 3, 16), ("slstm", 16, 64, 4, 128),
+    ("lstm", 16, 200, 5, 32), ("elman", 3, 70, 7, 16), ("lstm", 16, 128, 48, 16),   # narrow heads packed 2 / 4 to a box
 ]
 
 
