@@ -91,16 +91,18 @@ def time_shape(cell: str, B: int, T: int, N: int, D: int, reps: int = 5, device:
     return out
 
 
-def row(cell, B, T, N, D, r) -> str:
+def row(cell, B, T, N, D, r, cudnn=None) -> str:
+    lib = "" if cudnn is None else f" {N} x {cudnn[1]:.1f} |"
     if not r["supported"]:
-        return f"| {cell} | {B} | {T} | {N} | {D} | not supported (R slice exceeds tensor memory) | | | | | |"
+        return f"| {cell} | {B} | {T} | {N} | {D} | not supported (R slice exceeds tensor memory) | | | | | |" + lib
     tot = r["fwd"] + r["bwd"] + r["wgrad"]
     return (f"| {cell} | {B} | {T} | {N} | {D} | {r['cluster']} / {r['ctas']} | {r['fwd']:.3f} | {r['bwd']:.3f} | "
-            f"{r['wgrad']:.3f} | {B * T / tot * 1e3 / 1e6:.2f} | {r['fwd'] * 1e3 / T:.2f} / {r['bwd'] * 1e3 / T:.2f} |")
+            f"{r['wgrad']:.3f} | {B * T / tot * 1e3 / 1e6:.2f} | {r['fwd'] * 1e3 / T:.2f} / {r['bwd'] * 1e3 / T:.2f} |" + lib)
 
 
 HEADER = ("| cell | B | T | N | D | cluster / CTAs | fwd ms | bwd ms | dR+db ms | fwd+bwd M(B*T)/s | µs/step fwd / bwd |\n"
           "|---|---|---|---|---|---|---|---|---|---|---|")
+HEADER_LIB = HEADER.replace("|\n", "| cuDNN layer fwd+bwd ms (heads x one layer) |\n", 1) + "---|"
 
 
 def main(argv) -> None:
@@ -115,9 +117,13 @@ def main(argv) -> None:
     for cell in ("lstm", "gru", "elman"):
         shapes += [(cell, 16, 1024, n, d) for d, n in HEAD_DIM_SWEEP]
     shapes += [("lstm", 32, 2048, 4, 128)]  # one GPU's shard of N32 D128 B256 T2048 split over 8 GPUs by heads and batch
-    print(HEADER)
+    from .cudnn_baseline import time_cudnn
+
+    print(HEADER_LIB)
     for s in shapes:
-        print(row(*s, time_shape(*s)), flush=True)
+        cell, B, T, N, D = s
+        lib = time_cudnn(cell, B, T, D) if cell in ("lstm", "gru", "elman") else None
+        print(row(*s, time_shape(*s), lib), flush=True)
 
 
 if __name__ == "__main__":

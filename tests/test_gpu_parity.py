@@ -134,3 +134,21 @@ def test_bf16_inputs_and_flashrnn_entry(cuda_device):
     assert torch.equal(h_a, h_b) and torch.equal(c_a, c_b)
     with pytest.raises(ValueError):
         flashrnn(wx, R, b, None, function="lstm", backend="cuda_fused")
+
+
+@pytest.mark.parametrize("cell", ["lstm", "elman"])
+def test_matches_cudnn_layer(cell, cuda_device):
+    """Single head against torch.nn.LSTM / RNN (cuDNN, fp32) fed with the same precomputed Wx."""
+    from flashrnn_b200 import flashrnn_torch
+    from flashrnn_b200.cudnn_baseline import torch_layer_from
+    from flashrnn_b200.workloads import make_inputs
+
+    B, T, D = 4, 12, 64
+    wx, R, b, initial = (t.to(cuda_device) for t in make_inputs(cell, B, T, 1, D, 61))
+    hist, carry = flashrnn_torch(wx, R, b, initial, cell=cell)
+    layer = torch_layer_from(R, b, cell)
+    h0 = initial[0, :, 0, 0].unsqueeze(0).contiguous()
+    state = (h0, initial[1, :, 0, 0].unsqueeze(0).contiguous()) if cell == "lstm" else h0
+    with torch.backends.cudnn.flags(enabled=True, allow_tf32=False):
+        out, _ = layer(wx[:, :, :, 0].reshape(B, T, -1), state)
+    assert (hist[0, :, :, 0] - out).abs().max().item() <= 2e-2   # bf16 R / h operands vs fp32 cuDNN
