@@ -1,6 +1,7 @@
 // extern "C" boundary of the library: shape planning, argument checks, kernel dispatch.
 #include "../../include/flashrnn_b200.h"
 
+#include <cstdlib>
 #include <mutex>
 
 #include "frnn_common.cuh"
@@ -105,9 +106,13 @@ extern "C" int frnn_b200_plan(int cell, int B, int T, int N, int D, frnn_b200_pl
   // gets its own SMs; beyond that 16-row tiles halve the number of groups.
   out->batch_tile = 8;
   if (B > 8 && static_cast<long long>(N) * ((B + 7) / 8) * out->cluster > sm_count()) out->batch_tile = 16;
+  if (const char* forced = std::getenv("FRNN_B200_BATCH_TILE")) {  // tuning / experiments
+    const int v = std::atoi(forced);
+    if (v == 8 || v == 16) out->batch_tile = v;
+  }
   out->n_btiles = (B + out->batch_tile - 1) / out->batch_tile;
   out->grid_ctas = N * out->n_btiles * out->cluster;
-  const int bt = 16;
+  const int bt = out->batch_tile < 16 ? 16 : out->batch_tile;
   const int rows = c.gr * out->unit;
   const int mt = (rows + 127) / 128;
   const int fwd_cols = ((mt * bt + 31) / 32 * 32) + mt * (D / 2);
@@ -117,7 +122,7 @@ extern "C" int frnn_b200_plan(int cell, int B, int T, int N, int D, frnn_b200_pl
   out->supported = (D % 16 == 0) && fwd_cols <= 512 && bwd_cols <= 512 && (out->exchange == 0 || out->unit == 32);
   if (out->exchange) {
     const int64_t groups = static_cast<int64_t>(N) * out->n_btiles;
-    const int64_t fwd_b = 2ll * 16 * D * 2;                                          // two parity operand buffers
+    const int64_t fwd_b = 2ll * bt * D * 2;                                          // two parity operand buffers
     const int64_t bwd_b = 2ll * out->cluster * out->cluster * 32 * out->batch_tile * 4;  // partial-dh blocks
     out->xchg_bytes = 4096 + groups * 512 + groups * (fwd_b > bwd_b ? fwd_b : bwd_b);
   }

@@ -20,7 +20,7 @@ namespace {
 
 constexpr int kEpiThreads = 128;
 constexpr int kBwdThreads = 192;
-constexpr int kStages = 4;
+constexpr int kStages = 4;  // upper bound of the TMA ring depth (Cfg::NST is the depth in use)
 
 template <int CELL, int BV, int U, bool WX_BF16>
 struct BwdCfg {
@@ -32,6 +32,8 @@ struct BwdCfg {
   static constexpr int GCL = CELL == kElman ? 0 : CT::GC;  // cached gates actually loaded
   static constexpr int STAGE_FLOATS = (GCL + 3 * CT::S) * BV * U;
   static constexpr int STAGE_BYTES = STAGE_FLOATS * 4;
+  // TMA ring depth: four stages unless a stage is so large (wide batch tiles, many states) that fewer fit
+  static constexpr int NST = STAGE_BYTES * 4 <= 98304 ? 4 : (STAGE_BYTES * 3 <= 122880 ? 3 : 2);
   static constexpr int DGBUF_BYTES = BT * ROWS * 2;
   static constexpr int DBUF_BYTES = BV * CT::GB * U * 4;
   static_assert(ROWS % 16 == 0, "K must be a multiple of 16");
@@ -99,7 +101,7 @@ frnn_bwd_kernel(const BwdParams p, const __grid_constant__ CUtensorMap cache_map
     mbar_init(smem_u32(&s_part_bar[1]), 1);
     mbar_init(smem_u32(&s_dg_bar), kEpiThreads);
     for (int j = 0; j < 8; ++j) mbar_init(smem_u32(&s_mma_bar[j]), 1);
-    for (int s = 0; s < kStages; ++s) {
+    for (int s = 0; s < Cfg::NST; ++s) {
       mbar_init(smem_u32(&s_full[s]), 1);
       mbar_init(smem_u32(&s_empty[s]), kEpiThreads);
     }
@@ -217,10 +219,10 @@ frnn_bwd_kernel(const BwdParams p, const __grid_constant__ CUtensorMap cache_map
       const uint32_t stage_tx = static_cast<uint32_t>(p.box_b) * U * 4u * (GCL + 3 * S);
       const int sbu = p.box_b * U;  // floats per state plane in a stage
       for (int it = 0; it < T; ++it) {
-        const int s = it % kStages;
+        const int s = it % Cfg::NST;
         const int t = T - 1 - it;
-        if (it >= kStages) {
-          if (!mbar_wait_bounded<false>(smem_u32(&s_empty[s]), ((it / kStages) - 1) & 1, limit, abort_flag)) {
+        if (it >= Cfg::NST) {
+          if (!mbar_wait_bounded<false>(smem_u32(&s_empty[s]), ((it / Cfg::NST) - 1) & 1, limit, abort_flag)) {
             report(p.err, kErrWaitEmpty, it);
             break;
           }
@@ -257,8 +259,8 @@ frnn_bwd_kernel(const BwdParams p, const __grid_constant__ CUtensorMap cache_map
         for (int j = 0; j < IPT; ++j) ds[q][j] = dcar[q][j];
       float cache[CT::GC][IPT], sn[S][IPT], sp[S][IPT];
       if (it < T) {
-        const int s = it % kStages;
-        if (!dead && !mbar_wait_bounded<false>(smem_u32(&s_full[s]), (it / kStages) & 1, limit, abort_flag)) {
+        const int s = it % Cfg::NST;
+        if (!dead && !mbar_wait_bounded<false>(smem_u32(&s_full[s]), (it / Cfg::NST) & 1, limit, abort_flag)) {
           report(p.err, kErrWaitWx, it);
           dead = true;
         }
@@ -511,7 +513,7 @@ int launch_bwd(const BwdParams& p, const float* cache, const float* history, con
   const int part_bytes = p.C * BV * U * 4;
   const int part_bufs = p.xg_data != nullptr ? 1 : 2;
   // the ring of TMA stages doubles as the staging area of the prologue's R load (16 rows of D bf16)
-  const int ring_bytes = kStages * Cfg::STAGE_BYTES > 16 * p.D * 2 ? kStages * Cfg::STAGE_BYTES : 16 * p.D * 2;
+  const int ring_bytes = Cfg::NST * Cfg::STAGE_BYTES > 16 * p.D * 2 ? Cfg::NST * Cfg::STAGE_BYTES : 16 * p.D * 2;
   const int smem = ((Cfg::DGBUF_BYTES + part_bufs * part_bytes + Cfg::DBUF_BYTES + 127) & ~127) + ring_bytes;
   const int MTB = (p.D + 127) / 128;
   if (((MTB * Cfg::BT + 31) / 32 * 32) + MTB * (Cfg::ROWS / 2) > 512) return -3;
