@@ -469,6 +469,13 @@ int launch_fwd(const FwdParams& p, const void* wx, cudaStream_t stream) {
   }
   cfg.attrs = attr;
   cfg.numAttrs = 1;
+  if (p.xg_data == nullptr && p.C > 1) {
+    // a cluster that cannot be placed (too many CTAs or too much shared memory per GPC) is reported, not launched
+    int max_clusters = 0;
+    e = cudaOccupancyMaxActiveClusters(&max_clusters, kern, &cfg);
+    if (e != cudaSuccess) return static_cast<int>(e);
+    if (max_clusters < 1) return -2;
+  }
   e = cudaLaunchKernelEx(&cfg, kern, p, map);
   return static_cast<int>(e);
 }

@@ -152,3 +152,51 @@ def test_matches_cudnn_layer(cell, cuda_device):
     with torch.backends.cudnn.flags(enabled=True, allow_tf32=False):
         out, _ = layer(wx[:, :, :, 0].reshape(B, T, -1), state)
     assert (hist[0, :, :, 0] - out).abs().max().item() <= 2e-2   # bf16 R / h operands vs fp32 cuDNN
+
+
+def test_bf16_stream_backward_matches_oracle_on_rounded_inputs(cuda_device):
+    """Wx given in bf16 (as config 2 prescribes): all gradients against the oracle run on the same rounded Wx."""
+    from flashrnn_b200 import flashrnn
+    from flashrnn_b200.workloads import make_inputs
+
+    cell, B, T, N, D = "lstm", 8, 40, 3, 256
+    wx, R, b, initial = make_inputs(cell, B, T, N, D, 81)
+    wx_r = wx.bfloat16().float()
+    d_history = torch.zeros((2, B, T, N, D))
+    d_history[0] = 1.0
+    ref_h, _, (r_dwx, r_dR, r_db, r_dinit) = port.forward_backward(wx_r, R, b, initial, cell, d_history,
+                                                                    torch.zeros((2, B, 1, N, D)))
+    leaves = [t.to(cuda_device).requires_grad_(True) for t in (wx.bfloat16(), R, b, initial)]
+    hist, _ = flashrnn(*leaves, function=cell, backend="b200", dtype="bfloat16")
+    hist[0].sum().backward()
+    assert leaves[0].grad.dtype == torch.bfloat16 and leaves[1].grad.dtype == torch.float32
+    log = []
+    _check("bf16", "history", hist, ref_h, log)
+    _check("bf16", "dwx", leaves[0].grad.float(), r_dwx, log)
+    _check("bf16", "dR", leaves[1].grad, r_dR, log)
+    _check("bf16", "db", leaves[2].grad, r_db, log)
+    _check("bf16", "d_initial", leaves[3].grad, r_dinit, log)
+
+
+def test_repeatable_views_and_read_only_inputs(cuda_device):
+    """Same call twice is bit-identical (no atomics anywhere); strided views are accepted; inputs are not written."""
+    from flashrnn_b200 import flashrnn_torch
+    from flashrnn_b200.workloads import make_inputs
+
+    cell, B, T, N, D = "slstm", 6, 21, 2, 64
+    wx, R, b, initial = (t.to(cuda_device) for t in make_inputs(cell, B, T, N, D, 82))
+    wx_view = wx.transpose(0, 1).contiguous().transpose(0, 1)          # same values, different strides
+    copies = [t.clone() for t in (wx_view, R, b, initial)]
+    outs = []
+    for _ in range(2):
+        leaves = [t.detach().requires_grad_(True) for t in (wx_view, R, b, initial)]
+        h, c = flashrnn_torch(*leaves, cell=cell)
+        (h.square().sum() + c.sum()).backward()
+        outs.append([h.detach(), c.detach()] + [t.grad for t in leaves])
+    for a, bb in zip(*outs):
+        assert torch.equal(a, bb)
+    assert not wx_view.is_contiguous()
+    for t, c in zip((wx_view, R, b, initial), copies):
+        assert torch.equal(t, c)
+    h_ref, _ = flashrnn_torch(wx, R, b, initial, cell=cell)
+    assert torch.equal(h_ref, outs[0][0])
