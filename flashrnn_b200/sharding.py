@@ -57,3 +57,44 @@ def allreduce_weight_grads(dR: torch.Tensor, db: torch.Tensor, axis: str, group=
         return
     dist.all_reduce(dR, group=group)
     dist.all_reduce(db, group=group)
+
+
+class _SumGradOverRanks(torch.autograd.Function):
+    """Identity in forward; all-reduce (sum) of the gradient in backward."""
+
+    @staticmethod
+    def forward(ctx, t, group):
+        ctx.group = group
+        return t.view_as(t)
+
+    @staticmethod
+    def backward(ctx, grad):
+        import torch.distributed as dist
+
+        grad = grad.contiguous()
+        if dist.is_initialized() and dist.get_world_size(ctx.group) > 1:
+            dist.all_reduce(grad, group=ctx.group)
+        return grad, None
+
+
+def flashrnn_sharded(Wx, R, b, states=None, function: str = "lstm", dtype: str = "bfloat16", axis: Optional[str] = None,
+                     group=None, zero_normalizer: Optional[bool] = None):
+    """Run this rank's shard of one logical ``flashrnn`` call (one process per GPU).
+
+    ``Wx`` / ``states`` are this rank's slice along ``axis`` ("batch" or "heads", see ``shard_inputs``).
+    Under batch sharding ``R`` and ``b`` are the full replicated weights and their gradients are
+    summed over the ranks during backward (one NCCL all-reduce each, no collective in the time loop);
+    under head sharding ``R`` and ``b`` are this rank's head slice and nothing is exchanged.
+    For sLSTM pass ``zero_normalizer = slstm_zero_normalizer(unsharded initial state)``.
+    Returns this rank's slice of ``(states[S,B,T,N,D], last[S,B,1,N,D])``.
+    """
+    from .functional import flashrnn
+
+    if axis is None:
+        raise ValueError("say along which axis this rank's tensors were sliced: 'batch' or 'heads'")
+    if axis == "batch":
+        R = _SumGradOverRanks.apply(R, group)
+        b = _SumGradOverRanks.apply(b, group)
+    elif axis != "heads":
+        raise ValueError("axis must be 'batch' or 'heads'")
+    return flashrnn(Wx, R, b, states, function=function, backend="b200", dtype=dtype, zero_normalizer=zero_normalizer)
