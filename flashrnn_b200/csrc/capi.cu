@@ -122,8 +122,8 @@ extern "C" int frnn_b200_plan(int cell, int B, int T, int N, int D, frnn_b200_pl
   out->supported = (D % 16 == 0) && fwd_cols <= 512 && bwd_cols <= 512 && (out->exchange == 0 || out->unit == 32);
   if (out->exchange) {
     const int64_t groups = static_cast<int64_t>(N) * out->n_btiles;
-    const int64_t fwd_b = 2ll * bt * D * 2;                                          // two parity operand buffers
-    const int64_t bwd_b = 2ll * out->cluster * out->cluster * 32 * out->batch_tile * 4;  // partial-dh blocks
+    const int64_t fwd_b = 4ll * bt * D * 2;                                          // four operand slots
+    const int64_t bwd_b = 2ll * out->cluster * out->cluster * 32 * out->batch_tile * 4;  // two slots of partial-dh blocks
     out->xchg_bytes = 4096 + groups * 512 + groups * (fwd_b > bwd_b ? fwd_b : bwd_b);
   }
   const int64_t btnd = static_cast<int64_t>(B) * T * N * D;
@@ -167,7 +167,8 @@ extern "C" int frnn_b200_forward(int cell, const void* wx, int wx_bf16, const vo
   if (plan.exchange) {
     if (!xchg) return -5;
     const size_t counters = static_cast<size_t>(N) * plan.n_btiles * 512;
-    const cudaError_t me = cudaMemsetAsync(xchg, 0, static_cast<size_t>(plan.xchg_bytes), static_cast<cudaStream_t>(stream));
+    // every exchange word starts as "not yet written" (all ones)
+    const cudaError_t me = cudaMemsetAsync(xchg, 0xff, static_cast<size_t>(plan.xchg_bytes), static_cast<cudaStream_t>(stream));
     if (me != cudaSuccess) return static_cast<int>(me);
     p.xg_counters = static_cast<uint32_t*>(xchg);
     p.xg_data = static_cast<uint8_t*>(xchg) + ((counters + 4095) & ~static_cast<size_t>(4095));
@@ -202,7 +203,7 @@ extern "C" int frnn_b200_backward(int cell, const float* cache, const float* his
   if (plan.exchange) {
     if (!xchg) return -5;
     const size_t counters = static_cast<size_t>(N) * plan.n_btiles * 512;
-    const cudaError_t me = cudaMemsetAsync(xchg, 0, static_cast<size_t>(plan.xchg_bytes), static_cast<cudaStream_t>(stream));
+    const cudaError_t me = cudaMemsetAsync(xchg, 0xff, static_cast<size_t>(plan.xchg_bytes), static_cast<cudaStream_t>(stream));
     if (me != cudaSuccess) return static_cast<int>(me);
     p.xg_counters = static_cast<uint32_t*>(xchg);
     p.xg_data = static_cast<uint8_t*>(xchg) + ((counters + 4095) & ~static_cast<size_t>(4095));

@@ -82,14 +82,16 @@ frnn_bwd_kernel(const BwdParams p, const __grid_constant__ CUtensorMap cache_map
   // shared memory carve-up
   const int part_bytes = C * BV * U * 4;  // one parity buffer: [source CTA][batch][unit] fp32
   const bool xg = p.xg_data != nullptr;   // exchange partial dh through global memory instead of DSMEM
-  const int part_bufs = xg ? 1 : 2;       // the global copy is double-buffered, its staging area is not
+  const int part_bufs = xg ? 0 : 2;       // the global exchange is summed straight from global memory
   uint8_t* const dgbuf = smem;
   float* const part = reinterpret_cast<float*>(smem + Cfg::DGBUF_BYTES);
   float* const dbuf = reinterpret_cast<float*>(smem + Cfg::DGBUF_BYTES + part_bufs * part_bytes);
   uint8_t* const stages = smem + ((Cfg::DGBUF_BYTES + part_bufs * part_bytes + Cfg::DBUF_BYTES + 127) & ~127);
-  // global layout per group: [parity][dest CTA][source CTA][unit][padded batch] fp32
+  // Global layout per group: [slot][dest CTA][source CTA][batch][unit] fp32, two slots; the
+  // partial sums consumed in iteration i travel through slot i % 2. There is no separate flag:
+  // the lowest mantissa bit of every word is replaced by a phase bit that flips each time the slot
+  // is reused (the buffer starts as all ones), and the receiver polls the words themselves.
   uint8_t* const xg_p = xg ? p.xg_data + static_cast<size_t>(gid) * 2 * C * part_bytes : nullptr;
-  uint32_t* const xg_cnt = xg ? p.xg_counters + static_cast<size_t>(gid) * 128 : nullptr;
   const volatile int* abort_flag = p.err;
   const uint64_t limit = p.wait_limit_ns;
   // test hook: with err[4] = 1 no CTA scatters partial dh from iteration err[5] on, so the next wait runs out
@@ -245,7 +247,7 @@ frnn_bwd_kernel(const BwdParams p, const __grid_constant__ CUtensorMap cache_map
     const int sbu = p.box_b * U;
     const uint32_t dg_off = kmajor_offset(BT, ib, ul);
     long long pc[5] = {0, 0, 0, 0, 0};
-    long long pc5 = 0, pc6 = 0;
+    long long pc5 = 0, pc6 = 0, pc7 = 0, pc8 = 0;
     // Once a wait has failed (`dead`) the warp keeps walking through the loop without waiting, so
     // that the warp-wide tcgen05.ld below is always executed by all of its lanes.
     bool dead = false;
@@ -290,25 +292,73 @@ frnn_bwd_kernel(const BwdParams p, const __grid_constant__ CUtensorMap cache_map
       if (it >= 1) {
         // partial dh for this step from every CTA of the cluster
         const int pb = it & 1;
-        if (xg && tid == 0 && !dead) {
-          // all CTAs of the group have scattered: fetch this CTA's block [source][unit][batch]
-          const uint32_t target = static_cast<uint32_t>(C) * static_cast<uint32_t>(((it - 1) >> 1) + 1);
-          if (counter_wait_bounded(xg_cnt + pb * 64, target, limit, abort_flag)) {
-            fence_proxy_async_global();
-            mbar_arrive_expect_tx(smem_u32(&s_part_bar[pb]), static_cast<uint32_t>(part_bytes));
-            bulk_load_1d(smem_u32(part), xg_p + (static_cast<size_t>(pb) * C + rank) * part_bytes,
-                         static_cast<uint32_t>(part_bytes), smem_u32(&s_part_bar[pb]));
-          } else {
-            report(p.err, kErrWaitPart, it);
+        if (xg) {
+          // Global exchange: this thread's IPT floats of every source CTA's block are polled straight
+          // into registers until each word shows this iteration's phase bit, then added in source
+          // order. A slot is not rewritten before this CTA has scattered again, which it does only
+          // after this poll, so a word with the right phase can only be this iteration's.
+          constexpr int SB = IPT == 2 ? 24 : 12;  // sources per batch
+          const uint32_t phase = static_cast<uint32_t>(((it - 1) >> 1) & 1);
+          const uint8_t* src0 = xg_p + ((static_cast<size_t>(it & 1) * C + rank) * C) * (BV * U * 4) + (ib * U + ul) * 4;
+          for (int s0 = 0; s0 < C; s0 += SB) {
+            uint32_t v[SB][IPT];
+            uint32_t pend = 0;
+            if (active && !dead) {
+#pragma unroll
+              for (int k = 0; k < SB; ++k)
+                if (s0 + k < C) pend |= 1u << k;
+            }
+            uint64_t t0 = 0;
+            while (pend != 0u) {
+#pragma unroll
+              for (int k = 0; k < SB; ++k) {
+                if ((pend >> k) & 1u) {
+                  const uint8_t* a = src0 + static_cast<size_t>(s0 + k) * (BV * U * 4);
+                  if constexpr (IPT == 4) {
+                    const uint4 w = ld_relaxed_gpu_v4(a);
+                    v[k][0] = w.x; v[k][1] = w.y; v[k][2] = w.z; v[k][3] = w.w;
+                  } else {
+                    const uint2 w = ld_relaxed_gpu_v2(a);
+                    v[k][0] = w.x; v[k][1] = w.y;
+                  }
+                }
+              }
+#pragma unroll
+              for (int k = 0; k < SB; ++k) {
+                if ((pend >> k) & 1u) {
+                  bool ok = true;
+#pragma unroll
+                  for (int j = 0; j < IPT; ++j) ok = ok && (v[k][j] & 1u) == phase;
+                  if (ok) pend &= ~(1u << k);
+                }
+              }
+              if (pend != 0u) {
+                const uint64_t now = global_timer_ns();
+                if (t0 == 0) t0 = now;
+                if (*abort_flag != 0 || now - t0 > limit) {
+                  report(p.err, kErrWaitPart, it);
+                  dead = true;
+                  break;
+                }
+              }
+            }
+            if (active && !dead) {
+#pragma unroll
+              for (int k = 0; k < SB; ++k)
+                if (s0 + k < C) {
+#pragma unroll
+                  for (int j = 0; j < IPT; ++j) ds[0][j] += __uint_as_float(v[k][j] & ~1u);
+                }
+            }
           }
-        }
-        if (!dead && !mbar_wait_bounded<true, true>(smem_u32(&s_part_bar[pb]), ((it - 1) >> 1) & 1, limit, abort_flag)) {
+          if (prof) pc5 += clock64() - c1;
+        } else if (!dead && !mbar_wait_bounded<true, true>(smem_u32(&s_part_bar[pb]), ((it - 1) >> 1) & 1, limit, abort_flag)) {
           report(p.err, kErrWaitPart, it);
           dead = true;
         }
-        if (prof) pc5 += clock64() - c1;
-        if (active) {
-          const float* pbuf = part + static_cast<size_t>(xg ? 0 : pb) * (part_bytes / 4) + ib * U + ul;
+        if (prof && !xg) pc5 += clock64() - c1;
+        if (active && !xg) {
+          const float* pbuf = part + static_cast<size_t>(pb) * (part_bytes / 4) + ib * U + ul;
           // fixed summation order; the loads of eight sources are issued together before the adds
           for (int s0 = 0; s0 < C; s0 += 8) {
             float v[8][IPT];
@@ -451,26 +501,21 @@ frnn_bwd_kernel(const BwdParams p, const __grid_constant__ CUtensorMap cache_map
                 if (bcol < bv) st_async_v4_b32(ra + bcol * U * 4, r[c][h], r[c][h + 1], r[c][h + 2], r[c][h + 3], rb);
               }
           } else {
-            uint8_t* dst = xg_p + ((static_cast<size_t>(nb) * C + dest) * C + rank) * (BV * U * 4) + pl0 * 4;
+            uint8_t* dst = xg_p + ((static_cast<size_t>((it + 1) & 1) * C + dest) * C + rank) * (BV * U * 4) + pl0 * 4;
+            const uint32_t ph = static_cast<uint32_t>((it >> 1) & 1);  // phase of iteration it + 1
 #pragma unroll
             for (int c = 0; c < BV / 8; ++c)
 #pragma unroll
               for (int h = 0; h < 8; h += 4) {
                 const int bcol = 8 * c + h + qi;
                 if (bcol < bv)
-                  *reinterpret_cast<uint4*>(dst + bcol * U * 4) = make_uint4(r[c][h], r[c][h + 1], r[c][h + 2], r[c][h + 3]);
+                  st_relaxed_gpu_v4(dst + bcol * U * 4, make_uint4((r[c][h] & ~1u) | ph, (r[c][h + 1] & ~1u) | ph,
+                                                                   (r[c][h + 2] & ~1u) | ph, (r[c][h + 3] & ~1u) | ph));
               }
           }
         }
       }
-      if (xg) {
-        fence_proxy_async_global();
-        asm volatile("bar.sync 2, 128;" ::: "memory");
-        if (tid == 0 && !dead && it < mute_from) {
-          __threadfence();
-          red_release_gpu_add_u32(xg_cnt + nb * 64, 1u);
-        }
-      }
+      if (prof) pc7 += clock64() - c4;
       tc_fence_before_sync();
       if (prof) {
         pc[0] += c1 - c0; pc[1] += c2 - c1; pc[2] += c3 - c2; pc[3] += c4 - c3; pc[4] += clock64() - c4;
@@ -481,6 +526,8 @@ frnn_bwd_kernel(const BwdParams p, const __grid_constant__ CUtensorMap cache_map
       for (int q = 0; q < 5; ++q) p.err[8 + q] = static_cast<int>(pc[q]);
       p.err[13] = static_cast<int>(pc5);
       p.err[14] = static_cast<int>(pc6);
+      p.err[18] = static_cast<int>(pc7);  // scatter without the refill
+      p.err[19] = static_cast<int>(pc8);  // fence before the poll
     }
   }
 
@@ -511,7 +558,7 @@ int launch_bwd(const BwdParams& p, const float* cache, const float* history, con
   using Cfg = BwdCfg<CELL, BV, U, WX_BF16>;
   using CT = typename Cfg::CT;
   const int part_bytes = p.C * BV * U * 4;
-  const int part_bufs = p.xg_data != nullptr ? 1 : 2;
+  const int part_bufs = p.xg_data != nullptr ? 0 : 2;
   // the ring of TMA stages doubles as the staging area of the prologue's R load (16 rows of D bf16)
   const int ring_bytes = Cfg::NST * Cfg::STAGE_BYTES > 16 * p.D * 2 ? Cfg::NST * Cfg::STAGE_BYTES : 16 * p.D * 2;
   const int smem = ((Cfg::DGBUF_BYTES + part_bufs * part_bytes + Cfg::DBUF_BYTES + 127) & ~127) + ring_bytes;

@@ -77,8 +77,8 @@ frnn_fwd_kernel(const FwdParams p, const __grid_constant__ CUtensorMap wx_map) {
   const volatile int* abort_flag = p.err;
   const uint64_t limit = p.wait_limit_ns;
   const bool xg = p.xg_data != nullptr;  // exchange h through global memory instead of DSMEM
-  uint8_t* const xg_h = xg ? p.xg_data + static_cast<size_t>(gid) * 2 * hbuf_bytes : nullptr;
-  uint32_t* const xg_cnt = xg ? p.xg_counters + static_cast<size_t>(gid) * 128 : nullptr;
+  // four operand slots per group in global memory: h_t goes to slot (t + 1) % 4, see the epilogue
+  uint8_t* const xg_h = xg ? p.xg_data + static_cast<size_t>(gid) * 4 * hbuf_bytes : nullptr;
   // test hook: with err[4] = 1 no CTA publishes h from step err[5] on, so the next operand wait runs out
   const int mute_from = p.err[4] != 0 ? p.err[5] : 0x7fffffff;
   const bool prof = p.err[3] != 0 && blockIdx.x == 0 && lane == 0 && (warp == 0 || warp == 4);
@@ -88,8 +88,10 @@ frnn_fwd_kernel(const FwdParams p, const __grid_constant__ CUtensorMap wx_map) {
 
   // ---------------- prologue ----------------
   if (tid == 0) {
-    mbar_init(smem_u32(&s_hbar[0]), 1);
-    mbar_init(smem_u32(&s_hbar[1]), 1);
+    // cluster exchange: one arming arrival + the bytes pushed by the peers; global exchange: the
+    // epilogue threads copy the operand in and arrive themselves
+    mbar_init(smem_u32(&s_hbar[0]), xg ? kEpiThreads : 1);
+    mbar_init(smem_u32(&s_hbar[1]), xg ? kEpiThreads : 1);
     mbar_init(smem_u32(&s_mma_bar), 1);
     for (int s = 0; s < kWxStages; ++s) {
       mbar_init(smem_u32(&s_wx_full[s]), 1);
@@ -180,23 +182,8 @@ frnn_fwd_kernel(const FwdParams p, const __grid_constant__ CUtensorMap wx_map) {
       for (int t = 0; t < T; ++t) {
         const int pb = t & 1;
         const long long m0 = prof ? clock64() : 0;
-        if (t >= 1 && !xg) {
+        if (t >= 1) {
           if (!mbar_wait_bounded<true, true>(smem_u32(&s_hbar[pb]), ((t - 1) >> 1) & 1, limit, abort_flag)) {
-            report(p.err, kErrWaitH, t);
-            break;
-          }
-        } else if (t >= 1) {
-          // every CTA of the group has published h_{t-1}: fetch the whole operand with one bulk copy
-          const uint32_t target = static_cast<uint32_t>(C) * static_cast<uint32_t>(((t - 1) >> 1) + 1);
-          if (!counter_wait_bounded(xg_cnt + pb * 64, target, limit, abort_flag)) {
-            report(p.err, kErrWaitH, t);
-            break;
-          }
-          fence_proxy_async_global();
-          mbar_arrive_expect_tx(smem_u32(&s_hbar[pb]), static_cast<uint32_t>(hbuf_bytes));
-          bulk_load_1d(smem_u32(hbuf + pb * hbuf_bytes), xg_h + static_cast<size_t>(pb) * hbuf_bytes,
-                       static_cast<uint32_t>(hbuf_bytes), smem_u32(&s_hbar[pb]));
-          if (!mbar_wait_bounded<false, true>(smem_u32(&s_hbar[pb]), ((t - 1) >> 1) & 1, limit, abort_flag)) {
             report(p.err, kErrWaitH, t);
             break;
           }
@@ -376,21 +363,65 @@ frnn_fwd_kernel(const FwdParams p, const __grid_constant__ CUtensorMap wx_map) {
             }
           }
         } else {
-          // one lane of each packet group stores the packet into the group's global operand
-          // buffer; after all epilogue threads are through, one thread releases the arrival count
+          // One lane of each packet group stores the packet into slot (t + 1) % 4 of the group's
+          // global operand buffer; there is no separate flag: receivers poll the data words, which
+          // differ from the all-ones fill once written (two bf16 NaNs with all-ones payload never
+          // come out of the rounding). The same lane then refills its packet of slot (t + 3) % 4,
+          // which held h_{t-2}: every CTA has consumed that (it published h_{t-1} afterwards, and
+          // this CTA has consumed all of h_{t-1}). The fence at the end of the step orders the
+          // refill before this thread's next data store, so a receiver that has seen h_{t+1} of
+          // this packet position can no longer see h_{t-2} where it waits for h_{t+2}.
           if (active && publish && (lane & (LPP - 1)) == 0) {
-            *reinterpret_cast<uint4*>(xg_h + static_cast<size_t>((t + 1) & 1) * hbuf_bytes + (h_off & ~15u)) =
-                make_uint4(pk[0], pk[1], pk[2], pk[3]);
-            fence_proxy_async_global();
-          }
-          asm volatile("bar.sync 2, 128;" ::: "memory");
-          if (tid == 0 && publish) {
-            __threadfence();
-            red_release_gpu_add_u32(xg_cnt + ((t + 1) & 1) * 64, 1u);
+            const size_t at = h_off & ~15u;
+            st_relaxed_gpu_v4(xg_h + static_cast<size_t>((t + 1) & 3) * hbuf_bytes + at, make_uint4(pk[0], pk[1], pk[2], pk[3]));
+            st_relaxed_gpu_v4(xg_h + static_cast<size_t>((t + 3) & 3) * hbuf_bytes + at,
+                              make_uint4(kXgFill, kXgFill, kXgFill, kXgFill));
           }
         }
       }
       if (prof) { c6 = clock64(); *reinterpret_cast<volatile long long*>(&s_prof_clk[1]) = c6; }
+      if (xg && t + 1 < T) {
+        // Fetch the whole operand h_t of the group from slot (t + 1) % 4 into this CTA's operand
+        // buffer: thread `tid` owns the 16-byte packets tid, tid + 128, ... of the active batch
+        // rows, polls them until none shows the fill pattern and copies them to shared memory.
+        constexpr int KG_STEP = kEpiThreads / BV;            // k-groups between two packets of a thread
+        constexpr int XCH = (768 / 8 + KG_STEP - 1) / KG_STEP;  // packets per thread at the widest head
+        const int row = tid % BV, kg0 = tid / BV;
+        const uint8_t* src = xg_h + static_cast<size_t>((t + 1) & 3) * hbuf_bytes + kg0 * (BT * 16) + row * 16;
+        uint8_t* dst = hbuf + ((t + 1) & 1) * hbuf_bytes + kg0 * (BT * 16) + row * 16;
+        uint32_t pend = 0;
+        if (row < bv && !dead) {
+#pragma unroll
+          for (int j = 0; j < XCH; ++j)
+            if (kg0 + j * KG_STEP < D / 8) pend |= 1u << j;
+        }
+        uint64_t t0 = 0;
+        while (pend != 0u) {
+          uint4 v[XCH];
+#pragma unroll
+          for (int j = 0; j < XCH; ++j)
+            if ((pend >> j) & 1u) v[j] = ld_relaxed_gpu_v4(src + j * (KG_STEP * BT * 16));
+#pragma unroll
+          for (int j = 0; j < XCH; ++j) {
+            if (((pend >> j) & 1u) && xg_arrived(v[j])) {
+              *reinterpret_cast<uint4*>(dst + j * (KG_STEP * BT * 16)) = v[j];
+              pend &= ~(1u << j);
+            }
+          }
+          if (pend != 0u) {
+            const uint64_t now = global_timer_ns();
+            if (t0 == 0) t0 = now;
+            if (*abort_flag != 0 || now - t0 > limit) {
+              report(p.err, kErrWaitH, t + 1);
+              dead = true;
+              break;
+            }
+          }
+        }
+        fence_proxy_async_smem();
+        mbar_arrive(smem_u32(&s_hbar[(t + 1) & 1]));
+        fence_acq_rel_gpu();  // orders this step's refill and observations before the next step's (see above)
+      }
       if (active) {
 #pragma unroll
         for (int q = 0; q < CT::S; ++q) st_f32_vec<IPT>(hist + q * sBTND + t * ND, st[q]);

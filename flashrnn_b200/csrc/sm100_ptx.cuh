@@ -423,4 +423,33 @@ __device__ __forceinline__ bool counter_wait_bounded(const uint32_t* counter, ui
   }
 }
 
+// Relaxed (strong, gpu scope) 16-byte global accesses of the flag-in-data exchange: the receiver
+// polls the data words themselves, every 32-bit word carries its own "arrived" information (it
+// differs from the all-ones fill), so nothing is assumed about the atomicity of the whole vector.
+__device__ __forceinline__ uint4 ld_relaxed_gpu_v4(const void* p) {
+  uint4 v;
+  asm volatile("ld.relaxed.gpu.global.v4.u32 {%0, %1, %2, %3}, [%4];"
+               : "=r"(v.x), "=r"(v.y), "=r"(v.z), "=r"(v.w)
+               : "l"(p)
+               : "memory");
+  return v;
+}
+__device__ __forceinline__ void st_relaxed_gpu_v4(void* p, uint4 v) {
+  asm volatile("st.relaxed.gpu.global.v4.u32 [%0], {%1, %2, %3, %4};" ::"l"(p), "r"(v.x), "r"(v.y), "r"(v.z), "r"(v.w)
+               : "memory");
+}
+__device__ __forceinline__ void fence_acq_rel_gpu() { asm volatile("fence.acq_rel.gpu;" ::: "memory"); }
+constexpr uint32_t kXgFill = 0xffffffffu;  // "not yet written" pattern of an exchange word
+__device__ __forceinline__ bool xg_arrived(const uint4& v) {
+  return v.x != kXgFill && v.y != kXgFill && v.z != kXgFill && v.w != kXgFill;
+}
+__device__ __forceinline__ uint2 ld_relaxed_gpu_v2(const void* p) {
+  uint2 v;
+  asm volatile("ld.relaxed.gpu.global.v2.u32 {%0, %1}, [%2];" : "=r"(v.x), "=r"(v.y) : "l"(p) : "memory");
+  return v;
+}
+// A value that is about to be published must not look like the fill pattern: the one NaN encoding
+// that does is replaced by another NaN.
+__device__ __forceinline__ uint32_t xg_clean(uint32_t w) { return w == kXgFill ? 0x7fffffffu : w; }
+
 }  // namespace frnn

@@ -19,7 +19,9 @@ def _buffers(_lib, cell, B, T, N, D, dev):
              cache=torch.zeros(plan.cache_bytes // 4, device=dev),
              hbf=torch.zeros(plan.hbf_bytes // 2, dtype=torch.bfloat16, device=dev),
              dwx=torch.zeros((B, T, gw, N, D), device=dev), dgr=torch.zeros(plan.dgr_bytes // 2, dtype=torch.bfloat16, device=dev),
-             dinit=torch.zeros((S, B, 1, N, D), device=dev), dbp=torch.zeros(plan.dbpart_bytes // 4, device=dev))
+             dinit=torch.zeros((S, B, 1, N, D), device=dev), dbp=torch.zeros(plan.dbpart_bytes // 4, device=dev),
+             xchg=torch.zeros(max(plan.xchg_bytes, 16), dtype=torch.uint8, device=dev))
+    t["xchg_ptr"] = t["xchg"].data_ptr() if plan.exchange else None
     t["dH"] = torch.ones_like(t["hist"])
     t["dC"] = torch.zeros_like(t["carry"])
     return t
@@ -28,22 +30,24 @@ def _buffers(_lib, cell, B, T, N, D, dev):
 def _forward(lib, _lib, cell, B, T, N, D, t, err, limit_ms):
     return lib.frnn_b200_forward(_lib.CELLS[cell], t["wx"].data_ptr(), 0, t["R"].data_ptr(), t["b"].data_ptr(),
                                  t["init"].data_ptr(), t["hist"].data_ptr(), t["carry"].data_ptr(), t["cache"].data_ptr(),
-                                 t["hbf"].data_ptr(), None, B, T, N, D, 0, limit_ms, err.data_ptr(),
+                                 t["hbf"].data_ptr(), t["xchg_ptr"], B, T, N, D, 0, limit_ms, err.data_ptr(),
                                  torch.cuda.current_stream().cuda_stream)
 
 
 def _backward(lib, _lib, cell, B, T, N, D, t, err, limit_ms):
     return lib.frnn_b200_backward(_lib.CELLS[cell], t["cache"].data_ptr(), t["hist"].data_ptr(), t["init"].data_ptr(),
                                   t["R"].data_ptr(), t["dH"].data_ptr(), t["dC"].data_ptr(), t["dwx"].data_ptr(), 0,
-                                  t["dgr"].data_ptr(), t["dinit"].data_ptr(), t["dbp"].data_ptr(), None, B, T, N, D, 0,
+                                  t["dgr"].data_ptr(), t["dinit"].data_ptr(), t["dbp"].data_ptr(), t["xchg_ptr"], B, T, N, D, 0,
                                   limit_ms, err.data_ptr(), torch.cuda.current_stream().cuda_stream)
 
 
-def test_stalled_exchange_is_reported_and_context_survives(cuda_device):
+# one shape that exchanges inside a thread-block cluster, one that exchanges through global memory
+@pytest.mark.parametrize("shape", [("lstm", 8, 24, 2, 128), ("lstm", 4, 12, 1, 576)], ids=["cluster", "global"])
+def test_stalled_exchange_is_reported_and_context_survives(shape, cuda_device):
     from flashrnn_b200 import _lib
 
     lib = _lib.load()
-    cell, B, T, N, D = "lstm", 8, 24, 2, 128
+    cell, B, T, N, D = shape
     t = _buffers(_lib, cell, B, T, N, D, cuda_device)
     err = torch.zeros(32, dtype=torch.int32, device=cuda_device)
     assert _forward(lib, _lib, cell, B, T, N, D, t, err, 0) == 0
