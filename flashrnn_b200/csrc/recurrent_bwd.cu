@@ -48,7 +48,7 @@ __device__ __forceinline__ void report(int* err, int code, int detail) {
   __threadfence();
 }
 
-template <int CELL, int BV, int U, bool WX_BF16>
+template <int CELL, int BV, int U, bool WX_BF16, bool XG>
 __global__ void __launch_bounds__(kBwdThreads, 1)
 frnn_bwd_kernel(const BwdParams p, const __grid_constant__ CUtensorMap cache_map,
                 const __grid_constant__ CUtensorMap hist_map, const __grid_constant__ CUtensorMap init_map,
@@ -81,7 +81,7 @@ frnn_bwd_kernel(const BwdParams p, const __grid_constant__ CUtensorMap cache_map
 
   // shared memory carve-up
   const int part_bytes = C * BV * U * 4;  // one parity buffer: [source CTA][batch][unit] fp32
-  const bool xg = p.xg_data != nullptr;   // exchange partial dh through global memory instead of DSMEM
+  constexpr bool xg = XG;   // exchange partial dh through global memory instead of DSMEM
   const int part_bufs = xg ? 0 : 2;       // the global exchange is summed straight from global memory
   uint8_t* const dgbuf = smem;
   float* const part = reinterpret_cast<float*>(smem + Cfg::DGBUF_BYTES);
@@ -552,13 +552,13 @@ frnn_bwd_kernel(const BwdParams p, const __grid_constant__ CUtensorMap cache_map
   if (warp == 4) tmem_dealloc(tbase, tmem_cols);
 }
 
-template <int CELL, int BV, int U, bool WX_BF16>
+template <int CELL, int BV, int U, bool WX_BF16, bool XG>
 int launch_bwd(const BwdParams& p, const float* cache, const float* history, const float* initial,
                const float* d_history, cudaStream_t stream) {
   using Cfg = BwdCfg<CELL, BV, U, WX_BF16>;
   using CT = typename Cfg::CT;
   const int part_bytes = p.C * BV * U * 4;
-  const int part_bufs = p.xg_data != nullptr ? 0 : 2;
+  const int part_bufs = XG ? 0 : 2;
   // the ring of TMA stages doubles as the staging area of the prologue's R load (16 rows of D bf16)
   const int ring_bytes = Cfg::NST * Cfg::STAGE_BYTES > 16 * p.D * 2 ? Cfg::NST * Cfg::STAGE_BYTES : 16 * p.D * 2;
   const int smem = ((Cfg::DGBUF_BYTES + part_bufs * part_bytes + Cfg::DBUF_BYTES + 127) & ~127) + ring_bytes;
@@ -583,10 +583,10 @@ int launch_bwd(const BwdParams& p, const float* cache, const float* history, con
     const uint64_t dims1[5] = {uD, uN, 1u, uB, static_cast<uint64_t>(CT::S)};
     if (make_tensor_map(&init_map, initial, 4, 5, dims1, box) != 0) return -4;
   }
-  auto kern = frnn_bwd_kernel<CELL, BV, U, WX_BF16>;
+  auto kern = frnn_bwd_kernel<CELL, BV, U, WX_BF16, XG>;
   cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, smem);
   if (e != cudaSuccess) return static_cast<int>(e);
-  if (p.C > 8 && p.xg_data == nullptr) {
+  if (p.C > 8 && !XG) {
     e = cudaFuncSetAttribute(kern, cudaFuncAttributeNonPortableClusterSizeAllowed, 1);
     if (e != cudaSuccess) return static_cast<int>(e);
   }
@@ -597,7 +597,7 @@ int launch_bwd(const BwdParams& p, const float* cache, const float* history, con
   cfg.dynamicSmemBytes = smem;
   cfg.stream = stream;
   cudaLaunchAttribute attr[1];
-  if (p.xg_data == nullptr) {
+  if (!XG) {
     attr[0].id = cudaLaunchAttributeClusterDimension;
     attr[0].val.clusterDim.x = static_cast<unsigned>(p.C);
     attr[0].val.clusterDim.y = 1;
@@ -609,7 +609,7 @@ int launch_bwd(const BwdParams& p, const float* cache, const float* history, con
   }
   cfg.attrs = attr;
   cfg.numAttrs = 1;
-  if (p.xg_data == nullptr && p.C > 1) {
+  if (!XG && p.C > 1) {
     // a cluster that cannot be placed (too many CTAs or too much shared memory per GPC) is reported, not launched
     int max_clusters = 0;
     e = cudaOccupancyMaxActiveClusters(&max_clusters, kern, &cfg);
@@ -623,8 +623,14 @@ int launch_bwd(const BwdParams& p, const float* cache, const float* history, con
 template <int CELL, int BV, int U>
 int launch_bwd_dt(const BwdParams& p, const float* cache, const float* history, const float* initial,
                   const float* d_history, int wx_bf16, cudaStream_t s) {
-  return wx_bf16 ? launch_bwd<CELL, BV, U, true>(p, cache, history, initial, d_history, s)
-                 : launch_bwd<CELL, BV, U, false>(p, cache, history, initial, d_history, s);
+  if constexpr (U == 32) {  // groups wider than a cluster exchange through global memory (32-unit slices only)
+    if (p.xg_data != nullptr)
+      return wx_bf16 ? launch_bwd<CELL, BV, U, true, true>(p, cache, history, initial, d_history, s)
+                     : launch_bwd<CELL, BV, U, false, true>(p, cache, history, initial, d_history, s);
+  }
+  if (p.xg_data != nullptr) return -2;
+  return wx_bf16 ? launch_bwd<CELL, BV, U, true, false>(p, cache, history, initial, d_history, s)
+                 : launch_bwd<CELL, BV, U, false, false>(p, cache, history, initial, d_history, s);
 }
 template <int CELL>
 int launch_bwd_cell(const BwdParams& p, const float* cache, const float* history, const float* initial,

@@ -47,7 +47,7 @@ __device__ __forceinline__ void report(int* err, int code, int detail) {
   __threadfence();
 }
 
-template <int CELL, int BV, int U, bool WX_BF16>
+template <int CELL, int BV, int U, bool WX_BF16, bool XG>
 __global__ void __launch_bounds__(kFwdThreads, 1)
 frnn_fwd_kernel(const FwdParams p, const __grid_constant__ CUtensorMap wx_map) {
   using Cfg = FwdCfg<CELL, BV, U, WX_BF16>;
@@ -76,7 +76,7 @@ frnn_fwd_kernel(const FwdParams p, const __grid_constant__ CUtensorMap wx_map) {
   uint8_t* const wxs = smem + ((2 * hbuf_bytes + Cfg::GBUF_BYTES + 127) & ~127);
   const volatile int* abort_flag = p.err;
   const uint64_t limit = p.wait_limit_ns;
-  const bool xg = p.xg_data != nullptr;  // exchange h through global memory instead of DSMEM
+  constexpr bool xg = XG;  // exchange h through global memory instead of DSMEM
   // four operand slots per group in global memory: h_t goes to slot (t + 1) % 4, see the epilogue
   uint8_t* const xg_h = xg ? p.xg_data + static_cast<size_t>(gid) * 4 * hbuf_bytes : nullptr;
   // test hook: with err[4] = 1 no CTA publishes h from step err[5] on, so the next operand wait runs out
@@ -462,7 +462,7 @@ frnn_fwd_kernel(const FwdParams p, const __grid_constant__ CUtensorMap wx_map) {
   if (warp == 4) tmem_dealloc(tbase, tmem_cols);
 }
 
-template <int CELL, int BV, int U, bool WX_BF16>
+template <int CELL, int BV, int U, bool WX_BF16, bool XG>
 int launch_fwd(const FwdParams& p, const void* wx, cudaStream_t stream) {
   using Cfg = FwdCfg<CELL, BV, U, WX_BF16>;
   using CT = typename Cfg::CT;
@@ -474,10 +474,10 @@ int launch_fwd(const FwdParams& p, const void* wx, cudaStream_t stream) {
                             static_cast<uint64_t>(p.T), static_cast<uint64_t>(p.B)};
   const uint32_t box[5] = {static_cast<uint32_t>(U), 1u, static_cast<uint32_t>(CT::GW), 1u, static_cast<uint32_t>(p.wx_box_b)};
   if (make_tensor_map(&map, wx, Cfg::WX_ES, 5, dims, box) != 0) return -4;
-  auto kern = frnn_fwd_kernel<CELL, BV, U, WX_BF16>;
+  auto kern = frnn_fwd_kernel<CELL, BV, U, WX_BF16, XG>;
   cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, smem);
   if (e != cudaSuccess) return static_cast<int>(e);
-  if (p.C > 8 && p.xg_data == nullptr) {
+  if (p.C > 8 && !XG) {
     e = cudaFuncSetAttribute(kern, cudaFuncAttributeNonPortableClusterSizeAllowed, 1);
     if (e != cudaSuccess) return static_cast<int>(e);
   }
@@ -488,7 +488,7 @@ int launch_fwd(const FwdParams& p, const void* wx, cudaStream_t stream) {
   cfg.dynamicSmemBytes = smem;
   cfg.stream = stream;
   cudaLaunchAttribute attr[1];
-  if (p.xg_data == nullptr) {
+  if (!XG) {
     attr[0].id = cudaLaunchAttributeClusterDimension;
     attr[0].val.clusterDim.x = static_cast<unsigned>(p.C);
     attr[0].val.clusterDim.y = 1;
@@ -500,7 +500,7 @@ int launch_fwd(const FwdParams& p, const void* wx, cudaStream_t stream) {
   }
   cfg.attrs = attr;
   cfg.numAttrs = 1;
-  if (p.xg_data == nullptr && p.C > 1) {
+  if (!XG && p.C > 1) {
     // a cluster that cannot be placed (too many CTAs or too much shared memory per GPC) is reported, not launched
     int max_clusters = 0;
     e = cudaOccupancyMaxActiveClusters(&max_clusters, kern, &cfg);
@@ -513,7 +513,12 @@ int launch_fwd(const FwdParams& p, const void* wx, cudaStream_t stream) {
 
 template <int CELL, int BV, int U>
 int launch_fwd_dt(const FwdParams& p, const void* wx, int wx_bf16, cudaStream_t s) {
-  return wx_bf16 ? launch_fwd<CELL, BV, U, true>(p, wx, s) : launch_fwd<CELL, BV, U, false>(p, wx, s);
+  if constexpr (U == 32) {  // groups wider than a cluster exchange through global memory (32-unit slices only)
+    if (p.xg_data != nullptr)
+      return wx_bf16 ? launch_fwd<CELL, BV, U, true, true>(p, wx, s) : launch_fwd<CELL, BV, U, false, true>(p, wx, s);
+  }
+  if (p.xg_data != nullptr) return -2;
+  return wx_bf16 ? launch_fwd<CELL, BV, U, true, false>(p, wx, s) : launch_fwd<CELL, BV, U, false, false>(p, wx, s);
 }
 template <int CELL>
 int launch_fwd_cell(const FwdParams& p, const void* wx, int wx_bf16, int bv, int unit, cudaStream_t s) {
