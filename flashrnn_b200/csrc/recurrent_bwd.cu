@@ -32,8 +32,11 @@ struct BwdCfg {
   static constexpr int GCL = CELL == kElman ? 0 : CT::GC;  // cached gates actually loaded
   static constexpr int STAGE_FLOATS = (GCL + 3 * CT::S) * BV * U;
   static constexpr int STAGE_BYTES = STAGE_FLOATS * 4;
-  // TMA ring depth: four stages unless a stage is so large (wide batch tiles, many states) that fewer fit
-  static constexpr int NST = STAGE_BYTES * 4 <= 98304 ? 4 : (STAGE_BYTES * 3 <= 122880 ? 3 : 2);
+  // TMA ring depth: four stages unless a stage is so large (wide batch tiles, many states) that fewer
+  // fit. 16-row tiles run where CTAs outnumber SMs, so their ring stays below 80 KB and two CTAs
+  // share one SM's shared memory.
+  static constexpr int RING_MAX = BV == 16 ? 81920 : 122880;
+  static constexpr int NST = STAGE_BYTES * 4 <= (BV == 16 ? 81920 : 98304) ? 4 : (STAGE_BYTES * 3 <= RING_MAX ? 3 : 2);
   static constexpr int DGBUF_BYTES = BT * ROWS * 2;
   static constexpr int DBUF_BYTES = BV * CT::GB * U * 4;
   static_assert(ROWS % 16 == 0, "K must be a multiple of 16");
@@ -49,7 +52,7 @@ __device__ __forceinline__ void report(int* err, int code, int detail) {
 }
 
 template <int CELL, int BV, int U, bool WX_BF16, bool XG>
-__global__ void __launch_bounds__(kBwdThreads, 1)
+__global__ void __launch_bounds__(kBwdThreads, (BV == 16 && !XG) ? 2 : 1)  // 16-row tiles are chosen when CTAs outnumber SMs: let two share one
 frnn_bwd_kernel(const BwdParams p, const __grid_constant__ CUtensorMap cache_map,
                 const __grid_constant__ CUtensorMap hist_map, const __grid_constant__ CUtensorMap init_map,
                 const __grid_constant__ CUtensorMap dhist_map) {
