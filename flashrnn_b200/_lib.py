@@ -26,7 +26,7 @@ ERROR_TEXT = {
     103: "TMA input stage never filled",
     104: "TMA input stage never released",
     105: "epilogue barrier timed out",
-    106: "partial dh never arrived",
+    106: "partial sums of a peer CTA never arrived",
     107: "dg operand barrier timed out",
 }
 
@@ -40,6 +40,7 @@ class Plan(ctypes.Structure):
         ("supported", c_int),
         ("cache_bytes", c_int64), ("hbf_bytes", c_int64), ("dgr_bytes", c_int64), ("dbpart_bytes", c_int64),
         ("wgrad_work_bytes", c_int64), ("wgrad_ksplit", c_int), ("exchange", c_int), ("xchg_bytes", c_int64),
+        ("fwd_ksplit", c_int), ("fwd_ctas", c_int),
     ]
 
 

@@ -9,6 +9,7 @@
 namespace frnn {
 
 int forward_dispatch(int cell, const FwdParams& p, const void* wx, int wx_bf16, int bv, int unit, cudaStream_t s);
+int forward_ksplit_dispatch(int cell, const FwdParams& p, const void* wx, int wx_bf16, int bv, int ksplit, cudaStream_t s);
 int backward_dispatch(int cell, const BwdParams& p, const float* cache, const float* history, const float* initial,
                       const float* d_history, int wx_bf16, int bv, int unit, cudaStream_t s);
 int wgrad_plan(int gr, int B, int T, int N, int D, int* np_out, int* ksplit_out, int* cps_out);
@@ -112,18 +113,46 @@ extern "C" int frnn_b200_plan(int cell, int B, int T, int N, int D, frnn_b200_pl
   }
   out->n_btiles = (B + out->batch_tile - 1) / out->batch_tile;
   out->grid_ctas = N * out->n_btiles * out->cluster;
-  const int bt = out->batch_tile < 16 ? 16 : out->batch_tile;
-  const int rows = c.gr * out->unit;
+  const int bt = 16;  // UMMA N: batch tile padded to 16 columns
+  int rows = c.gr * out->unit;
   const int mt = (rows + 127) / 128;
   const int fwd_cols = ((mt * bt + 31) / 32 * 32) + mt * (D / 2);
   const int mtb = (D + 127) / 128;
-  const int bwd_cols = ((mtb * bt + 31) / 32 * 32) + mtb * (rows / 2);
-  out->exchange = out->cluster > 16 ? 1 : 0;  // wider than a cluster: exchange through global memory
+  int bwd_cols = ((mtb * bt + 31) / 32 * 32) + mtb * (rows / 2);
+  // exchange 0: one thread-block cluster per group; 1: groups wider than a cluster exchange through
+  // global memory; 2: heads whose rows of R do not fit one CTA's tensor memory: the forward splits
+  // the contraction over two CTAs per row tile, the backward runs with 16-unit slices.
+  out->exchange = out->cluster > 16 ? 1 : 0;
   out->supported = (D % 16 == 0) && fwd_cols <= 512 && bwd_cols <= 512 && (out->exchange == 0 || out->unit == 32);
+  if (!out->supported && D % 64 == 0 && D / 2 <= 896) {
+    out->exchange = 2;
+    out->unit = 16;
+    out->cluster = D / 16;  // CTAs per group, forward (D/32 row tiles x 2) and backward alike
+    rows = c.gr * 16;
+    bwd_cols = ((mtb * bt + 31) / 32 * 32) + mtb * (rows / 2);
+    out->supported = bwd_cols <= 512;
+  }
+  out->fwd_ctas = out->grid_ctas;
   if (out->exchange) {
+    // all CTAs of such a launch wait on one another: they must be resident together. The forward
+    // splits the contraction over two CTAs per 32-unit row tile where the width allows it (shorter
+    // tensor-core chain per step), so it may need more CTAs than the backward.
+    const bool fsplit = D % 64 == 0 && D / 2 <= 896;
+    const int fwd_per_group = fsplit ? D / 16 : out->cluster;
+    const int per_group = fwd_per_group > out->cluster ? fwd_per_group : out->cluster;
+    if (static_cast<long long>(N) * ((B + 7) / 8) * per_group > sm_count()) out->batch_tile = 16;
+    out->n_btiles = (B + out->batch_tile - 1) / out->batch_tile;
+    out->grid_ctas = N * out->n_btiles * out->cluster;
+    out->fwd_ksplit = fsplit ? 2 : 0;
+    out->fwd_ctas = N * out->n_btiles * fwd_per_group;
+    if (out->fwd_ksplit && out->fwd_ctas > sm_count() && out->exchange == 1) {
+      out->fwd_ksplit = 0;  // not enough SMs for the split forward: one CTA per 32 units
+      out->fwd_ctas = out->grid_ctas;
+    }
+    if (out->grid_ctas > sm_count() || out->fwd_ctas > sm_count()) out->supported = 0;
     const int64_t groups = static_cast<int64_t>(N) * out->n_btiles;
-    const int64_t fwd_b = 4ll * bt * D * 2;                                          // four operand slots
-    const int64_t bwd_b = 2ll * out->cluster * out->cluster * 32 * out->batch_tile * 4;  // two slots of partial-dh blocks
+    const int64_t fwd_b = 4ll * bt * D * 2;                                                      // four operand slots
+    const int64_t bwd_b = 2ll * out->cluster * out->cluster * out->unit * out->batch_tile * 4;  // two slots of partial-dh blocks
     out->xchg_bytes = 4096 + groups * 512 + groups * (fwd_b > bwd_b ? fwd_b : bwd_b);
   }
   const int64_t btnd = static_cast<int64_t>(B) * T * N * D;
@@ -173,6 +202,8 @@ extern "C" int frnn_b200_forward(int cell, const void* wx, int wx_bf16, const vo
     p.xg_counters = static_cast<uint32_t*>(xchg);
     p.xg_data = static_cast<uint8_t*>(xchg) + ((counters + 4095) & ~static_cast<size_t>(4095));
   }
+  if (plan.fwd_ksplit)
+    return forward_ksplit_dispatch(cell, p, wx, wx_bf16, plan.batch_tile, 2, static_cast<cudaStream_t>(stream));
   return forward_dispatch(cell, p, wx, wx_bf16, plan.batch_tile, plan.unit, static_cast<cudaStream_t>(stream));
 }
 

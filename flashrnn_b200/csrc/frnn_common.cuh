@@ -19,7 +19,7 @@ enum : int {
   kErrWaitWx = 103,     // TMA stage never filled
   kErrWaitEmpty = 104,  // TMA stage never released
   kErrWaitEpi = 105,    // epilogue-internal barrier
-  kErrWaitPart = 106,   // backward: partial dh never arrived
+  kErrWaitPart = 106,   // partial sums of a peer CTA never arrived
   kErrWaitDg = 107,     // backward: dg operand barrier
 };
 

@@ -20,6 +20,7 @@ namespace {
 
 constexpr int kEpiThreads = 128;
 constexpr int kBwdThreads = 192;
+constexpr int kMaxTiles = 16;  // 128-row tiles of the partial dh a CTA can produce (D <= 2048)
 constexpr int kStages = 4;  // upper bound of the TMA ring depth (Cfg::NST is the depth in use)
 
 template <int CELL, int BV, int U, bool WX_BF16>
@@ -63,7 +64,7 @@ frnn_bwd_kernel(const BwdParams p, const __grid_constant__ CUtensorMap cache_map
   extern __shared__ __align__(1024) uint8_t smem[];
   __shared__ __align__(8) uint64_t s_part_bar[2];
   __shared__ __align__(8) uint64_t s_dg_bar;
-  __shared__ __align__(8) uint64_t s_mma_bar[8];  // one per 128-row tile of the partial dh (at most 6)
+  __shared__ __align__(8) uint64_t s_mma_bar[kMaxTiles];  // one per 128-row tile of the partial dh
   __shared__ __align__(8) uint64_t s_full[kStages];
   __shared__ __align__(8) uint64_t s_empty[kStages];
   __shared__ uint32_t s_tmem_base;
@@ -105,7 +106,7 @@ frnn_bwd_kernel(const BwdParams p, const __grid_constant__ CUtensorMap cache_map
     mbar_init(smem_u32(&s_part_bar[0]), 1);
     mbar_init(smem_u32(&s_part_bar[1]), 1);
     mbar_init(smem_u32(&s_dg_bar), kEpiThreads);
-    for (int j = 0; j < 8; ++j) mbar_init(smem_u32(&s_mma_bar[j]), 1);
+    for (int j = 0; j < kMaxTiles; ++j) mbar_init(smem_u32(&s_mma_bar[j]), 1);
     for (int s = 0; s < Cfg::NST; ++s) {
       mbar_init(smem_u32(&s_full[s]), 1);
       mbar_init(smem_u32(&s_empty[s]), kEpiThreads);
@@ -232,6 +233,11 @@ frnn_bwd_kernel(const BwdParams p, const __grid_constant__ CUtensorMap cache_map
             break;
           }
         }
+        // Once any wait of the grid has run out, the epilogue threads stop waiting for the stages and
+        // release them early, so "released" no longer implies that the previous copy into this stage
+        // has landed; arming its barrier again could then be a second arrival in one phase. The flag
+        // is set before any thread skips a wait, so checking it after the wait above is enough.
+        if (*abort_flag != 0) break;
         const uint32_t bar = smem_u32(&s_full[s]);
         float* sb = reinterpret_cast<float*>(stages + s * Cfg::STAGE_BYTES);
         mbar_arrive_expect_tx(bar, stage_tx);
@@ -300,7 +306,7 @@ frnn_bwd_kernel(const BwdParams p, const __grid_constant__ CUtensorMap cache_map
           // into registers until each word shows this iteration's phase bit, then added in source
           // order. A slot is not rewritten before this CTA has scattered again, which it does only
           // after this poll, so a word with the right phase can only be this iteration's.
-          constexpr int SB = IPT == 2 ? 24 : 12;  // sources per batch
+          constexpr int SB = IPT == 2 ? 32 : 12;  // sources per batch
           const uint32_t phase = static_cast<uint32_t>(((it - 1) >> 1) & 1);
           const uint8_t* src0 = xg_p + ((static_cast<size_t>(it & 1) * C + rank) * C) * (BV * U * 4) + (ib * U + ul) * 4;
           for (int s0 = 0; s0 < C; s0 += SB) {
@@ -566,7 +572,7 @@ int launch_bwd(const BwdParams& p, const float* cache, const float* history, con
   const int ring_bytes = Cfg::NST * Cfg::STAGE_BYTES > 16 * p.D * 2 ? Cfg::NST * Cfg::STAGE_BYTES : 16 * p.D * 2;
   const int smem = ((Cfg::DGBUF_BYTES + part_bufs * part_bytes + Cfg::DBUF_BYTES + 127) & ~127) + ring_bytes;
   const int MTB = (p.D + 127) / 128;
-  if (((MTB * Cfg::BT + 31) / 32 * 32) + MTB * (Cfg::ROWS / 2) > 512) return -3;
+  if (MTB > kMaxTiles || ((MTB * Cfg::BT + 31) / 32 * 32) + MTB * (Cfg::ROWS / 2) > 512) return -3;
   if (smem > 227 * 1024) return -2;
   const uint64_t uD = p.D, uN = p.N, uT = p.T, uB = p.B;
   const uint32_t ub = static_cast<uint32_t>(p.box_b);
@@ -626,12 +632,9 @@ int launch_bwd(const BwdParams& p, const float* cache, const float* history, con
 template <int CELL, int BV, int U>
 int launch_bwd_dt(const BwdParams& p, const float* cache, const float* history, const float* initial,
                   const float* d_history, int wx_bf16, cudaStream_t s) {
-  if constexpr (U == 32) {  // groups wider than a cluster exchange through global memory (32-unit slices only)
-    if (p.xg_data != nullptr)
-      return wx_bf16 ? launch_bwd<CELL, BV, U, true, true>(p, cache, history, initial, d_history, s)
-                     : launch_bwd<CELL, BV, U, false, true>(p, cache, history, initial, d_history, s);
-  }
-  if (p.xg_data != nullptr) return -2;
+  if (p.xg_data != nullptr)  // groups wider than a cluster exchange through global memory
+    return wx_bf16 ? launch_bwd<CELL, BV, U, true, true>(p, cache, history, initial, d_history, s)
+                   : launch_bwd<CELL, BV, U, false, true>(p, cache, history, initial, d_history, s);
   return wx_bf16 ? launch_bwd<CELL, BV, U, true, false>(p, cache, history, initial, d_history, s)
                  : launch_bwd<CELL, BV, U, false, false>(p, cache, history, initial, d_history, s);
 }

@@ -225,6 +225,11 @@ frnn_fwd_kernel(const FwdParams p, const __grid_constant__ CUtensorMap wx_map) {
             break;
           }
         }
+        // Once any wait of the grid has run out, the epilogue threads stop waiting for the stages and
+        // release them early, so "released" no longer implies that the previous copy into this stage
+        // has landed; arming its barrier again could then be a second arrival in one phase. The flag
+        // is set before any thread skips a wait, so checking it after the wait above is enough.
+        if (*abort_flag != 0) break;
         mbar_arrive_expect_tx(smem_u32(&s_wx_full[s]), stage_tx);
         tma_load_5d(smem_u32(wxs + s * Cfg::WX_STAGE_BYTES), &wx_map, smem_u32(&s_wx_full[s]), rank * U, n, 0, t, b0);
       }

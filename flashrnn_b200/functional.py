@@ -84,7 +84,7 @@ class _Recurrence(torch.autograd.Function):
         if not plan.supported:
             raise ValueError(
                 f"flashrnn_b200: cell={cell} D={D} is outside the sm_100a kernel family "
-                f"(the R slice of a CTA must fit in tensor memory: D <= 768)"
+                f"(R must fit in the tensor memory of the CTAs of one launch: D <= 1280 for four gates)"
             )
         history = torch.empty((S, B, T, N, D), dtype=torch.float32, device=dev)
         carry = torch.empty((S, B, 1, N, D), dtype=torch.float32, device=dev)

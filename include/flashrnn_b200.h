@@ -55,8 +55,13 @@ typedef struct frnn_b200_plan {
   int64_t wgrad_work_bytes; /* float [wgrad_ksplit, gates_r,N,D,D] split-K partials, 0 if none */
   int wgrad_ksplit;
   int exchange;          /* 0: CTAs of a group exchange through cluster shared memory;
-                            1: group wider than a cluster (D > 512): through global memory  */
-  int64_t xchg_bytes;    /* scratch for exchange = 1 (forward and backward), else 0       */
+                            1: group wider than a cluster (D > 512): through global memory;
+                            2: as 1, with 16-unit slices in the backward (768 < D)           */
+  int64_t xchg_bytes;    /* scratch for exchange >= 1 (forward and backward), else 0      */
+  int fwd_ksplit;        /* 0, or 2: the forward splits the contraction of a 32-unit row
+                            tile over this many CTAs (a cluster) and exchanges h through
+                            global memory                                                  */
+  int fwd_ctas;          /* CTAs of the forward launch                                     */
 } frnn_b200_plan_t;
 
 /* Library / ABI version (major*1000 + minor). */
@@ -74,7 +79,7 @@ int frnn_b200_plan(int cell, int B, int T, int N, int D, frnn_b200_plan_t* out);
  *   bias, initial : fp32
  *   history   : out fp32 [S,B,T,N,D];  carry: out fp32 [S,B,1,N,D]
  *   cache, hbf: scratch written for the backward pass, or NULL for inference
- *   xchg      : scratch of plan.xchg_bytes when plan.exchange = 1 (cleared by the call), else NULL;
+ *   xchg      : scratch of plan.xchg_bytes when plan.exchange >= 1 (initialised by the call), else NULL;
  *               such shapes are launched cooperatively: N * n_btiles * cluster CTAs must be
  *               resident at once (one per SM), otherwise the launch returns a CUDA error
  *   slstm_zero_first: 1 if every element of initial n is zero (reference.py:99)

@@ -34,7 +34,11 @@ def test_plan_describes_the_headline_workload():
     assert (big.batch_tile, big.n_btiles, big.cluster) == (16, 16, 4)
     wide = _lib.plan("lstm", 16, 8, 1, 768)                  # wider than a cluster: global-memory exchange
     assert wide.supported and wide.exchange == 1 and wide.cluster == 24 and wide.xchg_bytes > 0
-    assert not _lib.plan("lstm", 8, 8, 1, 1024).supported     # the R slice no longer fits in tensor memory
+    assert wide.fwd_ksplit == 2 and wide.fwd_ctas == 2 * 48   # the forward splits the contraction over two CTAs per row tile
+    wider = _lib.plan("lstm", 8, 8, 1, 1024)                   # rows of R beyond one CTA's tensor memory: 16-unit backward slices
+    assert wider.supported and wider.exchange == 2 and wider.unit == 16 and wider.cluster == 64 and wider.fwd_ksplit == 2
+    assert not _lib.plan("lstm", 8, 8, 1, 2048).supported     # R no longer fits in the tensor memory of one launch
+    assert not _lib.plan("lstm", 64, 8, 1, 1024).supported    # more CTAs than SMs cannot wait on one another
     assert not _lib.plan("lstm", 8, 8, 1, 40).supported       # the ABI wants D % 16 == 0 (Python pads)
 
 

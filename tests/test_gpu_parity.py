@@ -78,6 +78,11 @@ SHAPES = [
     ("gru", 8, 7, 2, 576, 36, False),      # two such groups side by side
     ("slstm", 4, 5, 1, 768, 37, True),
     ("elman", 3, 9, 1, 640, 38, False),
+    ("lstm", 8, 10, 1, 1024, 42, False),   # rows of R beyond one CTA's tensor memory: contraction split over two CTAs
+    ("gru", 4, 6, 1, 1280, 43, False),
+    ("slstm", 3, 5, 1, 1024, 44, True),
+    ("elman", 5, 7, 1, 1792, 45, False),
+    ("lstm", 24, 5, 1, 1024, 46, False),   # the same with 16-row batch tiles
     ("lstm", 1, 1, 1, 3, 33, False),       # the reference's smallest portable-gate shape
     ("gru", 3, 3, 2, 7, 34, False),
 ]
