@@ -19,7 +19,7 @@ PKG = Path(__file__).resolve().parent
 CSRC = PKG / "csrc"
 LIB_DIR = PKG / "lib"
 LIB_PATH = LIB_DIR / "libflashrnn_b200.so"
-SOURCES = ("capi.cu", "recurrent_fwd.cu", "recurrent_fwd_ksplit.cu", "recurrent_bwd.cu", "wgrad.cu")
+SOURCES = ("capi.cu", "recurrent_fwd.cu", "recurrent_fwd_ksplit.cu", "recurrent_bwd.cu", "recurrent_bwd_ksplit.cu", "wgrad.cu")
 NVCC_FLAGS = (
     "-gencode", "arch=compute_100a,code=sm_100a", "-O3", "-std=c++17", "-lineinfo",
     "-Xcompiler", "-fPIC",

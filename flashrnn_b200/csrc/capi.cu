@@ -10,6 +10,10 @@ namespace frnn {
 
 int forward_dispatch(int cell, const FwdParams& p, const void* wx, int wx_bf16, int bv, int unit, cudaStream_t s);
 int forward_ksplit_dispatch(int cell, const FwdParams& p, const void* wx, int wx_bf16, int bv, int ksplit, cudaStream_t s);
+int backward_ksplit_width(int gates_r, int D);
+int backward_ksplit_dispatch(int cell, const BwdParams& p, const float* cache, const float* history, const float* initial,
+                             const float* d_history, int wx_bf16, int bv, int ksplit, cudaStream_t s, int* capacity_only);
+int backward_ksplit_capacity(int cell, int bv, int ksplit, int D);
 int backward_dispatch(int cell, const BwdParams& p, const float* cache, const float* history, const float* initial,
                       const float* d_history, int wx_bf16, int bv, int unit, cudaStream_t s);
 int wgrad_plan(int gr, int B, int T, int N, int D, int* np_out, int* ksplit_out, int* cps_out);
@@ -47,6 +51,25 @@ int sm_count() {
     return 148;
   }
   return n;
+}
+
+// CTAs of the clustered backward launch that the device can hold at once, remembered per shape
+// class (the query is a driver call and the plan is computed on every call).
+int bwd_ksplit_capacity_cached(int cell, int bv, int ks, int D) {
+  struct Entry { int cell, bv, ks, D, cap; };
+  static std::mutex mu;
+  static Entry table[32];
+  static int used = 0;
+  std::lock_guard<std::mutex> lock(mu);
+  for (int i = 0; i < used; ++i)
+    if (table[i].cell == cell && table[i].bv == bv && table[i].ks == ks && table[i].D == D) return table[i].cap;
+  int cap = backward_ksplit_capacity(cell, bv, ks, D);
+  if (cap <= 0) {
+    cudaGetLastError();
+    cap = sm_count() / ks * ks;  // no device visible: assume every SM can take part
+  }
+  if (used < 32) table[used++] = Entry{cell, bv, ks, D, cap};
+  return cap;
 }
 
 struct CellCounts {
@@ -124,36 +147,54 @@ extern "C" int frnn_b200_plan(int cell, int B, int T, int N, int D, frnn_b200_pl
   // the contraction over two CTAs per row tile, the backward runs with 16-unit slices.
   out->exchange = out->cluster > 16 ? 1 : 0;
   out->supported = (D % 16 == 0) && fwd_cols <= 512 && bwd_cols <= 512 && (out->exchange == 0 || out->unit == 32);
+  const int bks_width = out->exchange || !out->supported ? backward_ksplit_width(c.gr, D) : 0;
+  bool slices16_fit = true;  // can the 1-D backward hold its slice of R in tensor memory
   if (!out->supported && D % 64 == 0 && D / 2 <= 896) {
     out->exchange = 2;
     out->unit = 16;
-    out->cluster = D / 16;  // CTAs per group, forward (D/32 row tiles x 2) and backward alike
+    out->cluster = D / 16;  // CTAs per group, forward (D/32 row tiles x 2) and 1-D backward alike
     rows = c.gr * 16;
     bwd_cols = ((mtb * bt + 31) / 32 * 32) + mtb * (rows / 2);
-    out->supported = bwd_cols <= 512;
+    slices16_fit = bwd_cols <= 512;
+    out->supported = slices16_fit || bks_width > 0;
   }
   out->fwd_ctas = out->grid_ctas;
-  if (out->exchange) {
-    // all CTAs of such a launch wait on one another: they must be resident together. The forward
-    // splits the contraction over two CTAs per 32-unit row tile where the width allows it (shorter
-    // tensor-core chain per step), so it may need more CTAs than the backward.
-    const bool fsplit = D % 64 == 0 && D / 2 <= 896;
-    const int fwd_per_group = fsplit ? D / 16 : out->cluster;
-    const int per_group = fwd_per_group > out->cluster ? fwd_per_group : out->cluster;
-    if (static_cast<long long>(N) * ((B + 7) / 8) * per_group > sm_count()) out->batch_tile = 16;
-    out->n_btiles = (B + out->batch_tile - 1) / out->batch_tile;
-    out->grid_ctas = N * out->n_btiles * out->cluster;
-    out->fwd_ksplit = fsplit ? 2 : 0;
-    out->fwd_ctas = N * out->n_btiles * fwd_per_group;
-    if (out->fwd_ksplit && out->fwd_ctas > sm_count() && out->exchange == 1) {
-      out->fwd_ksplit = 0;  // not enough SMs for the split forward: one CTA per 32 units
-      out->fwd_ctas = out->grid_ctas;
+  if (out->exchange && out->supported) {
+    // All CTAs of such a launch wait on one another: they must be resident together. Where the width
+    // allows it the forward splits the contraction over two CTAs per 32-unit row tile and the
+    // backward owns columns of R (128-unit tiles x K-chunks); both shorten the tensor-core chain of
+    // a step and exchange bf16 operands instead of fp32 partial sums. The clustered backward can
+    // hold fewer CTAs than there are SMs; where it does not fit, the 1-D backward is used.
+    const int slice_ctas = out->cluster;
+    const int tile0 = out->batch_tile;
+    for (int bks = bks_width; ; bks = 0) {
+      out->batch_tile = tile0;
+      const bool fsplit = D % 64 == 0 && D / 2 <= 896;
+      const int fwd_per_group = fsplit ? D / 16 : slice_ctas;
+      const int bwd_per_group = bks ? (D / 128) * bks : slice_ctas;
+      const int per_group = fwd_per_group > bwd_per_group ? fwd_per_group : bwd_per_group;
+      const long long groups8 = static_cast<long long>(N) * ((B + 7) / 8);
+      if (groups8 * per_group > sm_count() || (bks && groups8 * bwd_per_group > bwd_ksplit_capacity_cached(cell, 8, bks, D)))
+        out->batch_tile = 16;
+      out->n_btiles = (B + out->batch_tile - 1) / out->batch_tile;
+      const int groups = N * out->n_btiles;
+      out->fwd_ksplit = fsplit ? 2 : 0;
+      out->fwd_ctas = groups * fwd_per_group;
+      out->bwd_ksplit = bks;
+      out->cluster = bwd_per_group;
+      out->grid_ctas = groups * out->cluster;
+      if (out->fwd_ksplit && out->fwd_ctas > sm_count() && out->exchange == 1) {
+        out->fwd_ksplit = 0;  // not enough SMs for the split forward: one CTA per 32 units
+        out->fwd_ctas = groups * (D / 32);
+      }
+      const int bwd_cap = bks ? bwd_ksplit_capacity_cached(cell, out->batch_tile, bks, D) : sm_count();
+      out->supported = out->grid_ctas <= bwd_cap && out->fwd_ctas <= sm_count() && (bks > 0 || slices16_fit);
+      const int64_t fwd_b = 4ll * bt * D * 2;  // four operand slots
+      const int64_t bwd_b = bks ? 4ll * bt * c.gr * D * 2                                              // four slots of dG
+                                : 2ll * out->cluster * out->cluster * out->unit * out->batch_tile * 4;  // two slots of partial dh
+      out->xchg_bytes = 4096 + groups * 512ll + groups * (fwd_b > bwd_b ? fwd_b : bwd_b);
+      if (out->supported || bks == 0) break;
     }
-    if (out->grid_ctas > sm_count() || out->fwd_ctas > sm_count()) out->supported = 0;
-    const int64_t groups = static_cast<int64_t>(N) * out->n_btiles;
-    const int64_t fwd_b = 4ll * bt * D * 2;                                                      // four operand slots
-    const int64_t bwd_b = 2ll * out->cluster * out->cluster * out->unit * out->batch_tile * 4;  // two slots of partial-dh blocks
-    out->xchg_bytes = 4096 + groups * 512 + groups * (fwd_b > bwd_b ? fwd_b : bwd_b);
   }
   const int64_t btnd = static_cast<int64_t>(B) * T * N * D;
   out->cache_bytes = btnd * c.gc * 4;
@@ -239,6 +280,9 @@ extern "C" int frnn_b200_backward(int cell, const float* cache, const float* his
     p.xg_counters = static_cast<uint32_t*>(xchg);
     p.xg_data = static_cast<uint8_t*>(xchg) + ((counters + 4095) & ~static_cast<size_t>(4095));
   }
+  if (plan.bwd_ksplit)
+    return backward_ksplit_dispatch(cell, p, cache, history, initial, d_history, wx_bf16, plan.batch_tile,
+                                    plan.bwd_ksplit, static_cast<cudaStream_t>(stream), nullptr);
   return backward_dispatch(cell, p, cache, history, initial, d_history, wx_bf16, plan.batch_tile, plan.unit,
                            static_cast<cudaStream_t>(stream));
 }

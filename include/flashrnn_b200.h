@@ -62,6 +62,9 @@ typedef struct frnn_b200_plan {
                             tile over this many CTAs (a cluster) and exchanges h through
                             global memory                                                  */
   int fwd_ctas;          /* CTAs of the forward launch                                     */
+  int bwd_ksplit;        /* 0, or 2/4/8: the backward owns columns of R in tiles of 128 units
+                            and splits the gates_r * D gate rows over this many CTAs (a
+                            cluster); cluster / grid_ctas then describe that launch        */
 } frnn_b200_plan_t;
 
 /* Library / ABI version (major*1000 + minor). */

@@ -83,6 +83,7 @@ SHAPES = [
     ("slstm", 3, 5, 1, 1024, 44, True),
     ("elman", 5, 7, 1, 1792, 45, False),
     ("lstm", 24, 5, 1, 1024, 46, False),   # the same with 16-row batch tiles
+    ("lstm", 4, 6, 1, 1536, 47, False),    # 96 CTAs per group: 12 unit tiles x 8 K-chunks in the backward
     ("lstm", 1, 1, 1, 3, 33, False),       # the reference's smallest portable-gate shape
     ("gru", 3, 3, 2, 7, 34, False),
 ]
