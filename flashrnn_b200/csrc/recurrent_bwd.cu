@@ -318,6 +318,7 @@ frnn_bwd_kernel(const BwdParams p, const __grid_constant__ CUtensorMap cache_map
                 if (s0 + k < C) pend |= 1u << k;
             }
             uint64_t t0 = 0;
+            uint32_t poll_rounds = 0;
             while (pend != 0u) {
 #pragma unroll
               for (int k = 0; k < SB; ++k) {
@@ -341,7 +342,8 @@ frnn_bwd_kernel(const BwdParams p, const __grid_constant__ CUtensorMap cache_map
                   if (ok) pend &= ~(1u << k);
                 }
               }
-              if (pend != 0u) {
+              // the global timer is slow to read: look at it (and at the abort flag) only every 16th round
+              if (pend != 0u && (++poll_rounds & 15u) == 0u) {
                 const uint64_t now = global_timer_ns();
                 if (t0 == 0) t0 = now;
                 if (*abort_flag != 0 || now - t0 > limit) {

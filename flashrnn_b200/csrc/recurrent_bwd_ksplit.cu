@@ -55,19 +55,6 @@ __device__ __forceinline__ void report_bks(int* err, int code, int detail) {
   __threadfence();
 }
 
-// Eight neighbouring lanes each hold one bf16 (low half of v); lane 0 of the group returns the
-// 16-byte packet of all eight, in lane order.
-__device__ __forceinline__ uint4 pack8_bf16(uint32_t v) {
-  const uint32_t w0 = (v & 0xffffu) | (__shfl_down_sync(0xffffffffu, v, 1) << 16);
-  const uint32_t w1 = __shfl_down_sync(0xffffffffu, w0, 2);
-  const uint32_t w2 = __shfl_down_sync(0xffffffffu, w0, 4);
-  const uint32_t w3 = __shfl_down_sync(0xffffffffu, w1, 4);
-  return make_uint4(w0, w1, w2, w3);
-}
-__device__ __forceinline__ uint32_t bf16_bits(float x) {
-  return static_cast<uint32_t>(__bfloat16_as_ushort(__float2bfloat16_rn(x)));
-}
-
 template <int CELL, int BV, int KS, bool WX_BF16>
 __global__ void __launch_bounds__(kThreads, 1)
 frnn_bwd_ks_kernel(const BwdParams p, const __grid_constant__ CUtensorMap cache_map,
@@ -267,6 +254,26 @@ frnn_bwd_ks_kernel(const BwdParams p, const __grid_constant__ CUtensorMap cache_
     const int prow = tid % BV, kg0 = tid / BV;
     const size_t poll_base = static_cast<size_t>(ks) * dg_bytes + static_cast<size_t>(kg0) * (BT * 16) + prow * 16;
     long long pc[8] = {0, 0, 0, 0, 0, 0, 0, 0};
+    int rounds = 0;
+    // Packets (eight units of one gate and batch row) of the staging layout [gate][batch][unit] that
+    // this thread moves, and where each lives inside an operand slot (gate row k = g * D + unit,
+    // K-chunk k / Kc, then K-major with 16-byte packets per batch row). The staging area is the
+    // buffer of the final db reduction, unused until then.
+    constexpr int PPR = UO / 8;                 // packets per (gate, batch row)
+    constexpr int NPK = CT::GR * BV * PPR;      // packets per step
+    constexpr int NPT = (NPK + kEpiThreads - 1) / kEpiThreads;
+    __nv_bfloat16* const pubbuf = reinterpret_cast<__nv_bfloat16*>(dbuf);
+    __nv_bfloat16* const pubw = pubbuf + CT::GR * BV * UO;
+    static_assert((CT::GR + (CELL == kGRU ? CT::GW : 0)) * 2 <= CT::GB * 4, "staging fits the db buffer");
+    uint32_t pk_at[NPT];
+#pragma unroll
+    for (int q = 0; q < NPT; ++q) {
+      const int pi = tid + q * kEpiThreads;
+      const int k = (pi / (BV * PPR)) * D + u0 + (pi % PPR) * 8;
+      pk_at[q] = pi < NPK ? static_cast<uint32_t>(k / Kc) * static_cast<uint32_t>(dg_bytes) +
+                                static_cast<uint32_t>((k % Kc) >> 3) * (BT * 16)
+                          : 0u;
+    }
     bool dead = false;  // after a failed wait the warp keeps walking through the loop without waiting
 
     float cache[NI][CT::GC], sn[NI][S], sp[NI][S], dhs[NI][S];
@@ -351,50 +358,67 @@ frnn_bwd_ks_kernel(const BwdParams p, const __grid_constant__ CUtensorMap cache_
         }
       }
       const long long c2 = prof ? clock64() : 0;
-      // publish round_bf16(dG_t) of the owned units: eight neighbouring lanes hold one 16-byte packet
-      // (eight units of one gate and batch row). The same packet goes to dgr for the dR contraction.
+      // round_bf16(dG_t) of the owned units is first laid out in shared memory as [gate][batch][unit], so
+      // that all 128 threads then move 16-byte packets (eight units of one gate and batch row): to the
+      // group's operand slot, to dgr for the dR contraction, and (bf16 Wx) to dWx.
       const bool publish = !dead && it < mute_from;
 #pragma unroll
       for (int j = 0; j < NI; ++j) {
         const int ib = ib0 + j * RPP;
-        const size_t row = static_cast<size_t>(b0 + ib) * T + t;
 #pragma unroll
-        for (int g = 0; g < CT::GR; ++g) {
-          const uint4 pk = pack8_bf16(bf16_bits(gr[j][g]));
-          if (act[j] && (lane & 7) == 0) {
-            const int k = g * D + d0;
-            const size_t at = static_cast<size_t>(k / Kc) * dg_bytes + static_cast<size_t>((k % Kc) >> 3) * (BT * 16) + ib * 16;
-            if (publish) {
-              // The data words double as arrival flags; the packet of slot (it + 2) % 4, which held dG of
-              // iteration it - 2 and has been consumed by every CTA, is refilled, and the fence after the
-              // poll below orders the refill before this thread's next data store to that slot.
-              st_relaxed_gpu_v4(xg_dg + static_cast<size_t>(it & 3) * slot_bytes + at,
-                                make_uint4(xg_clean(pk.x), xg_clean(pk.y), xg_clean(pk.z), xg_clean(pk.w)));
-              st_relaxed_gpu_v4(xg_dg + static_cast<size_t>((it + 2) & 3) * slot_bytes + at,
-                                make_uint4(kXgFill, kXgFill, kXgFill, kXgFill));
-            }
-            *reinterpret_cast<uint4*>(p.dgr + (row * CT::GR + g) * ND + n * D + d0) = pk;
-          }
-          if constexpr (WX_BF16 && CELL != kGRU) {
-            if (act[j] && (lane & 7) == 0 && g < CT::GW)
-              *reinterpret_cast<uint4*>(static_cast<__nv_bfloat16*>(p.dwx) + (row * CT::GW + g) * ND + n * D + d0) = pk;
-          }
-        }
+        for (int g = 0; g < CT::GR; ++g) pubbuf[(g * BV + ib) * UO + ul] = __float2bfloat16_rn(gr[j][g]);
         if constexpr (WX_BF16 && CELL == kGRU) {
 #pragma unroll
-          for (int g = 0; g < CT::GW; ++g) {
-            const uint4 pk = pack8_bf16(bf16_bits(gw[j][g]));
-            if (act[j] && (lane & 7) == 0)
-              *reinterpret_cast<uint4*>(static_cast<__nv_bfloat16*>(p.dwx) + (row * CT::GW + g) * ND + n * D + d0) = pk;
-          }
+          for (int g = 0; g < CT::GW; ++g) pubw[(g * BV + ib) * UO + ul] = __float2bfloat16_rn(gw[j][g]);
         }
         if constexpr (!WX_BF16) {
           if (act[j]) {
+            const size_t row = static_cast<size_t>(b0 + ib) * T + t;
 #pragma unroll
             for (int g = 0; g < CT::GW; ++g) static_cast<float*>(p.dwx)[(row * CT::GW + g) * ND + n * D + d0] = gw[j][g];
           }
         }
       }
+      asm volatile("bar.sync 1, 128;" ::: "memory");
+#pragma unroll
+      for (int q = 0; q < NPT; ++q) {
+        const int pi = tid + q * kEpiThreads;
+        const int b = (pi % (BV * PPR)) / PPR;
+        if (pi < NPK && b < bv) {
+          const int g = pi / (BV * PPR), u8 = pi % PPR;
+          const uint4 pk = reinterpret_cast<const uint4*>(pubbuf)[pi];
+          if (publish) {
+            // The data words double as arrival flags; the packet of slot (it + 2) % 4, which held dG of
+            // iteration it - 2 and has been consumed by every CTA, is refilled, and the fence after the
+            // poll below orders the refill before this thread's next data store to that slot.
+            const size_t at = pk_at[q] + b * 16;
+            st_relaxed_gpu_v4(xg_dg + static_cast<size_t>(it & 3) * slot_bytes + at,
+                              make_uint4(xg_clean(pk.x), xg_clean(pk.y), xg_clean(pk.z), xg_clean(pk.w)));
+            st_relaxed_gpu_v4(xg_dg + static_cast<size_t>((it + 2) & 3) * slot_bytes + at,
+                              make_uint4(kXgFill, kXgFill, kXgFill, kXgFill));
+          }
+          const size_t off = ((static_cast<size_t>(b0 + b) * T + t) * CT::GR + g) * ND + n * D + u0 + u8 * 8;
+          *reinterpret_cast<uint4*>(p.dgr + off) = pk;
+          if constexpr (WX_BF16 && CELL != kGRU)  // W-gate and R-gate gradients coincide, and so do the layouts
+            *reinterpret_cast<uint4*>(static_cast<__nv_bfloat16*>(p.dwx) + off) = pk;
+        }
+      }
+      if constexpr (WX_BF16 && CELL == kGRU) {
+        constexpr int NPKW = CT::GW * BV * PPR;
+#pragma unroll
+        for (int q = 0; q < (NPKW + kEpiThreads - 1) / kEpiThreads; ++q) {
+          const int pi = tid + q * kEpiThreads;
+          const int b = (pi % (BV * PPR)) / PPR;
+          if (pi < NPKW && b < bv) {
+            const int g = pi / (BV * PPR), u8 = pi % PPR;
+            const size_t off = ((static_cast<size_t>(b0 + b) * T + t) * CT::GW + g) * ND + n * D + u0 + u8 * 8;
+            *reinterpret_cast<uint4*>(static_cast<__nv_bfloat16*>(p.dwx) + off) = reinterpret_cast<const uint4*>(pubw)[pi];
+          }
+        }
+      }
+      // While the packets of the other CTAs are on their way: next step's inputs into registers. Polling
+      // right away would only add a wasted round trip to the far L2.
+      if (it + 1 < T) load_stage(it + 1);
       const long long c3 = prof ? clock64() : 0;
       {
         // fetch this CTA's K-chunk of dG_t from slot it % 4 into the operand buffer
@@ -407,7 +431,9 @@ frnn_bwd_ks_kernel(const BwdParams p, const __grid_constant__ CUtensorMap cache_
             if (kg0 + j * KG_STEP < Kc / 8) pend |= 1u << j;
         }
         uint64_t t0 = 0;
+        uint32_t poll_rounds = 0;
         while (pend != 0u) {
+          if (prof) ++rounds;
           uint4 v[XCH];
 #pragma unroll
           for (int j = 0; j < XCH; ++j)
@@ -419,7 +445,8 @@ frnn_bwd_ks_kernel(const BwdParams p, const __grid_constant__ CUtensorMap cache_
               pend &= ~(1u << j);
             }
           }
-          if (pend != 0u) {
+          // the global timer is slow to read: look at it (and at the abort flag) only every 16th round
+          if (pend != 0u && (++poll_rounds & 15u) == 0u) {
             const uint64_t now = global_timer_ns();
             if (t0 == 0) t0 = now;
             if (*abort_flag != 0 || now - t0 > limit) {
@@ -434,9 +461,7 @@ frnn_bwd_ks_kernel(const BwdParams p, const __grid_constant__ CUtensorMap cache_
         fence_acq_rel_gpu();
       }
       const long long c4 = prof ? clock64() : 0;
-      // while the tensor core works: next step's inputs into registers
-      if (it + 1 < T) load_stage(it + 1);
-      const long long c5 = prof ? clock64() : 0;
+      const long long c5 = c4;
       if (!dead && !mbar_wait_bounded<false>(smem_u32(&s_mma_bar), it & 1, limit, abort_flag)) {
         report_bks(p.err, kErrWaitMma, it);
         dead = true;
@@ -467,6 +492,7 @@ frnn_bwd_ks_kernel(const BwdParams p, const __grid_constant__ CUtensorMap cache_
     if (prof) {
 #pragma unroll
       for (int q = 0; q < 8; ++q) p.err[8 + q] = static_cast<int>(pc[q]);
+      p.err[18] = rounds;
     }
     // bias gradient: per-thread sums -> shared memory, reduced over the batch rows below
 #pragma unroll

@@ -350,6 +350,7 @@ frnn_fwd_ks_kernel(const FwdParams p, const __grid_constant__ CUtensorMap wx_map
             if (kg0 + j * KG_STEP < Kc / 8) pend |= 1u << j;
         }
         uint64_t t0 = 0;
+        uint32_t poll_rounds = 0;
         while (pend != 0u) {
           uint4 v[XCH];
 #pragma unroll
@@ -362,7 +363,8 @@ frnn_fwd_ks_kernel(const FwdParams p, const __grid_constant__ CUtensorMap wx_map
               pend &= ~(1u << j);
             }
           }
-          if (pend != 0u) {
+          // the global timer is slow to read: look at it (and at the abort flag) only every 16th round
+          if (pend != 0u && (++poll_rounds & 15u) == 0u) {
             const uint64_t now = global_timer_ns();
             if (t0 == 0) t0 = now;
             if (*abort_flag != 0 || now - t0 > limit) {

@@ -85,7 +85,7 @@ def time_shape(cell: str, B: int, T: int, N: int, D: int, reps: int = 5, device:
         torch.cuda.synchronize()
         v = err.tolist()
         out[name + "_phases"] = [round(v[8 + i] / T) for i in range(8)] + [round(v[16] / T), round(v[17] / T), 'prologue', v[20]]
-        out[name + "_extra"] = [round(v[18] / T), round(v[19] / T)]
+        out[name + "_extra"] = [round(v[18] / T), round(v[19] / T), round(v[21] / T)]
     err.zero_()
     if int(err[0].item()) != 0:
         raise RuntimeError(f"device-side error {err.tolist()}")
