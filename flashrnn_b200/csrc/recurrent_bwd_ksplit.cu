@@ -16,7 +16,7 @@
 //
 // Replaces FLASHRNNCellFusedBackward (flashrnn/flashrnn/fused/flashrnn_fused_backward.cu) for wide
 // heads; the exchange of dG instead of partial dh follows the reference's hybrid kernel
-// (flashrnn/flashrnn2/csrc/hybrid_bw2d.cu:664-678). Gradient formulas: cells.cuh.
+// (flashrnn/flashrnn2/hybrid_bw2d.cu:664-678). Gradient formulas: cells.cuh.
 #include "frnn_common.cuh"
 
 namespace frnn {

@@ -14,7 +14,7 @@
 // All CTAs of the launch must be resident at the same time (cooperative launch).
 //
 // Same arithmetic as reference.recurrence (flashrnn/flashrnn2/reference.py:72-114); the 2-D
-// decomposition follows the idea of the reference's hybrid kernel (csrc/hybrid_fw2d.cu:404-419).
+// decomposition follows the idea of the reference's hybrid kernel (flashrnn/flashrnn2/hybrid_fw2d.cu:404-419).
 #include "frnn_common.cuh"
 
 namespace frnn {

@@ -117,6 +117,7 @@ def main(argv) -> None:
     shapes = [("lstm", 8, 256, 1, 64), ("lstm", 8, 1024, 3, 256), ("slstm", 16, 2048, 4, 128)]
     for cell in ("lstm", "gru", "elman"):
         shapes += [(cell, 16, 1024, n, d) for d, n in HEAD_DIM_SWEEP]
+    shapes += [("lstm", 16, 1024, 1, 1024), ("gru", 16, 1024, 1, 1024), ("lstm", 8, 512, 1, 1536)]  # wider than the sweep
     shapes += [("lstm", 256, 2048, 4, 128)]  # one GPU's share of N32 D128 B256 T2048 with the 32 heads split over 8 GPUs
     from .cudnn_baseline import time_cudnn
 

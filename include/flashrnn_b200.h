@@ -19,7 +19,7 @@
  * (MMA warp: operand wait, issue).
  * Test hook for the failure path: with err[4] = 1 the CTAs stop publishing their per-step exchange
  * data from step err[5] on, so the next bounded wait (limit = wait_limit_ms) runs out and the call
- * reports err[0] = 101 (forward) / 106 (backward) and returns normally.
+ * reports err[0] = 101 (forward) / 106 or 107 (backward) and returns normally.
  *
  * Counterparts in the reference (0z5a/flashrnn):
  *   flashrnn/flashrnn/fused/flashrnn.cc:56-347      pybind class FlashRNNFuncFused

@@ -35,8 +35,12 @@ def test_plan_describes_the_headline_workload():
     wide = _lib.plan("lstm", 16, 8, 1, 768)                  # wider than a cluster: global-memory exchange
     assert wide.supported and wide.exchange == 1 and wide.cluster == 24 and wide.xchg_bytes > 0
     assert wide.fwd_ksplit == 2 and wide.fwd_ctas == 2 * 48   # the forward splits the contraction over two CTAs per row tile
+    assert wide.bwd_ksplit == 4                               # the backward owns columns of R: 6 unit tiles x 4 chunks of the 3072 gate rows
     wider = _lib.plan("lstm", 8, 8, 1, 1024)                   # rows of R beyond one CTA's tensor memory: 16-unit backward slices
     assert wider.supported and wider.exchange == 2 and wider.unit == 16 and wider.cluster == 64 and wider.fwd_ksplit == 2
+    assert wider.bwd_ksplit == 8 and wider.xchg_bytes >= 4 * 16 * 4096 * 2
+    odd = _lib.plan("lstm", 8, 8, 1, 960)                      # not a multiple of 128: 1-D backward with 16-unit slices
+    assert odd.supported and odd.exchange == 2 and odd.bwd_ksplit == 0 and odd.cluster == 60
     assert not _lib.plan("lstm", 8, 8, 1, 2048).supported     # R no longer fits in the tensor memory of one launch
     assert not _lib.plan("lstm", 64, 8, 1, 1024).supported    # more CTAs than SMs cannot wait on one another
     assert not _lib.plan("lstm", 8, 8, 1, 40).supported       # the ABI wants D % 16 == 0 (Python pads)

@@ -88,3 +88,18 @@ def test_shard_range_and_axis():
     assert sharding.choose_axis(256, 32, 8) == "heads" and sharding.choose_axis(8, 3, 2) == "batch"
     with pytest.raises(ValueError):
         sharding.shard_range(4, 2, 2)
+
+
+def test_sharded_call_wants_the_axis_and_a_cuda_device():
+    import torch
+
+    from flashrnn_b200 import sharding
+    from flashrnn_b200.workloads import make_inputs
+
+    wx, R, b, init = make_inputs("lstm", 2, 3, 2, 16, 5)
+    with pytest.raises(ValueError, match="axis"):
+        sharding.flashrnn_sharded(wx, R, b, init, function="lstm")
+    with pytest.raises(ValueError, match="axis"):
+        sharding.flashrnn_sharded(wx, R, b, init, function="lstm", axis="time")
+    with pytest.raises(RuntimeError, match="CUDA"):     # there is no CPU path behind the sharded call either
+        sharding.flashrnn_sharded(wx, R, b, init, function="lstm", axis="heads", dtype="float32")
