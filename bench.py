@@ -42,7 +42,7 @@ FLOP_WGRAD = 2 * GR * D * D * N * B * T        # dR contraction
 CPU_SAMPLE_T = 128                              # bounded CPU sample: same B, N, D, first 128 steps
 # dram__bytes_read.sum + dram__bytes_write.sum per launch on this workload, from the ncu capture summarised in
 # profiles/recurrence_kernels_cfg2_lstm_bf16_B8_T1024_N3_D256.md
-NCU_TRAFFIC_BYTES = {"fwd": 52.5e6 + 109.1e6, "bwd": 203.1e6 + 75.0e6, "wgrad": 63.0e6 + 2.0e6}
+NCU_TRAFFIC_BYTES = {"fwd": 52.0e6 + 107.0e6, "bwd": 203.1e6 + 74.9e6, "wgrad": 63.0e6 + 3.2e6}
 
 
 def _peaks():
@@ -364,17 +364,24 @@ def kernel_breakdown(_lib, dev, d_wx, d_R, d_b, d_init, flush, reps):
     if int(err[0].item()) != 0:
         raise RuntimeError(f"device-side error {err.tolist()}")
     # in-kernel phase timers of CTA 0 (SM cycles per step)
-    names = ("input_wait", "operand_or_mma_wait", "acc_read_or_cell", "sync_or_mma_wait", "cell_exchange_or_scatter")
+    # err[8..15] are the epilogue warps' phases, err[16..18] the MMA warp's (see the kernels' `prof` blocks)
+    names = {
+        "fwd": ("wx_stage_wait", "mma_wait", "tmem_read", "epilogue_barrier", "cell", "push_h", "state_stores",
+                "commit_to_epilogue"),
+        "bwd": ("stage_wait_and_read", "partial_wait_and_sum", "cell", "stores_and_first_tile_wait", "scatter",
+                "partial_wait_only", "stage_wait_only", None),
+    }
     for name, fn in (("fwd", fwd), ("bwd", bwd)):
         err.zero_()
         err[3] = 1
         fn()
         torch.cuda.synchronize()
         v = err.tolist()
-        out[name + "_phase_cycles_per_step"] = {**{k: round(v[8 + i] / T, 1) for i, k in enumerate(names)},
-                                                "x5": round(v[13] / T, 1), "x6": round(v[14] / T, 1),
-                                                "commit_to_epilogue": round(v[15] / T, 1), "push_to_mma_wake": round(v[18] / T, 1),
-                                                "mma_warp_wait": round(v[16] / T, 1), "mma_warp_issue": round(v[17] / T, 1)}
+        phases = {k: round(v[8 + i] / T, 1) for i, k in enumerate(names[name]) if k is not None}
+        phases.update({"mma_warp_wait": round(v[16] / T, 1), "mma_warp_issue": round(v[17] / T, 1)})
+        if name == "fwd":
+            phases["push_to_mma_wake"] = round(v[18] / T, 1)
+        out[name + "_phase_cycles_per_step"] = phases
     err.zero_()
     return out
 
