@@ -11,6 +11,7 @@ namespace frnn {
 int forward_dispatch(int cell, const FwdParams& p, const void* wx, int wx_bf16, int bv, int unit, cudaStream_t s);
 int forward_ksplit_dispatch(int cell, const FwdParams& p, const void* wx, int wx_bf16, int bv, int ksplit, cudaStream_t s);
 int backward_ksplit_width(int gates_r, int D);
+bool backward_ksplit_valid(int cell, int gates_r, int D, int ks);
 int backward_ksplit_dispatch(int cell, const BwdParams& p, const float* cache, const float* history, const float* initial,
                              const float* d_history, int wx_bf16, int bv, int ksplit, cudaStream_t s, int* capacity_only);
 int backward_ksplit_capacity(int cell, int bv, int ksplit, int D);
@@ -167,7 +168,17 @@ extern "C" int frnn_b200_plan(int cell, int B, int T, int N, int D, frnn_b200_pl
     // hold fewer CTAs than there are SMs; where it does not fit, the 1-D backward is used.
     const int slice_ctas = out->cluster;
     const int tile0 = out->batch_tile;
-    for (int bks = bks_width; ; bks = 0) {
+    // candidates for the backward, best first: the widest split of the gate rows that fits (shortest
+    // tensor-core chain per step), first without giving up 8-row batch tiles, then with 16-row tiles;
+    // last the 1-D backward
+    int cand[8], ncand = 0;
+    for (int pass = 0; pass < 2 && bks_width > 0; ++pass)
+      for (int ks = 8; ks >= 2; ks /= 2)
+        if (backward_ksplit_valid(cell, c.gr, D, ks)) cand[ncand++] = pass == 0 ? ks : -ks;
+    cand[ncand++] = 0;
+    for (int ci = 0; ci < ncand; ++ci) {
+      const bool keep_tile = cand[ci] > 0;
+      const int bks = cand[ci] > 0 ? cand[ci] : -cand[ci];
       out->batch_tile = tile0;
       const bool fsplit = D % 64 == 0 && D / 2 <= 896;
       const int fwd_per_group = fsplit ? D / 16 : slice_ctas;
@@ -193,7 +204,8 @@ extern "C" int frnn_b200_plan(int cell, int B, int T, int N, int D, frnn_b200_pl
       const int64_t bwd_b = bks ? 4ll * bt * c.gr * D * 2                                              // four slots of dG
                                 : 2ll * out->cluster * out->cluster * out->unit * out->batch_tile * 4;  // two slots of partial dh
       out->xchg_bytes = 4096 + groups * 512ll + groups * (fwd_b > bwd_b ? fwd_b : bwd_b);
-      if (out->supported || bks == 0) break;
+      if (out->supported && keep_tile && out->batch_tile != tile0) out->supported = 0;  // a later candidate may keep the tile
+      if (out->supported) break;
     }
   }
   const int64_t btnd = static_cast<int64_t>(B) * T * N * D;

@@ -620,6 +620,15 @@ int backward_ksplit_width(int gates_r, int D) {
     if (K % (ks * 16) == 0 && K / ks <= kMaxKc) return ks;
   return 0;
 }
+// Can the gate rows be split over exactly `ks` CTAs (a wider split than necessary shortens the
+// tensor-core chain of a step and the operand chunk every CTA has to fetch)?
+bool backward_ksplit_valid(int cell, int gates_r, int D, int ks) {
+  if (D % 128 != 0 || (ks != 2 && ks != 4 && ks != 8)) return false;
+  if (ks == 2 && gates_r != 1) return false;  // two chunks are only compiled for the single-gate cell
+  const int K = gates_r * D;
+  (void)cell;
+  return K % (ks * 16) == 0 && K / ks <= kMaxKc;
+}
 
 int backward_ksplit_dispatch(int cell, const BwdParams& p, const float* cache, const float* history,
                              const float* initial, const float* d_history, int wx_bf16, int bv, int ksplit,

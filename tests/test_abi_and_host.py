@@ -33,9 +33,11 @@ def test_plan_describes_the_headline_workload():
     big = _lib.plan("lstm", 256, 16, 32, 128)                # more groups than SMs: 16-row batch tiles
     assert (big.batch_tile, big.n_btiles, big.cluster) == (16, 16, 4)
     wide = _lib.plan("lstm", 16, 8, 1, 768)                  # wider than a cluster: global-memory exchange
-    assert wide.supported and wide.exchange == 1 and wide.cluster == 24 and wide.xchg_bytes > 0
+    assert wide.supported and wide.exchange == 1 and wide.xchg_bytes > 0
     assert wide.fwd_ksplit == 2 and wide.fwd_ctas == 2 * 48   # the forward splits the contraction over two CTAs per row tile
-    assert wide.bwd_ksplit == 4                               # the backward owns columns of R: 6 unit tiles x 4 chunks of the 3072 gate rows
+    assert wide.bwd_ksplit == 8 and wide.cluster == 6 * 8      # the backward owns columns of R: 6 unit tiles x 8 chunks of the 3072 gate rows
+    many = _lib.plan("lstm", 64, 8, 1, 768)                    # four 16-row groups: only the narrower split fits the SMs
+    assert many.supported and many.batch_tile == 16 and many.bwd_ksplit == 4 and many.fwd_ctas == 4 * 24
     wider = _lib.plan("lstm", 8, 8, 1, 1024)                   # rows of R beyond one CTA's tensor memory: 16-unit backward slices
     assert wider.supported and wider.exchange == 2 and wider.unit == 16 and wider.cluster == 64 and wider.fwd_ksplit == 2
     assert wider.bwd_ksplit == 8 and wider.xchg_bytes >= 4 * 16 * 4096 * 2
