@@ -40,7 +40,7 @@ class Plan(ctypes.Structure):
         ("supported", c_int),
         ("cache_bytes", c_int64), ("hbf_bytes", c_int64), ("dgr_bytes", c_int64), ("dbpart_bytes", c_int64),
         ("wgrad_work_bytes", c_int64), ("wgrad_ksplit", c_int), ("exchange", c_int), ("xchg_bytes", c_int64),
-        ("fwd_ksplit", c_int), ("fwd_ctas", c_int), ("bwd_ksplit", c_int),
+        ("fwd_ksplit", c_int), ("fwd_ctas", c_int), ("bwd_ksplit", c_int), ("fwd_batch_tile", c_int),
     ]
 
 

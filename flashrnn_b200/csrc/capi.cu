@@ -9,7 +9,9 @@
 namespace frnn {
 
 int forward_dispatch(int cell, const FwdParams& p, const void* wx, int wx_bf16, int bv, int unit, cudaStream_t s);
-int forward_ksplit_dispatch(int cell, const FwdParams& p, const void* wx, int wx_bf16, int bv, int ksplit, cudaStream_t s);
+int forward_ksplit_dispatch(int cell, const FwdParams& p, const void* wx, int wx_bf16, int bv, int ksplit, cudaStream_t s,
+                            int* capacity_only);
+int forward_ksplit_capacity(int cell, int bv, int ksplit, int D);
 int backward_ksplit_width(int gates_r, int D);
 bool backward_ksplit_valid(int cell, int gates_r, int D, int ks);
 int backward_ksplit_dispatch(int cell, const BwdParams& p, const float* cache, const float* history, const float* initial,
@@ -56,22 +58,25 @@ int sm_count() {
 
 // CTAs of the clustered backward launch that the device can hold at once, remembered per shape
 // class (the query is a driver call and the plan is computed on every call).
-int bwd_ksplit_capacity_cached(int cell, int bv, int ks, int D) {
-  struct Entry { int cell, bv, ks, D, cap; };
+int ksplit_capacity_cached(bool forward, int cell, int bv, int ks, int D) {
+  struct Entry { int fwd, cell, bv, ks, D, cap; };
   static std::mutex mu;
-  static Entry table[32];
+  static Entry table[64];
   static int used = 0;
   std::lock_guard<std::mutex> lock(mu);
   for (int i = 0; i < used; ++i)
-    if (table[i].cell == cell && table[i].bv == bv && table[i].ks == ks && table[i].D == D) return table[i].cap;
-  int cap = backward_ksplit_capacity(cell, bv, ks, D);
+    if (table[i].fwd == static_cast<int>(forward) && table[i].cell == cell && table[i].bv == bv && table[i].ks == ks &&
+        table[i].D == D)
+      return table[i].cap;
+  int cap = forward ? forward_ksplit_capacity(cell, bv, ks, D) : backward_ksplit_capacity(cell, bv, ks, D);
   if (cap <= 0) {
     cudaGetLastError();
     cap = sm_count() / ks * ks;  // no device visible: assume every SM can take part
   }
-  if (used < 32) table[used++] = Entry{cell, bv, ks, D, cap};
+  if (used < 64) table[used++] = Entry{static_cast<int>(forward), cell, bv, ks, D, cap};
   return cap;
 }
+int bwd_ksplit_capacity_cached(int cell, int bv, int ks, int D) { return ksplit_capacity_cached(false, cell, bv, ks, D); }
 
 struct CellCounts {
   int gr, gw, gb, s, gc;
@@ -160,53 +165,69 @@ extern "C" int frnn_b200_plan(int cell, int B, int T, int N, int D, frnn_b200_pl
     out->supported = slices16_fit || bks_width > 0;
   }
   out->fwd_ctas = out->grid_ctas;
+  out->fwd_batch_tile = out->batch_tile;
   if (out->exchange && out->supported) {
-    // All CTAs of such a launch wait on one another: they must be resident together. Where the width
-    // allows it the forward splits the contraction over two CTAs per 32-unit row tile and the
-    // backward owns columns of R (128-unit tiles x K-chunks); both shorten the tensor-core chain of
-    // a step and exchange bf16 operands instead of fp32 partial sums. The clustered backward can
-    // hold fewer CTAs than there are SMs; where it does not fit, the 1-D backward is used.
+    // All CTAs of such a launch wait on one another: they must be resident together. Forward and
+    // backward are separate launches and choose their decomposition and batch tile independently.
     const int slice_ctas = out->cluster;
-    const int tile0 = out->batch_tile;
-    // candidates for the backward, best first: the widest split of the gate rows that fits (shortest
-    // tensor-core chain per step), first without giving up 8-row batch tiles, then with 16-row tiles;
-    // last the 1-D backward
-    int cand[8], ncand = 0;
-    for (int pass = 0; pass < 2 && bks_width > 0; ++pass)
-      for (int ks = 8; ks >= 2; ks /= 2)
-        if (backward_ksplit_valid(cell, c.gr, D, ks)) cand[ncand++] = pass == 0 ? ks : -ks;
-    cand[ncand++] = 0;
-    for (int ci = 0; ci < ncand; ++ci) {
-      const bool keep_tile = cand[ci] > 0;
-      const int bks = cand[ci] > 0 ? cand[ci] : -cand[ci];
-      out->batch_tile = tile0;
-      const bool fsplit = D % 64 == 0 && D / 2 <= 896;
-      const int fwd_per_group = fsplit ? D / 16 : slice_ctas;
-      const int bwd_per_group = bks ? (D / 128) * bks : slice_ctas;
-      const int per_group = fwd_per_group > bwd_per_group ? fwd_per_group : bwd_per_group;
-      const long long groups8 = static_cast<long long>(N) * ((B + 7) / 8);
-      if (groups8 * per_group > sm_count() || (bks && groups8 * bwd_per_group > bwd_ksplit_capacity_cached(cell, 8, bks, D)))
-        out->batch_tile = 16;
-      out->n_btiles = (B + out->batch_tile - 1) / out->batch_tile;
-      const int groups = N * out->n_btiles;
-      out->fwd_ksplit = fsplit ? 2 : 0;
-      out->fwd_ctas = groups * fwd_per_group;
-      out->bwd_ksplit = bks;
-      out->cluster = bwd_per_group;
-      out->grid_ctas = groups * out->cluster;
-      if (out->fwd_ksplit && out->fwd_ctas > sm_count() && out->exchange == 1) {
-        out->fwd_ksplit = 0;  // not enough SMs for the split forward: one CTA per 32 units
-        out->fwd_ctas = groups * (D / 32);
+    const int sms = sm_count();
+    // Forward, best first: contraction of a 32-unit row tile split over 4 or 2 CTAs (shorter tensor-core
+    // chain per step) with 8-row batch tiles, then the same with 16-row tiles (about a quarter more
+    // time per step), last one CTA per 32 units (only while its rows of R fit tensor memory).
+    bool fwd_ok = false;
+    for (int tile = 8; tile <= 16 && !fwd_ok; tile += 8) {
+      if (tile == 16 && B <= 8) break;
+      const int groups = N * ((B + tile - 1) / tile);
+      for (int ks = 4; ks >= 2 && !fwd_ok; ks /= 2) {
+        if (D % 32 != 0 || D % ks != 0 || (D / ks) % 16 != 0 || D / ks > 896) continue;
+        if (groups * (D / 32) * ks > ksplit_capacity_cached(true, cell, tile, ks, D)) continue;
+        out->fwd_ksplit = ks;
+        out->fwd_batch_tile = tile;
+        out->fwd_ctas = groups * (D / 32) * ks;
+        fwd_ok = true;
       }
-      const int bwd_cap = bks ? bwd_ksplit_capacity_cached(cell, out->batch_tile, bks, D) : sm_count();
-      out->supported = out->grid_ctas <= bwd_cap && out->fwd_ctas <= sm_count() && (bks > 0 || slices16_fit);
-      const int64_t fwd_b = 4ll * bt * D * 2;  // four operand slots
-      const int64_t bwd_b = bks ? 4ll * bt * c.gr * D * 2                                              // four slots of dG
-                                : 2ll * out->cluster * out->cluster * out->unit * out->batch_tile * 4;  // two slots of partial dh
-      out->xchg_bytes = 4096 + groups * 512ll + groups * (fwd_b > bwd_b ? fwd_b : bwd_b);
-      if (out->supported && keep_tile && out->batch_tile != tile0) out->supported = 0;  // a later candidate may keep the tile
-      if (out->supported) break;
     }
+    for (int tile = 8; tile <= 16 && !fwd_ok && out->exchange == 1; tile += 8) {
+      const int groups = N * ((B + tile - 1) / tile);
+      if (groups * (D / 32) > sms) continue;
+      out->fwd_ksplit = 0;
+      out->fwd_batch_tile = tile;
+      out->fwd_ctas = groups * (D / 32);
+      fwd_ok = true;
+    }
+    // Backward, best first: columns of R in 128-unit tiles with the gate rows split over 8, 4 or 2 CTAs
+    // (the widest split that fits: shortest tensor-core chain per step), first with 8-row batch tiles,
+    // then with 16-row tiles; last the 1-D backward (32- or 16-unit slices of rows of R).
+    bool bwd_ok = false;
+    for (int tile = 8; tile <= 16 && !bwd_ok && bks_width > 0; tile += 8) {
+      if (tile == 16 && B <= 8) break;
+      const int groups = N * ((B + tile - 1) / tile);
+      for (int ks = 8; ks >= 2 && !bwd_ok; ks /= 2) {
+        if (!backward_ksplit_valid(cell, c.gr, D, ks)) continue;
+        if (groups * (D / 128) * ks > bwd_ksplit_capacity_cached(cell, tile, ks, D)) continue;
+        out->bwd_ksplit = ks;
+        out->batch_tile = tile;
+        out->cluster = (D / 128) * ks;
+        bwd_ok = true;
+      }
+    }
+    for (int tile = 8; tile <= 16 && !bwd_ok && slices16_fit; tile += 8) {
+      const int groups = N * ((B + tile - 1) / tile);
+      if (groups * slice_ctas > sms) continue;
+      out->bwd_ksplit = 0;
+      out->batch_tile = tile;
+      out->cluster = slice_ctas;
+      bwd_ok = true;
+    }
+    out->n_btiles = (B + out->batch_tile - 1) / out->batch_tile;
+    out->grid_ctas = N * out->n_btiles * out->cluster;
+    out->supported = fwd_ok && bwd_ok;
+    const int64_t fwd_groups = static_cast<int64_t>(N) * ((B + out->fwd_batch_tile - 1) / out->fwd_batch_tile);
+    const int64_t bwd_groups = static_cast<int64_t>(N) * out->n_btiles;
+    const int64_t fwd_b = 4ll * bt * D * 2;  // four operand slots
+    const int64_t bwd_b = out->bwd_ksplit ? 4ll * bt * c.gr * D * 2                                        // four slots of dG
+                                          : 2ll * out->cluster * out->cluster * out->unit * out->batch_tile * 4;  // two slots of partial dh
+    out->xchg_bytes = fwd_groups * fwd_b > bwd_groups * bwd_b ? fwd_groups * fwd_b : bwd_groups * bwd_b;
   }
   const int64_t btnd = static_cast<int64_t>(B) * T * N * D;
   out->cache_bytes = btnd * c.gc * 4;
@@ -243,21 +264,20 @@ extern "C" int frnn_b200_forward(int cell, const void* wx, int wx_bf16, const vo
   p.err = err;
   p.B = B; p.T = T; p.N = N; p.D = D;
   p.C = plan.cluster;
-  p.wx_box_b = plan.batch_tile;  // rows past B are filled with zeros by TMA
+  p.wx_box_b = plan.fwd_batch_tile;  // rows past B are filled with zeros by TMA
   p.slstm_zero_first = slstm_zero_first;
   p.wait_limit_ns = (wait_limit_ms > 0 ? static_cast<unsigned long long>(wait_limit_ms) : 2000ull) * 1000000ull;
   if (plan.exchange) {
     if (!xchg) return -5;
-    const size_t counters = static_cast<size_t>(N) * plan.n_btiles * 512;
     // every exchange word starts as "not yet written" (all ones)
     const cudaError_t me = cudaMemsetAsync(xchg, 0xff, static_cast<size_t>(plan.xchg_bytes), static_cast<cudaStream_t>(stream));
     if (me != cudaSuccess) return static_cast<int>(me);
-    p.xg_counters = static_cast<uint32_t*>(xchg);
-    p.xg_data = static_cast<uint8_t*>(xchg) + ((counters + 4095) & ~static_cast<size_t>(4095));
+    p.xg_data = static_cast<uint8_t*>(xchg);
   }
   if (plan.fwd_ksplit)
-    return forward_ksplit_dispatch(cell, p, wx, wx_bf16, plan.batch_tile, 2, static_cast<cudaStream_t>(stream));
-  return forward_dispatch(cell, p, wx, wx_bf16, plan.batch_tile, plan.unit, static_cast<cudaStream_t>(stream));
+    return forward_ksplit_dispatch(cell, p, wx, wx_bf16, plan.fwd_batch_tile, plan.fwd_ksplit, static_cast<cudaStream_t>(stream),
+                                   nullptr);
+  return forward_dispatch(cell, p, wx, wx_bf16, plan.fwd_batch_tile, plan.exchange ? 32 : plan.unit, static_cast<cudaStream_t>(stream));
 }
 
 extern "C" int frnn_b200_backward(int cell, const float* cache, const float* history, const float* initial,
@@ -286,11 +306,9 @@ extern "C" int frnn_b200_backward(int cell, const float* cache, const float* his
   p.wait_limit_ns = (wait_limit_ms > 0 ? static_cast<unsigned long long>(wait_limit_ms) : 2000ull) * 1000000ull;
   if (plan.exchange) {
     if (!xchg) return -5;
-    const size_t counters = static_cast<size_t>(N) * plan.n_btiles * 512;
     const cudaError_t me = cudaMemsetAsync(xchg, 0xff, static_cast<size_t>(plan.xchg_bytes), static_cast<cudaStream_t>(stream));
     if (me != cudaSuccess) return static_cast<int>(me);
-    p.xg_counters = static_cast<uint32_t*>(xchg);
-    p.xg_data = static_cast<uint8_t*>(xchg) + ((counters + 4095) & ~static_cast<size_t>(4095));
+    p.xg_data = static_cast<uint8_t*>(xchg);
   }
   if (plan.bwd_ksplit)
     return backward_ksplit_dispatch(cell, p, cache, history, initial, d_history, wx_bf16, plan.batch_tile,

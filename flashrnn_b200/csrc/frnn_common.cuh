@@ -51,9 +51,8 @@ struct FwdParams {
   int slstm_zero_first;
   unsigned long long wait_limit_ns;
   // Exchange through global memory (groups wider than a cluster), null for cluster exchange:
-  // per group two parity copies of the operand buffer, and two arrival counters 256 B apart.
+  // per group four slots of the bf16 operand (the data words double as arrival flags).
   uint8_t* xg_data;
-  uint32_t* xg_counters;
 };
 
 struct BwdParams {
@@ -69,10 +68,10 @@ struct BwdParams {
   int box_b;
   int slstm_zero_first;
   unsigned long long wait_limit_ns;
-  // Exchange through global memory, null for cluster exchange: per group two parity copies of
-  // the partial-dh blocks [dest CTA][source CTA][unit][padded batch] and two arrival counters.
+  // Exchange through global memory, null for cluster exchange: per group two slots of the
+  // partial-dh blocks [dest CTA][source CTA][batch][unit] (1-D backward, phase bit in every word) or
+  // four slots of the bf16 dG operand (backward that owns columns of R).
   uint8_t* xg_data;
-  uint32_t* xg_counters;
 };
 
 template <int N>

@@ -199,6 +199,7 @@ frnn_bwd_kernel(const BwdParams p, const __grid_constant__ CUtensorMap cache_map
       const uint32_t idesc = umma_idesc_bf16(128, BT, false, false);
       const uint32_t db_addr = smem_u32(dgbuf);
       long long pw = 0, pi = 0;
+      int committed = 0;  // iterations whose tcgen05.mma have been issued and committed
       for (int it = 0; it < T; ++it) {
         const long long m0 = prof ? clock64() : 0;
         if (!mbar_wait_bounded<false, true>(smem_u32(&s_dg_bar), it & 1, limit, abort_flag)) {
@@ -216,8 +217,15 @@ frnn_bwd_kernel(const BwdParams p, const __grid_constant__ CUtensorMap cache_map
           // are still on the tensor core
           umma_commit(smem_u32(&s_mma_bar[j]));
         }
+        ++committed;
         if (prof) { pw += m1 - m0; pi += clock64() - m1; }
       }
+      // Before the CTA may release its tensor memory and shared memory every issued tcgen05.mma must
+      // have finished. Normally the epilogue has waited for the last commit already; after a failed
+      // wait it has not (it stops waiting), so the issuing thread waits here itself. The commit
+      // completes without any other party, hence no abort flag and a plain bound.
+      if (committed > 0)
+        mbar_wait_bounded<false, true>(smem_u32(&s_mma_bar[MTB - 1]), (committed - 1) & 1, limit, nullptr);
       if (prof) { p.err[16] = static_cast<int>(pw); p.err[17] = static_cast<int>(pi); }
     }
   } else if (warp == 5) {
@@ -362,6 +370,9 @@ frnn_bwd_kernel(const BwdParams p, const __grid_constant__ CUtensorMap cache_map
                 }
             }
           }
+          // a wait that ran out in some lanes only must not leave the warp divided: the warp-wide
+          // tcgen05.ld of the next step needs all lanes on one path
+          dead = __any_sync(0xffffffffu, dead);
           if (prof) pc5 += clock64() - c1;
         } else if (!dead && !mbar_wait_bounded<true, true>(smem_u32(&s_part_bar[pb]), ((it - 1) >> 1) & 1, limit, abort_flag)) {
           report(p.err, kErrWaitPart, it);

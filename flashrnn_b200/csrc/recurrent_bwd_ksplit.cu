@@ -191,6 +191,7 @@ frnn_bwd_ks_kernel(const BwdParams p, const __grid_constant__ CUtensorMap cache_
     if (lane == 0) {
       const uint32_t idesc = umma_idesc_bf16(128, BT, false, false);
       long long pw = 0, pi = 0;
+      int committed = 0;  // steps whose tcgen05.mma have been issued and committed
       for (int it = 0; it < T; ++it) {
         const int pb = it & 1;
         const long long m0 = prof ? clock64() : 0;
@@ -207,8 +208,14 @@ frnn_bwd_ks_kernel(const BwdParams p, const __grid_constant__ CUtensorMap cache_
           umma_bf16_ts(tbase, tbase + Cfg::A_COL0 + kk * 8, bdesc, idesc, kk > 0 ? 1u : 0u);
         }
         umma_commit(smem_u32(&s_mma_bar));
+        ++committed;
         if (prof) { pw += m1 - m0; pi += clock64() - m1; }
       }
+      // Before the CTA may release its tensor memory and shared memory every issued tcgen05.mma must
+      // have finished. Normally the epilogue has waited for the last commit already; after a failed
+      // wait it has not (it stops waiting), so the issuing thread waits here itself. The commit
+      // completes without any other party, hence no abort flag and a plain bound.
+      if (committed > 0) mbar_wait_bounded<false, true>(smem_u32(&s_mma_bar), (committed - 1) & 1, limit, nullptr);
       if (prof) { p.err[16] = static_cast<int>(pw); p.err[17] = static_cast<int>(pi); }
     }
   } else if (warp == 5) {
@@ -456,6 +463,9 @@ frnn_bwd_ks_kernel(const BwdParams p, const __grid_constant__ CUtensorMap cache_
             }
           }
         }
+        // a wait that ran out in some lanes only must not leave the warp divided: the warp-wide
+        // tcgen05.ld of the next step needs all lanes on one path
+        dead = __any_sync(0xffffffffu, dead);
         fence_proxy_async_smem();
         mbar_arrive(smem_u32(&s_dg_bar[pb]));
         fence_acq_rel_gpu();

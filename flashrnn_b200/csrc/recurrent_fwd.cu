@@ -179,6 +179,7 @@ frnn_fwd_kernel(const FwdParams p, const __grid_constant__ CUtensorMap wx_map) {
     if (lane == 0) {
       const uint32_t idesc = umma_idesc_bf16(128, BT, false, false);
       long long pw = 0, pi = 0, px = 0, pf = 0;
+      int committed = 0;  // steps whose tcgen05.mma have been issued and committed
       for (int t = 0; t < T; ++t) {
         const int pb = t & 1;
         const long long m0 = prof ? clock64() : 0;
@@ -202,6 +203,7 @@ frnn_fwd_kernel(const FwdParams p, const __grid_constant__ CUtensorMap wx_map) {
           }
         }
         umma_commit(smem_u32(&s_mma_bar));
+        ++committed;
         // arm this parity's operand barrier for its next use (step t + 2), after the issue so that it
         // is off the critical path; its current phase has completed (we waited for it above)
         if (!xg && t >= 1 && t + 2 <= T - 1) mbar_arrive_expect_tx(smem_u32(&s_hbar[pb]), h_tx_bytes);
@@ -212,6 +214,11 @@ frnn_fwd_kernel(const FwdParams p, const __grid_constant__ CUtensorMap wx_map) {
           *reinterpret_cast<volatile long long*>(&s_prof_clk[0]) = m2;
         }
       }
+      // Before the CTA may release its tensor memory and shared memory every issued tcgen05.mma must
+      // have finished. Normally the epilogue has waited for the last commit already; after a failed
+      // wait it has not (it stops waiting), so the issuing thread waits here itself. The commit
+      // completes without any other party, hence no abort flag and a plain bound.
+      if (committed > 0) mbar_wait_bounded<false, true>(smem_u32(&s_mma_bar), (committed - 1) & 1, limit, nullptr);
       if (prof) { p.err[16] = static_cast<int>(pw); p.err[17] = static_cast<int>(pi); p.err[18] = static_cast<int>(px); p.err[19] = static_cast<int>(pf); }
     }
   } else if (warp == 5) {
@@ -425,6 +432,9 @@ frnn_fwd_kernel(const FwdParams p, const __grid_constant__ CUtensorMap wx_map) {
             }
           }
         }
+        // a wait that ran out in some lanes only must not leave the warp divided: the warp-wide
+        // tcgen05.ld of the next step needs all lanes on one path
+        dead = __any_sync(0xffffffffu, dead);
         fence_proxy_async_smem();
         mbar_arrive(smem_u32(&s_hbar[(t + 1) & 1]));
         fence_acq_rel_gpu();  // orders this step's refill and observations before the next step's (see above)

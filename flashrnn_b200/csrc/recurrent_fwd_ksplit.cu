@@ -179,6 +179,7 @@ frnn_fwd_ks_kernel(const FwdParams p, const __grid_constant__ CUtensorMap wx_map
     if (lane == 0) {
       const uint32_t idesc = umma_idesc_bf16(128, BT, false, false);
       long long pw = 0, pi = 0;
+      int committed = 0;  // steps whose tcgen05.mma have been issued and committed
       for (int t = 0; t < T; ++t) {
         const int pb = t & 1;
         const long long m0 = prof ? clock64() : 0;
@@ -195,8 +196,14 @@ frnn_fwd_ks_kernel(const FwdParams p, const __grid_constant__ CUtensorMap wx_map
           umma_bf16_ts(tbase, tbase + Cfg::A_COL0 + kk * 8, bdesc, idesc, kk > 0 ? 1u : 0u);
         }
         umma_commit(smem_u32(&s_mma_bar));
+        ++committed;
         if (prof) { pw += m1 - m0; pi += clock64() - m1; }
       }
+      // Before the CTA may release its tensor memory and shared memory every issued tcgen05.mma must
+      // have finished. Normally the epilogue has waited for the last commit already; after a failed
+      // wait it has not (it stops waiting), so the issuing thread waits here itself. The commit
+      // completes without any other party, hence no abort flag and a plain bound.
+      if (committed > 0) mbar_wait_bounded<false, true>(smem_u32(&s_mma_bar), (committed - 1) & 1, limit, nullptr);
       if (prof) { p.err[16] = static_cast<int>(pw); p.err[17] = static_cast<int>(pi); }
     }
   } else if (warp == 5) {
@@ -374,6 +381,9 @@ frnn_fwd_ks_kernel(const FwdParams p, const __grid_constant__ CUtensorMap wx_map
             }
           }
         }
+        // a wait that ran out in some lanes only must not leave the warp divided: the warp-wide
+        // tcgen05.ld of the next step needs all lanes on one path
+        dead = __any_sync(0xffffffffu, dead);
         fence_proxy_async_smem();
         mbar_arrive(smem_u32(&s_hbar[(t + 1) & 1]));
         fence_acq_rel_gpu();
@@ -426,10 +436,11 @@ frnn_fwd_ks_kernel(const FwdParams p, const __grid_constant__ CUtensorMap wx_map
 }
 
 template <int CELL, int BV, int KS, bool WX_BF16>
-int launch_fwd_ks(const FwdParams& p, const void* wx, cudaStream_t stream) {
+int launch_fwd_ks(const FwdParams& p, const void* wx, cudaStream_t stream, int* capacity_only = nullptr) {
   using Cfg = KsCfg<CELL, BV, KS, WX_BF16>;
   using CT = typename Cfg::CT;
-  if (p.D % (32 * KS) != 0 || p.D / KS > kMaxKc || p.xg_data == nullptr) return -2;
+  if (p.D % 32 != 0 || p.D % KS != 0 || (p.D / KS) % 16 != 0 || p.D / KS > kMaxKc) return -2;
+  if (capacity_only == nullptr && p.xg_data == nullptr) return -2;
   const int Kc = p.D / KS;
   const int hbuf_bytes = Cfg::BT * Kc * 2;
   const int smem = ((2 * hbuf_bytes + 2 * Cfg::PART_BYTES + 127) & ~127) + kWxStages * Cfg::WX_STAGE_BYTES;
@@ -437,7 +448,7 @@ int launch_fwd_ks(const FwdParams& p, const void* wx, cudaStream_t stream) {
   const uint64_t dims[5] = {static_cast<uint64_t>(p.D), static_cast<uint64_t>(p.N), static_cast<uint64_t>(CT::GW),
                             static_cast<uint64_t>(p.T), static_cast<uint64_t>(p.B)};
   const uint32_t box[5] = {static_cast<uint32_t>(Cfg::UO), 1u, static_cast<uint32_t>(CT::GW), 1u, static_cast<uint32_t>(p.wx_box_b)};
-  if (make_tensor_map(&map, wx, Cfg::WX_ES, 5, dims, box) != 0) return -4;
+  if (capacity_only == nullptr && make_tensor_map(&map, wx, Cfg::WX_ES, 5, dims, box) != 0) return -4;
   auto kern = frnn_fwd_ks_kernel<CELL, BV, KS, WX_BF16>;
   cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, smem);
   if (e != cudaSuccess) return static_cast<int>(e);
@@ -461,30 +472,57 @@ int launch_fwd_ks(const FwdParams& p, const void* wx, cudaStream_t stream) {
   int max_clusters = 0;
   e = cudaOccupancyMaxActiveClusters(&max_clusters, kern, &cfg);
   if (e != cudaSuccess) return static_cast<int>(e);
+  if (capacity_only != nullptr) {
+    *capacity_only = max_clusters * KS;
+    return 0;
+  }
   if (max_clusters * KS < static_cast<int>(cfg.gridDim.x)) return -2;
   e = cudaLaunchKernelEx(&cfg, kern, p, map);
   return static_cast<int>(e);
 }
 
 template <int CELL, int KS>
-int launch_fwd_ks_cell(const FwdParams& p, const void* wx, int wx_bf16, int bv, cudaStream_t s) {
-  if (bv == 8) return wx_bf16 ? launch_fwd_ks<CELL, 8, KS, true>(p, wx, s) : launch_fwd_ks<CELL, 8, KS, false>(p, wx, s);
-  if (bv == 16) return wx_bf16 ? launch_fwd_ks<CELL, 16, KS, true>(p, wx, s) : launch_fwd_ks<CELL, 16, KS, false>(p, wx, s);
+int launch_fwd_ks_cell(const FwdParams& p, const void* wx, int wx_bf16, int bv, cudaStream_t s, int* cap) {
+  if (bv == 8) return wx_bf16 ? launch_fwd_ks<CELL, 8, KS, true>(p, wx, s, cap) : launch_fwd_ks<CELL, 8, KS, false>(p, wx, s, cap);
+  if (bv == 16) return wx_bf16 ? launch_fwd_ks<CELL, 16, KS, true>(p, wx, s, cap) : launch_fwd_ks<CELL, 16, KS, false>(p, wx, s, cap);
   return -2;
 }
 
 }  // namespace
 
 // Forward launch for heads split over row tiles and K-chunks (ksplit = CTAs per row tile).
-int forward_ksplit_dispatch(int cell, const FwdParams& p, const void* wx, int wx_bf16, int bv, int ksplit, cudaStream_t s) {
-  if (ksplit != 2) return -2;
-  switch (cell) {
-    case kLSTM: return launch_fwd_ks_cell<kLSTM, 2>(p, wx, wx_bf16, bv, s);
-    case kSLSTM: return launch_fwd_ks_cell<kSLSTM, 2>(p, wx, wx_bf16, bv, s);
-    case kGRU: return launch_fwd_ks_cell<kGRU, 2>(p, wx, wx_bf16, bv, s);
-    case kElman: return launch_fwd_ks_cell<kElman, 2>(p, wx, wx_bf16, bv, s);
-    default: return -1;
+int forward_ksplit_dispatch(int cell, const FwdParams& p, const void* wx, int wx_bf16, int bv, int ksplit, cudaStream_t s,
+                            int* capacity_only) {
+  if (ksplit == 2) {
+    switch (cell) {
+      case kLSTM: return launch_fwd_ks_cell<kLSTM, 2>(p, wx, wx_bf16, bv, s, capacity_only);
+      case kSLSTM: return launch_fwd_ks_cell<kSLSTM, 2>(p, wx, wx_bf16, bv, s, capacity_only);
+      case kGRU: return launch_fwd_ks_cell<kGRU, 2>(p, wx, wx_bf16, bv, s, capacity_only);
+      case kElman: return launch_fwd_ks_cell<kElman, 2>(p, wx, wx_bf16, bv, s, capacity_only);
+      default: return -1;
+    }
   }
+  if (ksplit == 4) {
+    switch (cell) {
+      case kLSTM: return launch_fwd_ks_cell<kLSTM, 4>(p, wx, wx_bf16, bv, s, capacity_only);
+      case kSLSTM: return launch_fwd_ks_cell<kSLSTM, 4>(p, wx, wx_bf16, bv, s, capacity_only);
+      case kGRU: return launch_fwd_ks_cell<kGRU, 4>(p, wx, wx_bf16, bv, s, capacity_only);
+      case kElman: return launch_fwd_ks_cell<kElman, 4>(p, wx, wx_bf16, bv, s, capacity_only);
+      default: return -1;
+    }
+  }
+  return -2;
+}
+
+// How many CTAs of the forward launch for this shape the device can hold at once (clusters are placed
+// inside one GPC, so this can be less than the SM count); <= 0 if unknown.
+int forward_ksplit_capacity(int cell, int bv, int ksplit, int D) {
+  FwdParams p{};
+  p.B = bv; p.T = 1; p.N = 1; p.D = D;
+  p.wx_box_b = bv;
+  int cap = 0;
+  const int rc = forward_ksplit_dispatch(cell, p, nullptr, 1, bv, ksplit, nullptr, &cap);
+  return rc == 0 ? cap : 0;
 }
 
 }  // namespace frnn

@@ -58,13 +58,16 @@ typedef struct frnn_b200_plan {
                             1: group wider than a cluster (D > 512): through global memory;
                             2: as 1, with 16-unit slices in the backward (768 < D)           */
   int64_t xchg_bytes;    /* scratch for exchange >= 1 (forward and backward), else 0      */
-  int fwd_ksplit;        /* 0, or 2: the forward splits the contraction of a 32-unit row
+  int fwd_ksplit;        /* 0, or 2/4: the forward splits the contraction of a 32-unit row
                             tile over this many CTAs (a cluster) and exchanges h through
                             global memory                                                  */
   int fwd_ctas;          /* CTAs of the forward launch                                     */
   int bwd_ksplit;        /* 0, or 2/4/8: the backward owns columns of R in tiles of 128 units
                             and splits the gates_r * D gate rows over this many CTAs (a
                             cluster); cluster / grid_ctas then describe that launch        */
+  int fwd_batch_tile;    /* batch rows per group in the forward (batch_tile, n_btiles, cluster
+                            and grid_ctas describe the backward; the two launches choose
+                            independently when exchange >= 1)                               */
 } frnn_b200_plan_t;
 
 /* Library / ABI version (major*1000 + minor). */

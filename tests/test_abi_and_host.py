@@ -39,7 +39,8 @@ def test_plan_describes_the_headline_workload():
     many = _lib.plan("lstm", 64, 8, 1, 768)                    # four 16-row groups: only the narrower split fits the SMs
     assert many.supported and many.batch_tile == 16 and many.bwd_ksplit == 4 and many.fwd_ctas == 4 * 24
     wider = _lib.plan("lstm", 8, 8, 1, 1024)                   # rows of R beyond one CTA's tensor memory: 16-unit backward slices
-    assert wider.supported and wider.exchange == 2 and wider.unit == 16 and wider.cluster == 64 and wider.fwd_ksplit == 2
+    assert wider.supported and wider.exchange == 2 and wider.unit == 16 and wider.cluster == 64
+    assert wider.fwd_ksplit == 4 and wider.fwd_ctas == 32 * 4 and wider.fwd_batch_tile == 8   # one 8-row group: the wider forward split fits
     assert wider.bwd_ksplit == 8 and wider.xchg_bytes >= 4 * 16 * 4096 * 2
     odd = _lib.plan("lstm", 8, 8, 1, 960)                      # not a multiple of 128: 1-D backward with 16-unit slices
     assert odd.supported and odd.exchange == 2 and odd.bwd_ksplit == 0 and odd.cluster == 60
