@@ -25,17 +25,6 @@ __device__ __forceinline__ uint64_t global_timer_ns() {
   return t;
 }
 
-__device__ __forceinline__ bool elect_one() {
-  uint32_t pred;
-  asm volatile(
-      "{\n"
-      " .reg .pred p;\n"
-      " elect.sync _|p, 0xffffffff;\n"
-      " selp.u32 %0, 1, 0, p;\n"
-      "}\n"
-      : "=r"(pred));
-  return pred != 0;
-}
 
 // ----------------------------------------------------------------------------------------------
 // mbarrier
@@ -51,11 +40,6 @@ __device__ __forceinline__ void mbar_arrive(uint32_t bar) {
 }
 __device__ __forceinline__ void mbar_arrive_expect_tx(uint32_t bar, uint32_t bytes) {
   asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(bar), "r"(bytes)
-               : "memory");
-}
-// Arrive on a barrier that lives in another CTA of the cluster (address from mapa()).
-__device__ __forceinline__ void mbar_arrive_remote(uint32_t cluster_bar) {
-  asm volatile("mbarrier.arrive.release.cluster.shared::cluster.b64 _, [%0];" ::"r"(cluster_bar)
                : "memory");
 }
 // A waiting thread is parked by the hardware for up to this long (or until the phase completes),
@@ -155,42 +139,12 @@ __device__ __forceinline__ void tc_fence_after_sync() {
   asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
 }
 
-// ----------------------------------------------------------------------------------------------
-// clusters / distributed shared memory
-// ----------------------------------------------------------------------------------------------
-__device__ __forceinline__ uint32_t cluster_cta_rank() {
-  uint32_t r;
-  asm volatile("mov.u32 %0, %%cluster_ctarank;" : "=r"(r));
-  return r;
-}
-__device__ __forceinline__ uint32_t cluster_num_ctas() {
-  uint32_t r;
-  asm volatile("mov.u32 %0, %%cluster_nctarank;" : "=r"(r));
-  return r;
-}
 // Translate a shared::cta address of this CTA into the shared::cluster address of the same
 // offset inside CTA `rank` of the cluster.
 __device__ __forceinline__ uint32_t map_to_cta(uint32_t cta_addr, uint32_t rank) {
   uint32_t r;
   asm volatile("mapa.shared::cluster.u32 %0, %1, %2;" : "=r"(r) : "r"(cta_addr), "r"(rank));
   return r;
-}
-__device__ __forceinline__ void st_cluster_u32(uint32_t addr, uint32_t v) {
-  asm volatile("st.shared::cluster.u32 [%0], %1;" ::"r"(addr), "r"(v) : "memory");
-}
-__device__ __forceinline__ void st_cluster_f32(uint32_t addr, float v) {
-  asm volatile("st.shared::cluster.f32 [%0], %1;" ::"r"(addr), "f"(v) : "memory");
-}
-__device__ __forceinline__ void st_cluster_v4_u32(uint32_t addr, uint32_t a, uint32_t b, uint32_t c,
-                                                  uint32_t d) {
-  asm volatile("st.shared::cluster.v4.u32 [%0], {%1, %2, %3, %4};" ::"r"(addr), "r"(a), "r"(b),
-               "r"(c), "r"(d)
-               : "memory");
-}
-__device__ __forceinline__ void st_cluster_v4_f32(uint32_t addr, float a, float b, float c, float d) {
-  asm volatile("st.shared::cluster.v4.f32 [%0], {%1, %2, %3, %4};" ::"r"(addr), "f"(a), "f"(b),
-               "f"(c), "f"(d)
-               : "memory");
 }
 __device__ __forceinline__ void cluster_arrive() {
   asm volatile("barrier.cluster.arrive.release.aligned;" ::: "memory");
@@ -366,14 +320,6 @@ __device__ __forceinline__ void st_async_b32(uint32_t cluster_addr, uint32_t v, 
                "r"(v), "r"(cluster_bar)
                : "memory");
 }
-__device__ __forceinline__ void st_async_v2_b32(uint32_t cluster_addr, uint32_t a, uint32_t b,
-                                                uint32_t cluster_bar) {
-  asm volatile(
-      "st.async.weak.shared::cluster.mbarrier::complete_tx::bytes.v2.b32 [%0], {%1, %2}, [%3];" ::"r"(
-          cluster_addr),
-      "r"(a), "r"(b), "r"(cluster_bar)
-      : "memory");
-}
 __device__ __forceinline__ void st_async_v4_b32(uint32_t cluster_addr, uint32_t a, uint32_t b,
                                                 uint32_t c, uint32_t d, uint32_t cluster_bar) {
   asm volatile(
@@ -382,46 +328,7 @@ __device__ __forceinline__ void st_async_v4_b32(uint32_t cluster_addr, uint32_t 
       "r"(a), "r"(b), "r"(c), "r"(d), "r"(cluster_bar)
       : "memory");
 }
-__device__ __forceinline__ void mbar_expect_tx(uint32_t bar, uint32_t bytes) {
-  asm volatile("mbarrier.expect_tx.relaxed.cta.shared::cta.b64 [%0], %1;" ::"r"(bar), "r"(bytes) : "memory");
-}
 
-// ----------------------------------------------------------------------------------------------
-// exchange through global memory (groups of CTAs larger than a cluster)
-// ----------------------------------------------------------------------------------------------
-__device__ __forceinline__ uint32_t ld_acquire_gpu_u32(const uint32_t* p) {
-  uint32_t v;
-  asm volatile("ld.acquire.gpu.global.u32 %0, [%1];" : "=r"(v) : "l"(p) : "memory");
-  return v;
-}
-__device__ __forceinline__ void red_release_gpu_add_u32(uint32_t* p, uint32_t v) {
-  asm volatile("red.release.gpu.global.add.u32 [%0], %1;" ::"l"(p), "r"(v) : "memory");
-}
-__device__ __forceinline__ void fence_proxy_async_global() {
-  asm volatile("fence.proxy.async.global;" ::: "memory");
-}
-// 1-D bulk copy global -> this CTA's shared memory; size and both addresses multiples of 16 bytes.
-__device__ __forceinline__ void bulk_load_1d(uint32_t dst, const void* src, uint32_t bytes, uint32_t bar) {
-  asm volatile("cp.async.bulk.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1], %2, [%3];" ::"r"(dst),
-               "l"(reinterpret_cast<uint64_t>(src)), "r"(bytes), "r"(bar)
-               : "memory");
-}
-// Bounded wait until *counter >= target (acquire, gpu scope).
-__device__ __forceinline__ bool counter_wait_bounded(const uint32_t* counter, uint32_t target, uint64_t limit_ns,
-                                                     const volatile int* abort_flag) {
-  for (int fast = 0; fast < 64; ++fast) {
-    if (ld_acquire_gpu_u32(counter) >= target) return true;
-  }
-  const uint64_t t0 = global_timer_ns();
-  uint32_t spins = 0;
-  while (true) {
-    if (ld_acquire_gpu_u32(counter) >= target) return true;
-    if ((++spins & 63u) == 0u) {
-      if (abort_flag != nullptr && *abort_flag != 0) return false;
-      if (global_timer_ns() - t0 > limit_ns) return false;
-    }
-  }
-}
 
 // Relaxed (strong, gpu scope) 16-byte global accesses of the flag-in-data exchange: the receiver
 // polls the data words themselves, every 32-bit word carries its own "arrived" information (it
