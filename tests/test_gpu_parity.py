@@ -206,3 +206,46 @@ def test_repeatable_views_and_read_only_inputs(cuda_device):
         assert torch.equal(t, c)
     h_ref, _ = flashrnn_torch(wx, R, b, initial, cell=cell)
     assert torch.equal(h_ref, outs[0][0])
+
+
+def test_random_shapes_with_a_loss_on_the_hidden_state(cuda_device):
+    """Thirty seeded random shapes over all cells, widths 16 ... 1536 and ragged batches; the gradient enters through
+    h only (what a loss on the hidden state gives; gradients fed into sLSTM's normaliser state meet the clamp's
+    discontinuity and are covered by the fixed shapes above)."""
+    import random
+
+    from flashrnn_b200 import _lib, flashrnn_torch, poll_errors
+    from flashrnn_b200.workloads import make_inputs
+
+    rng = random.Random(20261125)
+    widths = [16, 32, 48, 64, 96, 128, 192, 256, 320, 384, 448, 512, 576, 608, 640, 704, 768, 832, 896, 960, 1024, 1152,
+              1280, 1408, 1536]
+    done = 0
+    while done < 30:
+        cell = rng.choice(["lstm", "gru", "elman", "slstm"])
+        D = rng.choice(widths)
+        B = rng.choice([1, 2, 3, 5, 8, 9, 13, 16, 17, 24])
+        N = rng.choice([1, 1, 2, 3]) if D <= 512 else 1
+        T = rng.choice([1, 2, 3, 5, 8, 11])
+        if not _lib.plan(cell, B, T, N, D).supported:
+            continue
+        done += 1
+        zero = cell == "slstm" and rng.random() < 0.5
+        wx, R, b, initial = make_inputs(cell, B, T, N, D, 3000 + done, zero)
+        S = port.SIZES[cell][3]
+        gen = torch.Generator().manual_seed(done)
+        d_history = torch.zeros((S, B, T, N, D))
+        d_history[0] = torch.randn((B, T, N, D), generator=gen)
+        d_carry = torch.zeros((S, B, 1, N, D))
+        d_carry[0] = torch.randn((B, 1, N, D), generator=gen)
+        ref_h, ref_c, ref_g = port.forward_backward(wx, R, b, initial, cell, d_history, d_carry)
+        leaves = [t.to(cuda_device).requires_grad_(True) for t in (wx, R, b, initial)]
+        h, c = flashrnn_torch(*leaves, cell=cell)
+        ((h * d_history.to(cuda_device)).sum() + (c * d_carry.to(cuda_device)).sum()).backward()
+        torch.cuda.synchronize()
+        poll_errors(block=True)
+        log = []
+        name = f"{cell}-B{B}-T{T}-N{N}-D{D}"
+        for key, got, ref in zip(("history", "carry", "dwx", "dR", "db", "d_initial"), [h, c] + [t.grad for t in leaves],
+                                 [ref_h, ref_c] + list(ref_g)):
+            _check(name, key, got, ref, log)
