@@ -5,5 +5,6 @@ Public surface = the reference's: ``flashrnn``, ``FlashRNNConfig``, ``flashrnn_t
 """
 
 from .functional import BACKEND, SIZES, FlashRNNConfig, flashrnn, flashrnn_torch, poll_errors
+from .prepared import PreparedSequence
 
-__all__ = ["BACKEND", "SIZES", "FlashRNNConfig", "flashrnn", "flashrnn_torch", "poll_errors"]
+__all__ = ["BACKEND", "SIZES", "FlashRNNConfig", "PreparedSequence", "flashrnn", "flashrnn_torch", "poll_errors"]

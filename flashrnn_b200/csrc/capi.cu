@@ -244,10 +244,12 @@ extern "C" int frnn_b200_plan(int cell, int B, int T, int N, int D, frnn_b200_pl
   return 0;
 }
 
-extern "C" int frnn_b200_forward(int cell, const void* wx, int wx_bf16, const void* r_bf16, const float* bias,
-                                 const float* initial, float* history, float* carry, float* cache, void* hbf,
-                                 void* xchg, int B, int T, int N, int D, int slstm_zero_first, int wait_limit_ms,
-                                 int* err, void* stream) {
+namespace {
+
+int forward_common(int cell, const void* wx, int wx_bf16, const void* r_bf16, const float* bias, const float* initial,
+                   float* history, float* carry, float* cache, void* hbf, void* xchg, int B, int T, int N, int D,
+                   int slstm_zero_first, const int* zero_first_dev, int output_mode, int wait_limit_ms, int* err,
+                   void* stream) {
   frnn_b200_plan_t plan;
   const int rc = frnn_b200_plan(cell, B, T, N, D, &plan);
   if (rc != 0) return rc;
@@ -263,9 +265,11 @@ extern "C" int frnn_b200_forward(int cell, const void* wx, int wx_bf16, const vo
   p.hbf = static_cast<__nv_bfloat16*>(hbf);
   p.err = err;
   p.B = B; p.T = T; p.N = N; p.D = D;
-  p.C = plan.cluster;
+  p.C = plan.exchange ? D / 32 : plan.cluster;  // CTAs per group of the 1-D forward
   p.wx_box_b = plan.fwd_batch_tile;  // rows past B are filled with zeros by TMA
   p.slstm_zero_first = slstm_zero_first;
+  p.zero_first_dev = zero_first_dev;
+  p.output_mode = output_mode;
   p.wait_limit_ns = (wait_limit_ms > 0 ? static_cast<unsigned long long>(wait_limit_ms) : 2000ull) * 1000000ull;
   if (plan.exchange) {
     if (!xchg) return -5;
@@ -278,6 +282,26 @@ extern "C" int frnn_b200_forward(int cell, const void* wx, int wx_bf16, const vo
     return forward_ksplit_dispatch(cell, p, wx, wx_bf16, plan.fwd_batch_tile, plan.fwd_ksplit, static_cast<cudaStream_t>(stream),
                                    nullptr);
   return forward_dispatch(cell, p, wx, wx_bf16, plan.fwd_batch_tile, plan.exchange ? 32 : plan.unit, static_cast<cudaStream_t>(stream));
+}
+
+}  // namespace
+
+extern "C" int frnn_b200_forward(int cell, const void* wx, int wx_bf16, const void* r_bf16, const float* bias,
+                                 const float* initial, float* history, float* carry, float* cache, void* hbf,
+                                 void* xchg, int B, int T, int N, int D, int slstm_zero_first, int wait_limit_ms,
+                                 int* err, void* stream) {
+  return forward_common(cell, wx, wx_bf16, r_bf16, bias, initial, history, carry, cache, hbf, xchg, B, T, N, D,
+                        slstm_zero_first, nullptr, 0, wait_limit_ms, err, stream);
+}
+
+extern "C" int frnn_b200_forward_prepared(int cell, const void* wx, int wx_bf16, const void* r_bf16, const float* bias,
+                                          const float* initial, float* output, float* carry, void* xchg, int B, int T,
+                                          int N, int D, int output_mode, const int* slstm_zero_first_dev,
+                                          int wait_limit_ms, int* err, void* stream) {
+  if (output_mode < 0 || output_mode > 2) return -5;
+  if (cell == kSLSTM && slstm_zero_first_dev == nullptr) return -5;
+  return forward_common(cell, wx, wx_bf16, r_bf16, bias, initial, output, carry, nullptr, nullptr, xchg, B, T, N, D, 0,
+                        cell == kSLSTM ? slstm_zero_first_dev : nullptr, output_mode, wait_limit_ms, err, stream);
 }
 
 extern "C" int frnn_b200_backward(int cell, const float* cache, const float* history, const float* initial,

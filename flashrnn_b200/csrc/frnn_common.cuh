@@ -49,6 +49,12 @@ struct FwdParams {
   int C;
   int wx_box_b;            // batch extent of the Wx TMA box
   int slstm_zero_first;
+  // Forward-only extras (prepared sequences): when non-null, the sLSTM predicate is read from this
+  // device word instead of slstm_zero_first (no host read, so the call can sit in a CUDA graph);
+  // output_mode 0 writes every state's history [S][B][T][N][D], 1 the hidden state only
+  // [B][T][N][D], 2 only the last hidden state [B][1][N][D].
+  const int* zero_first_dev;
+  int output_mode;
   unsigned long long wait_limit_ns;
   // Exchange through global memory (groups wider than a cluster), null for cluster exchange:
   // per group four slots of the bf16 operand (the data words double as arrival flags).

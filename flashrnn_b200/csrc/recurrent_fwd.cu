@@ -81,6 +81,8 @@ frnn_fwd_kernel(const FwdParams p, const __grid_constant__ CUtensorMap wx_map) {
   uint8_t* const xg_h = xg ? p.xg_data + static_cast<size_t>(gid) * 4 * hbuf_bytes : nullptr;
   // test hook: with err[4] = 1 no CTA publishes h from step err[5] on, so the next operand wait runs out
   const int mute_from = p.err[4] != 0 ? p.err[5] : 0x7fffffff;
+  const bool zero_first = p.zero_first_dev != nullptr ? *p.zero_first_dev != 0 : p.slstm_zero_first != 0;
+  const int hist_states = p.output_mode == 0 ? CT::S : (p.output_mode == 1 ? 1 : 0);  // state planes written per step
   const bool prof = p.err[3] != 0 && blockIdx.x == 0 && lane == 0 && (warp == 0 || warp == 4);
   const int a_cols = MT * (D / 2);
   uint32_t tmem_cols = 32;
@@ -321,7 +323,7 @@ frnn_fwd_kernel(const FwdParams p, const __grid_constant__ CUtensorMap wx_map) {
         float ry[CT::GR][IPT];
 #pragma unroll
         for (int g = 0; g < CT::GR; ++g) ld_f32_vec<IPT>(gbuf + ib * Cfg::GROW + g * U + ul, ry[g]);
-        const bool take_i = CELL == kSLSTM && t == 0 && p.slstm_zero_first != 0;
+        const bool take_i = CELL == kSLSTM && t == 0 && zero_first;
 #pragma unroll
         for (int j = 0; j < IPT; ++j) {
           float ryj[CT::GR], wxj[CT::GW], bj[CT::GB], sj[CT::S], cj[CT::GC];
@@ -441,7 +443,8 @@ frnn_fwd_kernel(const FwdParams p, const __grid_constant__ CUtensorMap wx_map) {
       }
       if (active) {
 #pragma unroll
-        for (int q = 0; q < CT::S; ++q) st_f32_vec<IPT>(hist + q * sBTND + t * ND, st[q]);
+        for (int q = 0; q < CT::S; ++q)
+          if (q < hist_states) st_f32_vec<IPT>(hist + q * sBTND + t * ND, st[q]);
         if (cache != nullptr && CELL != kElman) {
 #pragma unroll
           for (int q = 0; q < CT::GC; ++q) st_f32_vec<IPT>(cache + (static_cast<size_t>(t) * CT::GC + q) * ND, cv[q]);
@@ -464,6 +467,7 @@ frnn_fwd_kernel(const FwdParams p, const __grid_constant__ CUtensorMap wx_map) {
     if (active) {
 #pragma unroll
       for (int q = 0; q < CT::S; ++q) st_f32_vec<IPT>(p.carry + static_cast<size_t>(q) * B * N * D + item_bn, st[q]);
+      if (p.output_mode == 2) st_f32_vec<IPT>(p.history + item_bn, st[0]);  // "last": h_{T-1} as [B][1][N][D]
     }
   }
 

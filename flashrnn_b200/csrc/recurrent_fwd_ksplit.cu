@@ -89,6 +89,8 @@ frnn_fwd_ks_kernel(const FwdParams p, const __grid_constant__ CUtensorMap wx_map
   uint8_t* const xg_h = p.xg_data + static_cast<size_t>(gid) * 4 * (static_cast<size_t>(BT) * D * 2);
   const size_t slot_bytes = static_cast<size_t>(BT) * D * 2;
   const int mute_from = p.err[4] != 0 ? p.err[5] : 0x7fffffff;  // test hook: nobody publishes h from this step on
+  const bool zero_first = p.zero_first_dev != nullptr ? *p.zero_first_dev != 0 : p.slstm_zero_first != 0;
+  const int hist_states = p.output_mode == 0 ? CT::S : (p.output_mode == 1 ? 1 : 0);  // state planes written per step
   const bool prof = p.err[3] != 0 && blockIdx.x == 0 && lane == 0 && (warp == 0 || warp == 4);
   uint32_t tmem_cols = 64;
   while (tmem_cols < static_cast<uint32_t>(Cfg::A_COL0 + Kc / 2)) tmem_cols <<= 1;
@@ -319,7 +321,7 @@ frnn_fwd_ks_kernel(const FwdParams p, const __grid_constant__ CUtensorMap wx_map
       if (tid == 0 && !dead && t + 2 < T) mbar_arrive_expect_tx(smem_u32(&s_part_bar[pb]), part_tx);
       float cv[NI][CT::GC];
       uint32_t hb16[NI];
-      const bool take_i = CELL == kSLSTM && t == 0 && p.slstm_zero_first != 0;
+      const bool take_i = CELL == kSLSTM && t == 0 && zero_first;
 #pragma unroll
       for (int j = 0; j < NI; ++j) {
         cell_forward<CELL>(ry[j], wx[j], bias, st[j], cv[j], take_i);
@@ -394,7 +396,8 @@ frnn_fwd_ks_kernel(const FwdParams p, const __grid_constant__ CUtensorMap wx_map
         if (act[j]) {
           const size_t row = (static_cast<size_t>(b0 + ib0 + j * RPP) * T + t);
 #pragma unroll
-          for (int q = 0; q < CT::S; ++q) p.history[q * sBTND + row * ND + n * D + d0] = st[j][q];
+          for (int q = 0; q < CT::S; ++q)
+            if (q < hist_states) p.history[q * sBTND + row * ND + n * D + d0] = st[j][q];
           if (p.cache != nullptr && CELL != kElman) {
 #pragma unroll
             for (int q = 0; q < CT::GC; ++q) p.cache[(row * CT::GC + q) * ND + n * D + d0] = cv[j][q];
@@ -419,6 +422,8 @@ frnn_fwd_ks_kernel(const FwdParams p, const __grid_constant__ CUtensorMap wx_map
 #pragma unroll
         for (int q = 0; q < CT::S; ++q)
           p.carry[static_cast<size_t>(q) * B * ND + static_cast<size_t>(b0 + ib0 + j * RPP) * ND + n * D + d0] = st[j][q];
+        if (p.output_mode == 2)  // "last": h_{T-1} as [B][1][N][D]
+          p.history[static_cast<size_t>(b0 + ib0 + j * RPP) * ND + n * D + d0] = st[j][0];
       }
     }
   }

@@ -95,6 +95,21 @@ int frnn_b200_forward(int cell, const void* wx, int wx_bf16, const void* r_bf16,
                       void* xchg, int B, int T, int N, int D, int slstm_zero_first, int wait_limit_ms,
                       int* err, void* stream);
 
+/* Forward-only variant for preallocated, replayable sequences (the reference's PreparedSequence,
+ * flashrnn/flashrnn2/prepared.py:18-192, and the output modes of hybrid_fw2d.cu:52-66): no gate
+ * cache and no bf16 copy of h are written.
+ *   output_mode 0: output = every state's history, fp32 [S,B,T,N,D]
+ *               1: output = the hidden state only, fp32 [B,T,N,D]
+ *               2: output = the last hidden state only, fp32 [B,1,N,D]
+ *   slstm_zero_first_dev : device word read by the kernel (non-zero: the normaliser of the whole
+ *               logical call starts at zero); required for the sLSTM cell, ignored otherwise. No
+ *               host read is involved, so the call can be captured in a CUDA graph.
+ * Everything else as frnn_b200_forward. */
+int frnn_b200_forward_prepared(int cell, const void* wx, int wx_bf16, const void* r_bf16, const float* bias,
+                               const float* initial, float* output, float* carry, void* xchg, int B, int T, int N,
+                               int D, int output_mode, const int* slstm_zero_first_dev, int wait_limit_ms, int* err,
+                               void* stream);
+
 /* Reverse-time recurrence (flashrnn/flashrnn/fused/flashrnn.cc:147-247 backward();
  * gradient structure of flashrnn/flashrnn/vanilla_fwbw/bw.py:20-98).
  *   cache, history, initial : as written / passed in the forward call

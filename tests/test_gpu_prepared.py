@@ -1,0 +1,75 @@
+"""Prepared (preallocated, forward-only, replayable) sequences against the ordinary forward call.
+
+Follows the reference's tests of PreparedSequence (tests/flashrnn2/test_prepared.py): every output
+mode returns the same numbers as the full call, the captured graph replays on updated inputs, and
+the sLSTM zero-normaliser predicate is evaluated on the device at every run."""
+
+import pytest
+import torch
+
+pytestmark = pytest.mark.gpu
+
+
+def _inputs(cell, B, T, N, D, seed, dev, zero=False, dtype=torch.float32):
+    from flashrnn_b200.workloads import make_inputs
+
+    wx, R, b, init = (t.to(dev) for t in make_inputs(cell, B, T, N, D, seed, zero))
+    return wx.to(dtype).contiguous(), R.contiguous(), b.contiguous(), init.contiguous()
+
+
+@pytest.mark.parametrize("shape", [("lstm", 8, 16, 3, 256), ("gru", 5, 9, 2, 48), ("slstm", 16, 12, 4, 128),
+                                   ("elman", 3, 7, 1, 64), ("lstm", 4, 6, 1, 768), ("slstm", 3, 5, 1, 1024)],
+                         ids=lambda s: f"{s[0]}-B{s[1]}-T{s[2]}-N{s[3]}-D{s[4]}")
+def test_output_modes_match_the_full_call(shape, cuda_device):
+    from flashrnn_b200 import PreparedSequence, flashrnn_torch
+
+    cell, B, T, N, D = shape
+    for zero in ((False, True) if cell == "slstm" else (False,)):
+        wx, R, b, init = _inputs(cell, B, T, N, D, 71, cuda_device, zero)
+        ref_h, ref_c = flashrnn_torch(wx, R, b, init, cell=cell)
+        for mode in ("full", "hidden", "last"):
+            seq = PreparedSequence(wx, R, b, init, cell, output_mode=mode)
+            out, final = seq.run()
+            seq.check()
+            want = ref_h if mode == "full" else (ref_h[0] if mode == "hidden" else ref_h[0, :, -1:])
+            assert out.shape == want.shape and torch.equal(out, want), (shape, zero, mode)
+            assert torch.equal(final, ref_c), (shape, zero, mode)
+
+
+# a cluster launch and a cooperative launch (wide head, exchange through global memory)
+@pytest.mark.parametrize("shape", [("slstm", 8, 24, 2, 128), ("slstm", 4, 10, 1, 768)], ids=["cluster", "global"])
+def test_captured_graph_replays_on_updated_inputs(shape, cuda_device):
+    from flashrnn_b200 import PreparedSequence, flashrnn_torch
+
+    cell, B, T, N, D = shape
+    wx, R, b, init = _inputs(cell, B, T, N, D, 72, cuda_device, zero=True, dtype=torch.bfloat16)
+    seq = PreparedSequence(wx, R, b, init, cell, output_mode="hidden").capture()
+    out, final = seq.run()
+    seq.check()
+    ref_h, ref_c = flashrnn_torch(wx.float(), R, b, init, cell=cell)
+    assert torch.equal(out, ref_h[0]) and torch.equal(final, ref_c)
+    # new inputs and a non-zero normaliser, written into the bound tensors: the replay must pick both up
+    wx2, _, _, init2 = _inputs(cell, B, T, N, D, 73, cuda_device, zero=False, dtype=torch.bfloat16)
+    seq.wx.copy_(wx2)
+    seq.initial.copy_(init2)
+    out, final = seq.run()
+    seq.check()
+    ref_h, ref_c = flashrnn_torch(wx2.float(), R, b, init2, cell=cell)
+    assert torch.equal(out, ref_h[0]) and torch.equal(final, ref_c)
+    with pytest.raises(ValueError):
+        seq.capture()
+    seq.close()
+
+
+def test_prepared_argument_checks(cuda_device):
+    from flashrnn_b200 import PreparedSequence
+
+    wx, R, b, init = _inputs("lstm", 2, 3, 1, 32, 74, cuda_device)
+    with pytest.raises(ValueError, match="output mode"):
+        PreparedSequence(wx, R, b, init, "lstm", output_mode="everything")
+    with pytest.raises(ValueError, match="forward-only"):
+        PreparedSequence(wx.clone().requires_grad_(True), R, b, init, "lstm")
+    with pytest.raises(ValueError, match="one chunk"):
+        PreparedSequence(wx, R, b, init, "lstm", chunks=(1, 2))
+    with pytest.raises(ValueError, match="initial-state"):
+        PreparedSequence(wx, R, b, init[:1], "lstm")
