@@ -2,6 +2,7 @@
 
     python -m flashrnn_b200.timing                 # the benchmark configurations that fit one GPU
     python -m flashrnn_b200.timing lstm 16 1024 3 256
+    torchrun ... -m flashrnn_b200.timing config5b   # N32 D128 B256 T2048, heads sharded over the ranks
 
 The head-dimension sweep mirrors the reference's published one
 (flashrnn/speed_experiments/kernel_speed_benchmark.py:104-127: N*D = 768, B = 16, T = 1024).
@@ -106,7 +107,66 @@ HEADER = ("| cell | B | T | N | D | cluster / CTAs | fwd ms | bwd ms | dR+db ms 
 HEADER_LIB = HEADER.replace("|\n", "| cuDNN layer fwd+bwd ms (heads x one layer) |\n", 1) + "---|"
 
 
+def time_config5b_sharded(B: int = 256, T: int = 2048, steps: int = 5, warmup: int = 2) -> None:
+    """fwd+bwd of N32 D128 B256 T2048 (LSTM, bf16 Wx) with the 32 heads split over the ranks.
+
+    Run under torchrun, one process per GPU (4 or 8 ranks: one GPU's share must fit its memory):
+        python -m torch.distributed.run --nnodes=1 --nproc-per-node 8 --master-addr 127.0.0.1 \
+            -m flashrnn_b200.timing config5b
+    Heads are independent, so the time loop has no collective and the weight gradients stay sharded;
+    the reported time is the maximum over the ranks, the rate is B*T of the whole job over that time."""
+    import os
+
+    import torch.distributed as dist
+
+    from .sharding import flashrnn_sharded, shard_range
+
+    rank, world = int(os.environ.get("RANK", "0")), int(os.environ.get("WORLD_SIZE", "1"))
+    local = int(os.environ.get("LOCAL_RANK", "0"))
+    torch.cuda.set_device(local)
+    dev = torch.device("cuda", local)
+    if world > 1:
+        dist.init_process_group("nccl", device_id=dev)
+    cell, N, D = "lstm", 32, 128
+    lo, hi = shard_range(N, world, rank)
+    n = hi - lo
+    if n * B * T > 8 * 256 * 2048:
+        raise SystemExit("config 5b needs at least 4 ranks: more than 8 heads of it do not fit one GPU's memory "
+                         "(pass a smaller B and T to try the script on fewer GPUs)")
+    gen = torch.Generator(device=dev).manual_seed(5 + rank)
+    wx = torch.randn((B, T, 4, n, D), generator=gen, device=dev, dtype=torch.bfloat16)
+    R = torch.randn((4, n, D, D), generator=gen, device=dev) * D ** -0.5
+    b = torch.randn((4, n, D), generator=gen, device=dev) * 0.1
+    init = torch.randn((2, B, 1, n, D), generator=gen, device=dev) * 0.5
+    times = []
+    for i in range(warmup + steps):
+        leaves = [t.detach().requires_grad_(True) for t in (wx, R, b, init)]
+        torch.cuda.synchronize()
+        if world > 1:
+            dist.barrier()
+        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        e0.record()
+        hist, _ = flashrnn_sharded(*leaves, function=cell, dtype="bfloat16", axis="heads")
+        hist[0].sum().backward()
+        e1.record()
+        e1.synchronize()
+        if i >= warmup:
+            times.append(e0.elapsed_time(e1))
+        del hist, leaves
+    ms = torch.tensor([sum(times) / len(times)], dtype=torch.float64, device=dev)
+    if world > 1:
+        dist.all_reduce(ms, op=dist.ReduceOp.MAX)
+    if rank == 0:
+        t_ms = float(ms.item())
+        print(f"| config 5b: lstm N{N} D{D} B{B} T{T}, heads over {world} GPUs ({n} per GPU) | "
+              f"{t_ms:.2f} ms per fwd+bwd step (max over ranks) | {B * T / t_ms * 1e3 / 1e6:.1f} M (B*T)/s |")
+    if world > 1:
+        dist.destroy_process_group()
+
+
 def main(argv) -> None:
+    if argv and argv[0] == "config5b":  # optionally followed by B and T (defaults: the configuration's 256 and 2048)
+        return time_config5b_sharded(*map(int, argv[1:3]))
     if len(argv) == 5:
         cell, B, T, N, D = argv[0], *map(int, argv[1:])
         r = time_shape(cell, B, T, N, D)
