@@ -298,7 +298,7 @@ def main():
             "roofline": {"bound": "tensor", "kernel": f"frnn_{dom}_kernel", "achieved": achieved, "peak": bf16_peak,
                          "unit": "TFLOP/s", "frac": achieved / bf16_peak, "peak_source": peak_kind,
                          "traffic": NCU_TRAFFIC_BYTES[dom],
-                         "note": "step-latency bound: T dependent steps; see DESIGN.md for the per-step budget"},
+                         "note": "step-latency bound: T dependent steps; kernels_ms.*_phase_cycles_per_step is the per-step budget"},
             "clocks": clocks.summary(),
         }
         if not args.no_cpu_baseline and world == 1:
