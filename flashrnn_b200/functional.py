@@ -190,10 +190,32 @@ def _run(wx, recurrent, bias, initial, cell: str, zero_normalizer: Optional[bool
         recurrent = _pad_width(recurrent, pad, (-1, -2))
         bias = _pad_width(bias, pad, (-1,))
         initial = _pad_width(initial, pad, (-1,))
-    history, carry = _Recurrence.apply(wx, recurrent, bias, initial, cell, zero_first)
+    B, T, _, N, Dp = wx.shape
+    rows = _rows_per_launch(cell, B, T, N, Dp)
+    if rows >= B:
+        history, carry = _Recurrence.apply(wx, recurrent, bias, initial, cell, zero_first)
+    else:
+        # Wide heads run with all CTAs of a launch resident at once, which bounds the batch rows one
+        # launch can take; more rows go through several launches (batch rows are independent, and
+        # autograd adds up the weight gradients of the pieces).
+        pieces = [_Recurrence.apply(wx[i:i + rows], recurrent, bias, initial[:, i:i + rows], cell, zero_first)
+                  for i in range(0, B, rows)]
+        history = torch.cat([h for h, _ in pieces], dim=1)
+        carry = torch.cat([c for _, c in pieces], dim=1)
     if pad:
         history, carry = history[..., :D], carry[..., :D]
     return history, carry
+
+
+def _rows_per_launch(cell: str, B: int, T: int, N: int, D: int) -> int:
+    """Batch rows one launch can take: B where the shape is supported as a whole (or not at all, which the
+    launch then reports), else the largest multiple of 8 below B for which the plan is supported."""
+    if _lib.plan(cell, B, T, N, D).supported:
+        return B
+    for rows in range((B - 1) // 8 * 8, 0, -8):
+        if _lib.plan(cell, rows, T, N, D).supported:
+            return rows
+    return B
 
 
 def flashrnn_torch(wx, recurrent, bias, initial, *, cell: str = "lstm", numerics: str = "fp32_state_bf16_mma",

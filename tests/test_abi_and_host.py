@@ -77,3 +77,16 @@ def test_there_is_no_cpu_path():
     wx, R, b, init = make_inputs("lstm", 2, 3, 2, 16, 0)
     with pytest.raises(RuntimeError, match="CUDA devices only"):
         flashrnn_torch(wx, R, b, init)
+
+
+def test_wide_head_batches_are_split_over_launches():
+    """A launch whose CTAs all wait on one another can only take as many batch rows as fit the SMs; the host
+    runs larger batches as several launches (the plan alone decides, no GPU needed)."""
+    from flashrnn_b200 import functional
+
+    assert functional._rows_per_launch("lstm", 8, 1024, 3, 256) == 8          # cluster path: never split
+    assert functional._rows_per_launch("lstm", 256, 64, 32, 128) == 256
+    rows = functional._rows_per_launch("lstm", 64, 8, 1, 1024)                # two 16-row groups of 64 CTAs
+    assert rows == 32 and _lib.plan("lstm", rows, 8, 1, 1024).supported
+    assert functional._rows_per_launch("lstm", 8, 8, 1, 2048) == 8            # unsupported at any batch: left to the launch to report
+

@@ -249,3 +249,25 @@ def test_random_shapes_with_a_loss_on_the_hidden_state(cuda_device):
         for key, got, ref in zip(("history", "carry", "dwx", "dR", "db", "d_initial"), [h, c] + [t.grad for t in leaves],
                                  [ref_h, ref_c] + list(ref_g)):
             _check(name, key, got, ref, log)
+
+
+def test_wide_head_batch_larger_than_one_launch(cuda_device):
+    """LSTM D=1024 with 40 batch rows: more than the resident CTAs of one launch can take, so the host runs
+    two launches; forward and all gradients (dR/db summed over the launches by autograd) against the oracle."""
+    from flashrnn_b200 import functional
+    from flashrnn_b200.workloads import make_inputs
+
+    cell, B, T, N, D = "lstm", 40, 4, 1, 1024
+    assert functional._rows_per_launch(cell, B, T, N, D) < B
+    wx, R, b, initial = make_inputs(cell, B, T, N, D, 91)
+    gen = torch.Generator().manual_seed(92)
+    d_history = torch.randn((2, B, T, N, D), generator=gen)
+    d_carry = torch.randn((2, B, 1, N, D), generator=gen)
+    ref_h, ref_c, ref_g = port.forward_backward(wx, R, b, initial, cell, d_history, d_carry)
+    g = dict(meta=dict(cell=cell, T=T, n_chunks=1), wx=wx, R=R, b=b, initial=initial, d_history=d_history, d_carry=d_carry)
+    history, carry, grads = _run_gpu(g, cuda_device)
+    log = []
+    for key, got, ref in zip(("history", "carry", "dwx", "dR", "db", "d_initial"), [history, carry] + list(grads),
+                             [ref_h, ref_c] + list(ref_g)):
+        _check("split", key, got, ref, log)
+
