@@ -33,11 +33,29 @@ __device__ __forceinline__ float exp2_fast(float x) {
   asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(r) : "f"(x));
   return r;
 }
-__device__ __forceinline__ float sigmoid_f(float x) { return rcp_fast(1.0f + exp2_fast(-1.4426950408889634f * x)); }
-__device__ __forceinline__ float tanh_f(float x) {
+// Two-instruction forms (ex2 + rcp, about 2 ulp).
+__device__ __forceinline__ float sigmoid_p(float x) { return rcp_fast(1.0f + exp2_fast(-1.4426950408889634f * x)); }
+__device__ __forceinline__ float tanh_p(float x) {
   // 1 - 2/(1+e^{2x}); saturates correctly at +-1 when e^{2x} over/underflows.
   return 1.0f - 2.0f * rcp_fast(1.0f + exp2_fast(2.885390081777927f * x));
 }
+#ifndef FRNN_PRECISE_ACTIVATIONS
+// One MUFU instruction per activation (tanh.approx.f32, relative error about 2^-11) for the LSTM,
+// GRU and Elman cells: against the oracle the error of every output is unchanged (it is set by the
+// bf16 rounding of the recurrent operands), and the forward step gets about 100 cycles shorter.
+// The sLSTM keeps the two-instruction forms: its normaliser clamp makes gradients discontinuous,
+// so it gets the most accurate forward values that cost nothing on its critical path.
+// Compile with -DFRNN_PRECISE_ACTIVATIONS for the two-instruction forms everywhere.
+__device__ __forceinline__ float tanh_f(float x) {
+  float r;
+  asm("tanh.approx.f32 %0, %1;" : "=f"(r) : "f"(x));
+  return r;
+}
+__device__ __forceinline__ float sigmoid_f(float x) { return fmaf(0.5f, tanh_f(0.5f * x), 0.5f); }
+#else
+__device__ __forceinline__ float sigmoid_f(float x) { return sigmoid_p(x); }
+__device__ __forceinline__ float tanh_f(float x) { return tanh_p(x); }
+#endif
 __device__ __forceinline__ float logsigmoid_f(float x) {
   return fminf(x, 0.0f) - __logf(1.0f + __expf(-fabsf(x)));
 }
@@ -68,9 +86,9 @@ __device__ __forceinline__ void cell_forward(const float* ry, const float* wx, c
     const float m = slstm_take_i ? i : fmaxf(i, logf);
     const float ig = __expf(i - m);
     const float fg = __expf(logf - m);
-    const float c = fg * st[1] + ig * tanh_f(z);
+    const float c = fg * st[1] + ig * tanh_p(z);
     const float n = fmaxf(fg * st[2] + ig, 1.0f);
-    st[0] = sigmoid_f(o) * c / n;
+    st[0] = sigmoid_p(o) * c / n;
     st[1] = c; st[2] = n; st[3] = m;
     cache[0] = i; cache[1] = f; cache[2] = z; cache[3] = o;
   } else if constexpr (CELL == kGRU) {
@@ -118,9 +136,9 @@ __device__ __forceinline__ void cell_backward(const float* cache, const float* s
     const float i = cache[0], f = cache[1], z = cache[2], o = cache[3];
     const float c_p = sp[1], n_p = sp[2], m_p = sp[3];
     const float c_n = sn[1], n_n = sn[2], m_n = sn[3];
-    const float so = sigmoid_f(o);
-    const float tz = tanh_f(z);
-    const float sgf = sigmoid_f(f);
+    const float so = sigmoid_p(o);
+    const float tz = tanh_p(z);
+    const float sgf = sigmoid_p(f);
     const float logf = logsigmoid_f(f) + m_p;
     const float ig = __expf(i - m_n);
     const float fg = __expf(logf - m_n);
