@@ -42,7 +42,7 @@ FLOP_WGRAD = 2 * GR * D * D * N * B * T        # dR contraction
 CPU_SAMPLE_T = 128                              # bounded CPU sample: same B, N, D, first 128 steps
 # dram__bytes_read.sum + dram__bytes_write.sum per launch on this workload, from the ncu capture summarised in
 # profiles/recurrence_kernels_cfg2_lstm_bf16_B8_T1024_N3_D256.md
-NCU_TRAFFIC_BYTES = {"fwd": 52.0e6 + 107.0e6, "bwd": 203.1e6 + 74.9e6, "wgrad": 63.0e6 + 3.2e6}
+NCU_TRAFFIC_BYTES = {"fwd": 52.1e6 + 109.8e6, "bwd": 204.0e6 + 74.6e6, "wgrad": 63.0e6 + 2.2e6}
 
 
 def _peaks():
