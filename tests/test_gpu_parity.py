@@ -271,3 +271,32 @@ def test_wide_head_batch_larger_than_one_launch(cuda_device):
                              [ref_h, ref_c] + list(ref_g)):
         _check("split", key, got, ref, log)
 
+
+
+@pytest.mark.parametrize("cell", ["lstm", "gru"])
+def test_wide_head_bf16_stream_backward(cell, cuda_device):
+    """bf16 Wx on a head that runs the column-owning backward (D = 768): dWx comes back in bf16 through the packet
+    path (shared with dgr for the LSTM, separate for the GRU); all gradients against the oracle on the rounded Wx."""
+    from flashrnn_b200 import _lib, flashrnn
+
+    from flashrnn_b200.workloads import make_inputs
+
+    B, T, N, D = 5, 6, 1, 768
+    assert _lib.plan(cell, B, T, N, D).bwd_ksplit > 0
+    wx, R, b, initial = make_inputs(cell, B, T, N, D, 93)
+    wx_r = wx.bfloat16().float()
+    S = port.SIZES[cell][3]
+    d_history = torch.zeros((S, B, T, N, D))
+    d_history[0] = torch.randn((B, T, N, D), generator=torch.Generator().manual_seed(94))
+    ref_h, _, (r_dwx, r_dR, r_db, r_dinit) = port.forward_backward(wx_r, R, b, initial, cell, d_history,
+                                                                    torch.zeros((S, B, 1, N, D)))
+    leaves = [t.to(cuda_device).requires_grad_(True) for t in (wx.bfloat16(), R, b, initial)]
+    hist, _ = flashrnn(*leaves, function=cell, backend="b200", dtype="bfloat16")
+    (hist * d_history.to(cuda_device)).sum().backward()
+    assert leaves[0].grad.dtype == torch.bfloat16
+    log = []
+    _check(cell, "history", hist, ref_h, log)
+    _check(cell, "dwx", leaves[0].grad.float(), r_dwx, log)
+    _check(cell, "dR", leaves[1].grad, r_dR, log)
+    _check(cell, "db", leaves[2].grad, r_db, log)
+    _check(cell, "d_initial", leaves[3].grad, r_dinit, log)
