@@ -84,6 +84,10 @@ SHAPES = [
     ("elman", 5, 7, 1, 1792, 45, False),
     ("lstm", 24, 5, 1, 1024, 46, False),   # the same with 16-row batch tiles
     ("lstm", 4, 6, 1, 1536, 47, False),    # 96 CTAs per group: 12 unit tiles x 8 K-chunks in the backward
+    ("lstm", 6, 7, 1, 608, 48, False),     # not a multiple of 128: split forward, 1-D backward through global memory
+    ("lstm", 64, 3, 1, 768, 51, False),    # four 16-row groups: the split forward does not fit, one CTA per 32 units
+    ("gru", 9, 5, 1, 736, 49, False),
+    ("lstm", 5, 6, 1, 960, 50, False),     # not a multiple of 128: split forward, 1-D backward with 16-unit slices
     ("lstm", 1, 1, 1, 3, 33, False),       # the reference's smallest portable-gate shape
     ("gru", 3, 3, 2, 7, 34, False),
 ]

@@ -42,8 +42,9 @@ def _backward(lib, _lib, cell, B, T, N, D, t, err, limit_ms):
 
 
 # one shape that exchanges inside a thread-block cluster, one that exchanges through global memory
-@pytest.mark.parametrize("shape", [("lstm", 8, 24, 2, 128), ("lstm", 4, 12, 1, 576), ("lstm", 4, 12, 1, 768)],
-                         ids=["cluster", "global", "global-ksplit"])
+@pytest.mark.parametrize("shape", [("lstm", 8, 24, 2, 128), ("lstm", 4, 12, 1, 576), ("lstm", 4, 12, 1, 768),
+                                   ("lstm", 64, 12, 1, 768)],
+                         ids=["cluster", "global", "global-ksplit", "global-1d"])
 def test_stalled_exchange_is_reported_and_context_survives(shape, cuda_device):
     from flashrnn_b200 import _lib
 
