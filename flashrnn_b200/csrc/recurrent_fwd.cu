@@ -399,7 +399,7 @@ frnn_fwd_kernel(const FwdParams p, const __grid_constant__ CUtensorMap wx_map) {
         // buffer: thread `tid` owns the 16-byte packets tid, tid + 128, ... of the active batch
         // rows, polls them until none shows the fill pattern and copies them to shared memory.
         constexpr int KG_STEP = kEpiThreads / BV;            // k-groups between two packets of a thread
-        constexpr int XCH = (768 / 8 + KG_STEP - 1) / KG_STEP;  // packets per thread at the widest head
+        constexpr int XCH = (960 / 8 + KG_STEP - 1) / KG_STEP;  // packets per thread at the widest head this kernel takes (D/2 + 32 TMEM columns <= 512)
         const int row = tid % BV, kg0 = tid / BV;
         const uint8_t* src = xg_h + static_cast<size_t>((t + 1) & 3) * hbuf_bytes + kg0 * (BT * 16) + row * 16;
         uint8_t* dst = hbuf + ((t + 1) & 1) * hbuf_bytes + kg0 * (BT * 16) + row * 16;

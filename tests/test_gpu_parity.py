@@ -86,6 +86,7 @@ SHAPES = [
     ("lstm", 4, 6, 1, 1536, 47, False),    # 96 CTAs per group: 12 unit tiles x 8 K-chunks in the backward
     ("lstm", 6, 7, 1, 608, 48, False),     # not a multiple of 128: split forward, 1-D backward through global memory
     ("lstm", 64, 3, 1, 768, 51, False),    # four 16-row groups: the split forward does not fit, one CTA per 32 units
+    ("gru", 33, 3, 1, 960, 52, False),     # three gates: the widest head of the one-CTA-per-32-units kernels (30 CTAs per group)
     ("gru", 9, 5, 1, 736, 49, False),
     ("lstm", 5, 6, 1, 960, 50, False),     # not a multiple of 128: split forward, 1-D backward with 16-unit slices
     ("lstm", 1, 1, 1, 3, 33, False),       # the reference's smallest portable-gate shape
