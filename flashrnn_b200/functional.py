@@ -84,7 +84,7 @@ class _Recurrence(torch.autograd.Function):
         if not plan.supported:
             raise ValueError(
                 f"flashrnn_b200: cell={cell} D={D} is outside the sm_100a kernel family "
-                f"(R must fit in the tensor memory of the CTAs of one launch: D <= 1280 for four gates)"
+                f"(the recurrent matrix of a head must fit the tensor memory of the CTAs of one launch: D <= 1792)"
             )
         history = torch.empty((S, B, T, N, D), dtype=torch.float32, device=dev)
         carry = torch.empty((S, B, 1, N, D), dtype=torch.float32, device=dev)
@@ -191,20 +191,37 @@ def _run(wx, recurrent, bias, initial, cell: str, zero_normalizer: Optional[bool
         bias = _pad_width(bias, pad, (-1,))
         initial = _pad_width(initial, pad, (-1,))
     B, T, _, N, Dp = wx.shape
-    rows = _rows_per_launch(cell, B, T, N, Dp)
-    if rows >= B:
+    heads, rows = _launch_split(cell, B, T, N, Dp)
+    if heads >= N and rows >= B:
         history, carry = _Recurrence.apply(wx, recurrent, bias, initial, cell, zero_first)
     else:
-        # Wide heads run with all CTAs of a launch resident at once, which bounds the batch rows one
-        # launch can take; more rows go through several launches (batch rows are independent, and
-        # autograd adds up the weight gradients of the pieces).
-        pieces = [_Recurrence.apply(wx[i:i + rows], recurrent, bias, initial[:, i:i + rows], cell, zero_first)
-                  for i in range(0, B, rows)]
-        history = torch.cat([h for h, _ in pieces], dim=1)
-        carry = torch.cat([c for _, c in pieces], dim=1)
+        # Wide heads run with all CTAs of a launch resident at once, which bounds the heads and batch
+        # rows one launch can take; more go through several launches (heads and batch rows are
+        # independent, and autograd adds up the weight gradients of the batch pieces).
+        per_head = []
+        for n0 in range(0, N, heads):
+            n1 = min(N, n0 + heads)
+            wx_h = wx if heads >= N else wx[:, :, :, n0:n1].contiguous()
+            pieces = [_Recurrence.apply(wx_h[i:i + rows], recurrent[:, n0:n1], bias[:, n0:n1],
+                                        initial[:, i:i + rows, :, n0:n1], cell, zero_first)
+                      for i in range(0, B, rows)]
+            per_head.append((torch.cat([h for h, _ in pieces], dim=1), torch.cat([c for _, c in pieces], dim=1)))
+        history = torch.cat([h for h, _ in per_head], dim=3)
+        carry = torch.cat([c for _, c in per_head], dim=3)
     if pad:
         history, carry = history[..., :D], carry[..., :D]
     return history, carry
+
+
+def _launch_split(cell: str, B: int, T: int, N: int, D: int):
+    """(heads, batch rows) one launch takes: (N, B) where the shape is supported as a whole; else the most heads
+    for which some number of batch rows is supported, with that number of rows (see ``_rows_per_launch``);
+    (N, B) again when nothing is (the launch then reports the shape)."""
+    for heads in range(N, 0, -1):
+        rows = _rows_per_launch(cell, B, T, heads, D)
+        if _lib.plan(cell, rows, T, heads, D).supported:
+            return heads, rows
+    return N, B
 
 
 def _rows_per_launch(cell: str, B: int, T: int, N: int, D: int) -> int:

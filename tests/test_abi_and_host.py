@@ -89,4 +89,9 @@ def test_wide_head_batches_are_split_over_launches():
     rows = functional._rows_per_launch("lstm", 64, 8, 1, 1024)                # two 16-row groups of 64 CTAs
     assert rows == 32 and _lib.plan("lstm", rows, 8, 1, 1024).supported
     assert functional._rows_per_launch("lstm", 8, 8, 1, 2048) == 8            # unsupported at any batch: left to the launch to report
+    # several wide heads: as many heads per launch as fit, then batch rows
+    assert functional._launch_split("lstm", 8, 1024, 3, 256) == (3, 8)
+    heads, rows = functional._launch_split("gru", 17, 4, 2, 1280)
+    assert heads == 1 and rows == 16 and _lib.plan("gru", rows, 4, heads, 1280).supported
+    assert functional._launch_split("lstm", 8, 8, 1, 2048) == (1, 8)
 

@@ -263,7 +263,7 @@ def test_wide_head_batch_larger_than_one_launch(cuda_device):
     from flashrnn_b200.workloads import make_inputs
 
     cell, B, T, N, D = "lstm", 40, 4, 1, 1024
-    assert functional._rows_per_launch(cell, B, T, N, D) < B
+    assert functional._launch_split(cell, B, T, N, D)[1] < B
     wx, R, b, initial = make_inputs(cell, B, T, N, D, 91)
     gen = torch.Generator().manual_seed(92)
     d_history = torch.randn((2, B, T, N, D), generator=gen)
@@ -305,3 +305,26 @@ def test_wide_head_bf16_stream_backward(cell, cuda_device):
     _check(cell, "dR", leaves[1].grad, r_dR, log)
     _check(cell, "db", leaves[2].grad, r_db, log)
     _check(cell, "d_initial", leaves[3].grad, r_dinit, log)
+
+
+def test_several_wide_heads_run_as_one_launch_per_head(cuda_device):
+    """GRU with two heads of 1280 units and 17 batch rows: one launch takes one head and 16 rows, so the host runs
+    four launches; forward and all gradients against the oracle."""
+    from flashrnn_b200 import functional
+    from flashrnn_b200.workloads import make_inputs
+
+    cell, B, T, N, D = "gru", 17, 4, 2, 1280
+    heads, rows = functional._launch_split(cell, B, T, N, D)
+    assert heads < N and rows < B
+    wx, R, b, initial = make_inputs(cell, B, T, N, D, 95)
+    gen = torch.Generator().manual_seed(96)
+    d_history = torch.randn((1, B, T, N, D), generator=gen)
+    d_carry = torch.randn((1, B, 1, N, D), generator=gen)
+    ref_h, ref_c, ref_g = port.forward_backward(wx, R, b, initial, cell, d_history, d_carry)
+    g = dict(meta=dict(cell=cell, T=T, n_chunks=1), wx=wx, R=R, b=b, initial=initial, d_history=d_history, d_carry=d_carry)
+    history, carry, grads = _run_gpu(g, cuda_device)
+    log = []
+    for key, got, ref in zip(("history", "carry", "dwx", "dR", "db", "d_initial"), [history, carry] + list(grads),
+                             [ref_h, ref_c] + list(ref_g)):
+        _check("heads", key, got, ref, log)
+
