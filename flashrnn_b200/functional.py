@@ -182,7 +182,13 @@ def _run(wx, recurrent, bias, initial, cell: str, zero_normalizer: Optional[bool
         zero_first = bool(zero_normalizer)  # predicate of the whole logical call, given by a sharding caller
     else:
         zero_first = bool(torch.all(initial[2] == 0))
+    # The kernels tile the head width in multiples of 16 (heads wider than 768: 64, and 128 where only the
+    # column-owning backward fits); the smallest such width that a launch supports is used.
     pad = (-D) % 16
+    for multiple in (16, 64, 128):
+        if _lib.plan(cell, min(wx.shape[0], 8), wx.shape[1], 1, D + (-D) % multiple).supported:
+            pad = (-D) % multiple
+            break
     if pad:
         # The kernels tile the head width in multiples of 16; zero rows/columns of R, zero
         # inputs and zero initial state keep the padded units at exactly zero.

@@ -89,6 +89,8 @@ SHAPES = [
     ("gru", 33, 3, 1, 960, 52, False),     # three gates: the widest head of the one-CTA-per-32-units kernels (30 CTAs per group)
     ("gru", 9, 5, 1, 736, 49, False),
     ("lstm", 5, 6, 1, 960, 50, False),     # not a multiple of 128: split forward, 1-D backward with 16-unit slices
+    ("gru", 3, 4, 1, 1000, 53, False),     # odd wide width: padded to 1024 by the Python layer
+    ("lstm", 2, 3, 1, 777, 54, False),     # padded to 832
     ("lstm", 1, 1, 1, 3, 33, False),       # the reference's smallest portable-gate shape
     ("gru", 3, 3, 2, 7, 34, False),
 ]
