@@ -7,7 +7,9 @@ A "step" is one forward + BPTT backward (+ dR/db) of the whole workload
 (LSTM bf16, B=8, T=1024, N=3, D=256, seeded synthetic inputs) with loss = sum(h) and
 gradients for all four inputs. With N > 1 every rank runs the same-shaped workload on its own
 batch shard (weak scaling over batch; no collective inside the time loop) and the weight
-gradients dR/db are all-reduced over NCCL once per step.
+gradients dR/db are all-reduced over NCCL once per step (one flat buffer, one call). Before the
+timed region every multi-GPU run checks, on a small shape, that this rank's shard reproduces the
+same rows of the unsharded call, and that the all-reduced dR equals the unsharded dR.
 
 Prints ONE JSON line (rank 0). `value` is timed with CUDA events with the inputs resident in
 HBM; `e2e` goes through the public `flashrnn(...)` call with pinned HOST inputs: every step's
@@ -40,8 +42,10 @@ FLOP_FWD = 2 * GR * D * D * N * B * T          # R*h contraction of the forward 
 FLOP_BWD = 2 * GR * D * D * N * B * T          # R^T*dg contraction of the backward kernel
 FLOP_WGRAD = 2 * GR * D * D * N * B * T        # dR contraction
 CPU_SAMPLE_T = 128                              # bounded CPU sample: same B, N, D, first 128 steps
-# dram__bytes_read.sum + dram__bytes_write.sum per launch on this workload, from the ncu capture summarised in
-# profiles/recurrence_kernels_cfg2_lstm_bf16_B8_T1024_N3_D256.md
+REFERENCE_BUDGET_S = 150.0                      # wall-clock budget of the reference arm's timed steps
+# dram__bytes_read.sum + dram__bytes_write.sum per launch on this workload. NOT measured by this run: quoted from
+# the ncu capture summarised in the profile below (bench.py cannot run ncu on itself); re-capture when a kernel changes.
+NCU_TRAFFIC_PROFILE = "profiles/recurrence_kernels_cfg2_lstm_bf16_B8_T1024_N3_D256.md"
 NCU_TRAFFIC_BYTES = {"fwd": 52.1e6 + 109.8e6, "bwd": 204.0e6 + 74.6e6, "wgrad": 63.0e6 + 2.2e6}
 
 
@@ -106,43 +110,93 @@ class ClockSampler:
         return {"sm_mhz": statistics.median(sm), "sm_max_mhz": max(mx), "reasons": sorted(reasons), "samples": len(sm)}
 
 
-def cpu_baseline(threads: int | None = None, steps: int = 1):
-    """Time the CPU oracle (forward + explicit BPTT) on a bounded sample of the workload."""
-    from flashrnn_b200.workloads import make_inputs
+def config_dict(world: int) -> dict:
+    """The workload description; identical in the GPU arm's and the reference arm's JSON line."""
+    return {"workload": WORKLOAD, "cell": CELL, "B_per_gpu": B, "T": T, "N": N, "D": D,
+            "sharding": "batch (weights replicated, dR+db summed by one all-reduce)" if world > 1 else "none",
+            "l2": "GPU arm: 256 MiB written between timed steps (untimed)"}
+
+
+def _host_threads() -> int:
+    """All host cores, set explicitly: torchrun exports OMP_NUM_THREADS=1 to its children."""
+    n = os.cpu_count() or 1
+    torch.set_num_threads(n)
+    return torch.get_num_threads()
+
+
+def _reference_callable():
+    """(fn(wx, R, b, init) -> seconds for fwd + backward of sum(h), kind, description)."""
+    from oracle.build_ref import load_reference
+
+    ref = load_reference()
+    if ref is not None:
+        def run(wx, R, b, init):
+            leaves = [t.detach().clone().requires_grad_(True) for t in (wx, R, b, init)]
+            t0 = time.perf_counter()
+            hist, _ = ref(*leaves, cell=CELL, numerics="fp32_state_bf16_mma")
+            hist[0].sum().backward()
+            return time.perf_counter() - t0
+
+        return run, "reference", ("the reference's own flashrnn_torch(numerics='fp32_state_bf16_mma') + torch autograd "
+                                  "(unmodified modules under oracle/_ref), fp32 originals of the inputs")
     from oracle import recurrence_port as port
 
-    if threads:
-        torch.set_num_threads(threads)
-    wx, R, b, initial = make_inputs(CELL, B, CPU_SAMPLE_T, N, D, SEED)
-    d_history = torch.zeros((2, B, CPU_SAMPLE_T, N, D))
-    d_history[0] = 1.0
-    d_carry = torch.zeros((2, B, 1, N, D))
-    port.forward_backward(wx[:, :8], R, b, initial, CELL, d_history[:, :, :8], d_carry)  # warm-up
-    times = []
-    for _ in range(steps):
+    def run(wx, R, b, init):
+        d_history = torch.zeros((2,) + tuple(wx.shape[:2]) + tuple(wx.shape[3:]))
+        d_history[0] = 1.0
         t0 = time.perf_counter()
-        port.forward_backward(wx, R, b, initial, CELL, d_history, d_carry)
-        times.append(time.perf_counter() - t0)
-    dt = sum(times) / len(times)
+        port.forward_backward(wx, R, b, init, CELL, d_history, torch.zeros_like(init))
+        return time.perf_counter() - t0
+
+    return run, "port", "oracle port (oracle/_ref was not built: no reference checkout at build time), fwd + explicit BPTT"
+
+
+def cpu_baseline(reps: int = 3):
+    """The reference's CPU implementation on a bounded sample of the workload: the first CPU_SAMPLE_T steps,
+    `reps` passes after one warm-up, median."""
+    from flashrnn_b200.workloads import make_inputs
+
+    cores = _host_threads()
+    run, kind, what = _reference_callable()
+    wx, R, b, initial = make_inputs(CELL, B, CPU_SAMPLE_T, N, D, SEED)
+    run(wx[:, :8], R, b, initial)  # warm-up
+    times = sorted(run(wx, R, b, initial) for _ in range(reps))
+    dt = times[len(times) // 2]
     return {
-        "value": B * CPU_SAMPLE_T / dt, "unit": "(B*T)/s", "cores": torch.get_num_threads(), "kind": "port",
-        "sample": f"oracle port (torch CPU, fp32 state, bf16-rounded operands), B={B} N={N} D={D}, first "
-                  f"{CPU_SAMPLE_T} of {T} steps, fwd + explicit BPTT, {dt:.2f} s per pass",
-    }, dt
+        "value": B * CPU_SAMPLE_T / dt, "unit": "(B*T)/s", "cores": cores, "kind": kind,
+        "sample": f"{what}; B={B} N={N} D={D}, first {CPU_SAMPLE_T} of {T} steps, median of {reps} passes "
+                  f"({dt:.2f} s per pass)",
+    }
 
 
 def run_reference(args):
+    """Reference arm: the reference's own CPU implementation on the FULL workload (all T steps, fwd + autograd
+    backward of sum(h)), all host threads. A step takes seconds, so the arm runs as many of the requested steps as
+    fit REFERENCE_BUDGET_S and prints the count it really ran; warm-up is one short call (the CPU path has no
+    caches to warm beyond the first allocation)."""
     rank = int(os.environ.get("RANK", "0"))
     if rank != 0:
         return
-    base, dt = cpu_baseline(steps=max(1, min(args.steps, 3)))
+    from flashrnn_b200.workloads import make_inputs
+
+    cores = _host_threads()
+    run, kind, what = _reference_callable()
+    wx, R, b, initial = make_inputs(CELL, B, T, N, D, SEED)
+    run(wx[:, :16], R, b, initial)  # warm-up
+    times, t_start = [], time.perf_counter()
+    while len(times) < max(1, args.steps) and (not times or time.perf_counter() - t_start + times[-1] < REFERENCE_BUDGET_S):
+        times.append(run(wx, R, b, initial))
+    dt = sum(times) / len(times)
+    value = B * T / dt
+    base = {"value": value, "unit": "(B*T)/s", "cores": cores, "kind": kind,
+            "sample": f"{what}; the full workload (T={T}), {len(times)} step(s) of {dt:.2f} s"}
     line = {
-        "impl": "reference", "metric": METRIC, "value": base["value"], "unit": "(B*T)/s", "n_gpus": args.gpus,
-        "steps": args.steps, "warmup": args.warmup, "ms_per_step": dt * 1e3 * (T / CPU_SAMPLE_T),
-        "higher_is_better": True, "scaling": "weak", "vs_baseline": None, "dtype": "f32 state, bf16 operands",
-        "data": "synthetic", "config": {"workload": WORKLOAD, "sample": base["sample"]},
+        "impl": "reference", "metric": METRIC, "value": value, "unit": "(B*T)/s", "n_gpus": args.gpus,
+        "steps": len(times), "steps_requested": args.steps, "warmup": 1, "ms_per_step": dt * 1e3,
+        "higher_is_better": True, "scaling": "weak", "vs_baseline": None, "dtype": "bf16 operands, f32 state/accumulate",
+        "data": "synthetic", "config": config_dict(int(os.environ.get("WORLD_SIZE", "1"))),
         "cpu_baseline": base,
-        "e2e": {"value": base["value"], "unit": "(B*T)/s", "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
+        "e2e": {"value": value, "unit": "(B*T)/s", "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
         "gpu_launches": 0,
     }
     print(json.dumps(line))
@@ -174,24 +228,30 @@ def main():
         dist.init_process_group("nccl", device_id=dev)
 
     from flashrnn_b200 import _lib, flashrnn, poll_errors
+    from flashrnn_b200.sharding import flashrnn_sharded
     from flashrnn_b200.workloads import make_inputs
 
     _lib.load()
+    shard_check = check_sharded_equals_unsharded(dev, dist, rank, world) if world > 1 else None
     # every rank holds its own batch shard of a global batch of world*B sequences
     wx32, R32, b32, init32 = make_inputs(CELL, B, T, N, D, SEED + rank)
     R32, b32 = make_inputs(CELL, B, T, N, D, SEED)[1:3]  # weights are replicated
     h_wx = wx32.to(torch.bfloat16).pin_memory()
     h_R, h_b, h_init = R32.pin_memory(), b32.pin_memory(), init32.pin_memory()
+    h2d_bytes = sum(t.numel() * t.element_size() for t in (h_wx, h_R, h_b, h_init))
     d_wx, d_R, d_b, d_init = (t.to(dev) for t in (h_wx, h_R, h_b, h_init))
     flush = torch.empty(256 * 1024 * 1024, dtype=torch.uint8, device=dev)
 
+    def call(leaves):
+        # N > 1: this rank's batch shard; dR and db are summed over the ranks by ONE all-reduce inside backward
+        if dist is not None:
+            return flashrnn_sharded(*leaves, function=CELL, dtype="bfloat16", axis="batch")
+        return flashrnn(*leaves, function=CELL, backend="b200", dtype="bfloat16")
+
     def step_resident():
         leaves = [t.detach().requires_grad_(True) for t in (d_wx, d_R, d_b, d_init)]
-        hist, _ = flashrnn(*leaves, function=CELL, backend="b200", dtype="bfloat16")
+        hist, _ = call(leaves)
         hist[0].sum().backward()
-        if dist is not None:
-            dist.all_reduce(leaves[1].grad)
-            dist.all_reduce(leaves[2].grad)
         return leaves
 
     # End-to-end: every step copies its inputs from pinned host memory and copies the loss back to pinned host
@@ -223,12 +283,9 @@ def main():
             if i + 1 < steps:
                 start_copy(i + 1)
             leaves = [t.detach().requires_grad_(True) for t in dev_sets[i % 2]]
-            hist, _ = flashrnn(*leaves, function=CELL, backend="b200", dtype="bfloat16")
+            hist, _ = call(leaves)
             loss = hist[0].sum()
             loss.backward()
-            if dist is not None:
-                dist.all_reduce(leaves[1].grad)
-                dist.all_reduce(leaves[2].grad)
             losses[i:i + 1].copy_(loss.detach().reshape(1), non_blocking=True)  # device -> host read of the result
             set_free[i % 2].record()
         e1.record()
@@ -271,6 +328,11 @@ def main():
 
     # per-kernel durations, measured with the same inputs through the C ABI
     breakdown = kernel_breakdown(_lib, dev, d_wx, d_R, d_b, d_init, flush, max(3, min(args.steps, 10)))
+    if dist is not None:
+        breakdown["allreduce_dR_db"] = time_allreduce(dev, dist, GR * N * D * D + 4 * N * D)
+    del d_wx, h_wx, dev_sets
+    wide = wide_head_sharded(dev, dist, rank, world)
+    heads = head_sharded_config(dev, dist, rank, world)
 
     t_ms = torch.tensor([ms, ms_e2e], dtype=torch.float64, device=dev)
     if dist is not None:
@@ -287,25 +349,127 @@ def main():
             "metric": METRIC, "value": value, "unit": "(B*T)/s", "n_gpus": world, "steps": args.steps,
             "warmup": args.warmup, "ms_per_step": ms / args.steps, "higher_is_better": True, "scaling": "weak",
             "vs_baseline": None, "dtype": "bf16 operands, f32 state/accumulate", "data": "synthetic",
-            "config": {"workload": WORKLOAD, "cell": CELL, "B_per_gpu": B, "T": T, "N": N, "D": D,
-                       "sharding": "batch (weights replicated, dR/db all-reduced)" if world > 1 else "none",
-                       "l2": "256 MiB written between timed steps (untimed)"},
+            "config": config_dict(world),
             "e2e": {"value": e2e_value, "unit": "(B*T)/s", "ms_per_step": ms_e2e / args.steps,
-                    "h2d_bytes_per_step": sum(t.numel() * t.element_size() for t in (h_wx, h_R, h_b, h_init)),
-                    "d2h_bytes_per_step": 4},
+                    "h2d_bytes_per_step": h2d_bytes,
+                    "d2h_bytes_per_step": 4,
+                    "d2h_note": "training step: only the scalar loss returns to the host; history and gradients stay "
+                                "on the device"},
             "gpu_launches": args.steps * 5,
             "kernels_ms": breakdown,
             "roofline": {"bound": "tensor", "kernel": f"frnn_{dom}_kernel", "achieved": achieved, "peak": bf16_peak,
                          "unit": "TFLOP/s", "frac": achieved / bf16_peak, "peak_source": peak_kind,
                          "traffic": NCU_TRAFFIC_BYTES[dom],
+                         "traffic_source": f"quoted from the committed ncu summary {NCU_TRAFFIC_PROFILE}, not measured by this run",
                          "note": "step-latency bound: T dependent steps; kernels_ms.*_phase_cycles_per_step is the per-step budget"},
             "clocks": clocks.summary(),
         }
+        if shard_check is not None:
+            line["sharded_equals_unsharded"] = shard_check
+        if wide is not None:
+            line["wide_head_row_sharded"] = wide
+        if heads is not None:
+            line["head_sharded_cfg5b"] = heads
         if not args.no_cpu_baseline and world == 1:
-            line["cpu_baseline"], _ = cpu_baseline()
+            line["cpu_baseline"] = cpu_baseline()
         print(json.dumps(line))
     if dist is not None:
         dist.destroy_process_group()
+
+
+def check_sharded_equals_unsharded(dev, dist, rank, world):
+    """Before anything is timed: on a small shape, this rank's batch shard through flashrnn_sharded must reproduce
+    the same rows of the unsharded call run on this GPU (history / dWx bit-identical: batch rows never interact),
+    and the all-reduced dR / db must equal the unsharded ones up to summation order. Raises on a mismatch."""
+    from flashrnn_b200 import flashrnn
+    from flashrnn_b200.sharding import flashrnn_sharded, shard_range
+    from flashrnn_b200.workloads import make_inputs
+
+    cell, Bs, Ts, Ns, Ds = "lstm", 8 * world, 24, 2, 128
+    wx, R, b, init = (t.to(dev) for t in make_inputs(cell, Bs, Ts, Ns, Ds, 77))
+    wx = wx.bfloat16()
+    full = [t.detach().requires_grad_(True) for t in (wx, R, b, init)]
+    hist_f, _ = flashrnn(*full, function=cell, backend="b200", dtype="bfloat16")
+    hist_f[0].sum().backward()
+    lo, hi = shard_range(Bs, world, rank)
+    mine = [t.detach().requires_grad_(True) for t in (wx[lo:hi].contiguous(), R, b, init[:, lo:hi].contiguous())]
+    hist_s, _ = flashrnn_sharded(*mine, function=cell, dtype="bfloat16", axis="batch")
+    hist_s[0].sum().backward()
+    torch.cuda.synchronize()
+    same_rows = bool(torch.equal(hist_s, hist_f[:, lo:hi])) and bool(torch.equal(mine[0].grad, full[0].grad[lo:hi]))
+    scale = float(full[1].grad.abs().max())
+    err_dR = float((mine[1].grad - full[1].grad).abs().max()) / scale
+    err_db = float((mine[2].grad - full[2].grad).abs().max()) / float(full[2].grad.abs().max())
+    flags = torch.tensor([float(same_rows), err_dR, err_db], dtype=torch.float64, device=dev)
+    worst = flags.clone()
+    dist.all_reduce(worst, op=dist.ReduceOp.MAX)
+    dist.all_reduce(flags, op=dist.ReduceOp.MIN)
+    ok = bool(flags[0] == 1.0) and float(worst[1]) <= 1e-5 and float(worst[2]) <= 1e-5
+    out = {"shape": f"{cell} B{Bs} T{Ts} N{Ns} D{Ds}", "rows_bit_identical_on_every_rank": bool(flags[0] == 1.0),
+           "dR_max_err_scaled": float(worst[1]), "db_max_err_scaled": float(worst[2]), "ok": ok}
+    if not ok:
+        raise RuntimeError(f"sharded run does not reproduce the unsharded one: {out}")
+    return out
+
+
+def time_allreduce(dev, dist, numel, reps=10):
+    """Device time (ms, max over ranks) of the one all-reduce of the flat dR+db buffer."""
+    buf = torch.zeros(numel, dtype=torch.float32, device=dev)
+    for _ in range(3):
+        dist.all_reduce(buf)
+    torch.cuda.synchronize()
+    dist.barrier()
+    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    e0.record()
+    for _ in range(reps):
+        dist.all_reduce(buf)
+    e1.record()
+    e1.synchronize()
+    t = torch.tensor([e0.elapsed_time(e1) / reps], dtype=torch.float64, device=dev)
+    dist.all_reduce(t, op=dist.ReduceOp.MAX)
+    return float(t.item())
+
+
+def head_sharded_config(dev, dist, rank, world, steps=3, warmup=2):
+    """Extra keys: fwd+bwd step of the head-sharded configuration (LSTM N32 D128 B256 T2048, bf16 Wx) with the 32
+    heads split over the ranks, no collective at all. Needs >= 4 GPUs (one GPU's share must fit its memory)."""
+    if world < 4 or 32 % world != 0:
+        return None
+    from flashrnn_b200.sharding import flashrnn_sharded
+
+    cell, Nh, Dh, Bh, Th = "lstm", 32 // world, 128, 256, 2048
+    gen = torch.Generator(device=dev).manual_seed(5 + rank)
+    wx = torch.randn((Bh, Th, 4, Nh, Dh), generator=gen, device=dev, dtype=torch.bfloat16)
+    R = torch.randn((4, Nh, Dh, Dh), generator=gen, device=dev) * Dh ** -0.5
+    b = torch.randn((4, Nh, Dh), generator=gen, device=dev) * 0.1
+    init = torch.randn((2, Bh, 1, Nh, Dh), generator=gen, device=dev) * 0.5
+    times = []
+    for i in range(warmup + steps):
+        leaves = [t.detach().requires_grad_(True) for t in (wx, R, b, init)]
+        torch.cuda.synchronize()
+        dist.barrier()
+        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        e0.record()
+        hist, _ = flashrnn_sharded(*leaves, function=cell, dtype="bfloat16", axis="heads")
+        hist[0].sum().backward()
+        e1.record()
+        e1.synchronize()
+        if i >= warmup:
+            times.append(e0.elapsed_time(e1))
+        del hist, leaves
+    t = torch.tensor([sum(times) / len(times)], dtype=torch.float64, device=dev)
+    dist.all_reduce(t, op=dist.ReduceOp.MAX)
+    ms = float(t.item())
+    del wx, R, b, init
+    torch.cuda.empty_cache()
+    return {"workload": f"lstm bf16 N32 D128 B256 T2048, {Nh} heads per GPU, no collective", "ms_per_step": ms,
+            "value": Bh * Th / ms * 1e3, "unit": "(B*T)/s", "steps": steps, "warmup": warmup}
+
+
+def wide_head_sharded(dev, dist, rank, world):
+    """Extra keys: the row-sharded wide head (one head of D = 4096 split over the ranks with the per-step exchange
+    done by peer stores inside the kernels). Filled in by the multi-GPU kernels when they are present."""
+    return None
 
 
 def kernel_breakdown(_lib, dev, d_wx, d_R, d_b, d_init, flush, reps):

@@ -88,11 +88,31 @@ def load() -> ctypes.CDLL:
     return lib
 
 
+_plans: dict = {}
+
+
 def plan(cell: str, B: int, T: int, N: int, D: int) -> Plan:
+    """Launch plan of a shape on the CURRENT CUDA device (the plan depends on its SM count). Remembered per
+    (device, shape): the host path asks several times per call."""
+    dev = -1
+    try:
+        import torch
+
+        if torch.cuda.is_available():
+            dev = torch.cuda.current_device()
+    except ImportError:  # the binding itself does not need torch
+        pass
+    key = (dev, cell, B, T, N, D)
+    hit = _plans.get(key)
+    if hit is not None:
+        return hit
     out = Plan()
     rc = load().frnn_b200_plan(CELLS[cell], B, T, N, D, ctypes.byref(out))
     if rc != 0:
         raise ValueError(f"frnn_b200_plan failed: {ERROR_TEXT.get(rc, rc)}")
+    if len(_plans) > 4096:
+        _plans.clear()
+    _plans[key] = out
     return out
 
 

@@ -1,7 +1,6 @@
 // extern "C" boundary of the library: shape planning, argument checks, kernel dispatch.
 #include "../../include/flashrnn_b200.h"
 
-#include <cstdlib>
 #include <mutex>
 
 #include "frnn_common.cuh"
@@ -136,10 +135,6 @@ extern "C" int frnn_b200_plan(int cell, int B, int T, int N, int D, frnn_b200_pl
   // gets its own SMs; beyond that 16-row tiles halve the number of groups.
   out->batch_tile = 8;
   if (B > 8 && static_cast<long long>(N) * ((B + 7) / 8) * out->cluster > sm_count()) out->batch_tile = 16;
-  if (const char* forced = std::getenv("FRNN_B200_BATCH_TILE")) {  // tuning / experiments
-    const int v = std::atoi(forced);
-    if (v == 8 || v == 16) out->batch_tile = v;
-  }
   out->n_btiles = (B + out->batch_tile - 1) / out->batch_tile;
   out->grid_ctas = N * out->n_btiles * out->cluster;
   const int bt = 16;  // UMMA N: batch tile padded to 16 columns

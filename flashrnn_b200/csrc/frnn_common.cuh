@@ -23,19 +23,6 @@ enum : int {
   kErrWaitDg = 107,     // backward: dg operand barrier
 };
 
-// How one (head, batch tile) group is laid out over a thread-block cluster.
-struct Plan {
-  int cell;
-  int unit;        // U: hidden units owned by one CTA
-  int cluster;     // C = D / U CTAs per group
-  int batch_tile;  // BV: batch rows per group
-  int n_btiles;    // ceil(B / BV)
-  int grid;        // N * n_btiles * C
-  int smem_fwd, smem_bwd;
-  int tmem_cols_fwd, tmem_cols_bwd;
-  int supported;   // 0 when the shape does not fit this kernel family
-};
-
 struct FwdParams {
   const __nv_bfloat16* R;  // [GR][N][D][D] (out, in)
   const float* bias;       // [GB][N][D]
@@ -131,6 +118,41 @@ __device__ __forceinline__ uint32_t pack_bf16x2(float lo, float hi) {
 // rows: 8x8 core matrices, K-adjacent core matrices `rows*16` bytes apart.
 __host__ __device__ __forceinline__ uint32_t kmajor_offset(int rows, int row, int k) {
   return static_cast<uint32_t>((k >> 3) * (rows * 16) + (row >> 3) * 128 + (row & 7) * 16 + (k & 7) * 2);
+}
+
+// Host: keep the CTAs that can share one SM within the SM's 512 tensor-memory columns.
+// tcgen05.alloc has no time limit: a CTA whose request does not fit waits until a co-resident CTA
+// frees its columns. CTAs of one launch wait on one another (cluster barriers, exchange), so a CTA
+// stuck in the allocation behind a CTA of another group could keep both groups from ever finishing.
+// The launchers therefore ask the occupancy calculator how many CTAs of the kernel fit one SM with
+// the chosen shared-memory size and, where that many would ask for more than 512 columns together,
+// enlarge the dynamic shared memory until no more than 512 / tmem_cols CTAs fit. Returns 0, a
+// cudaError_t, or -3 when the budget cannot be met. Sets the kernel's dynamic shared-memory limit.
+template <typename Kern>
+inline int fit_tmem_budget(Kern kern, int threads, uint32_t tmem_cols, int* smem) {
+  const int allowed = tmem_cols >= 512u ? 1 : static_cast<int>(512u / tmem_cols);
+  for (int attempt = 0; attempt < 2; ++attempt) {
+    cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, *smem);
+    if (e != cudaSuccess) return static_cast<int>(e);
+    int blocks = 0;
+    e = cudaOccupancyMaxActiveBlocksPerMultiprocessor(&blocks, kern, threads, static_cast<size_t>(*smem));
+    if (e != cudaSuccess) return static_cast<int>(e);
+    if (blocks <= allowed) return 0;
+    if (attempt == 1) return -3;
+    int dev = 0, per_sm = 0;
+    if (cudaGetDevice(&dev) != cudaSuccess ||
+        cudaDeviceGetAttribute(&per_sm, cudaDevAttrMaxSharedMemoryPerMultiprocessor, dev) != cudaSuccess)
+      return -3;
+    const int need = (per_sm / (allowed + 1) + 128) & ~127;  // allowed + 1 CTAs of this size exceed the SM
+    if (need > 227 * 1024) return -3;
+    if (need > *smem) *smem = need;
+  }
+  return -3;
+}
+inline uint32_t tmem_cols_pow2(int needed, uint32_t minimum) {
+  uint32_t c = minimum;
+  while (c < static_cast<uint32_t>(needed)) c <<= 1;
+  return c;
 }
 
 // Host: build a tiled tensor map (no swizzle, no interleave). dims/box innermost first.

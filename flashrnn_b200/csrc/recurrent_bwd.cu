@@ -583,7 +583,7 @@ int launch_bwd(const BwdParams& p, const float* cache, const float* history, con
   const int part_bufs = XG ? 0 : 2;
   // the ring of TMA stages doubles as the staging area of the prologue's R load (16 rows of D bf16)
   const int ring_bytes = Cfg::NST * Cfg::STAGE_BYTES > 16 * p.D * 2 ? Cfg::NST * Cfg::STAGE_BYTES : 16 * p.D * 2;
-  const int smem = ((Cfg::DGBUF_BYTES + part_bufs * part_bytes + Cfg::DBUF_BYTES + 127) & ~127) + ring_bytes;
+  int smem = ((Cfg::DGBUF_BYTES + part_bufs * part_bytes + Cfg::DBUF_BYTES + 127) & ~127) + ring_bytes;
   const int MTB = (p.D + 127) / 128;
   if (MTB > kMaxTiles || ((MTB * Cfg::BT + 31) / 32 * 32) + MTB * (Cfg::ROWS / 2) > 512) return -3;
   if (smem > 227 * 1024) return -2;
@@ -606,8 +606,10 @@ int launch_bwd(const BwdParams& p, const float* cache, const float* history, con
     if (make_tensor_map(&init_map, initial, 4, 5, dims1, box) != 0) return -4;
   }
   auto kern = frnn_bwd_kernel<CELL, BV, U, WX_BF16, XG>;
-  cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, smem);
-  if (e != cudaSuccess) return static_cast<int>(e);
+  const int fit = fit_tmem_budget(
+      kern, kBwdThreads, tmem_cols_pow2(((MTB * Cfg::BT + 31) / 32 * 32) + MTB * (Cfg::ROWS / 2), 32u), &smem);
+  if (fit != 0) return fit;
+  cudaError_t e = cudaSuccess;
   if (p.C > 8 && !XG) {
     e = cudaFuncSetAttribute(kern, cudaFuncAttributeNonPortableClusterSizeAllowed, 1);
     if (e != cudaSuccess) return static_cast<int>(e);

@@ -543,7 +543,7 @@ int launch_bwd_ks(const BwdParams& p, const float* cache, const float* history, 
   if (capacity_only == nullptr && p.xg_data == nullptr) return -2;
   const int Kc = K / KS;
   const int dg_bytes = Cfg::BT * Kc * 2;
-  const int smem = ((2 * dg_bytes + 2 * Cfg::PART_BYTES + Cfg::DBUF_BYTES + 127) & ~127) + Cfg::NST * Cfg::STAGE_BYTES;
+  int smem = ((2 * dg_bytes + 2 * Cfg::PART_BYTES + Cfg::DBUF_BYTES + 127) & ~127) + Cfg::NST * Cfg::STAGE_BYTES;
   if (smem > 227 * 1024) return -2;
   const uint64_t uD = p.D, uN = p.N, uT = p.T, uB = p.B;
   const uint32_t ub = static_cast<uint32_t>(p.box_b);
@@ -565,8 +565,9 @@ int launch_bwd_ks(const BwdParams& p, const float* cache, const float* history, 
     if (make_tensor_map(&init_map, initial, 4, 5, dims1, box) != 0) return -4;
   }
   auto kern = frnn_bwd_ks_kernel<CELL, BV, KS, WX_BF16>;
-  cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, smem);
-  if (e != cudaSuccess) return static_cast<int>(e);
+  const int fit = fit_tmem_budget(kern, kThreads, tmem_cols_pow2(Cfg::A_COL0 + Kc / 2, 64u), &smem);
+  if (fit != 0) return fit;
+  cudaError_t e = cudaSuccess;
   const int n_btiles = (p.B + BV - 1) / BV;
   cudaLaunchConfig_t cfg = {};
   cfg.gridDim = dim3(static_cast<unsigned>(p.N * n_btiles * (p.D / 128) * KS));

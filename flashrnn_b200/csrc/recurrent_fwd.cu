@@ -488,7 +488,7 @@ int launch_fwd(const FwdParams& p, const void* wx, cudaStream_t stream) {
   using Cfg = FwdCfg<CELL, BV, U, WX_BF16>;
   using CT = typename Cfg::CT;
   const int hbuf_bytes = Cfg::BT * p.D * 2;
-  const int smem = ((2 * hbuf_bytes + Cfg::GBUF_BYTES + 127) & ~127) + kWxStages * Cfg::WX_STAGE_BYTES;
+  int smem = ((2 * hbuf_bytes + Cfg::GBUF_BYTES + 127) & ~127) + kWxStages * Cfg::WX_STAGE_BYTES;
   if (Cfg::A_COL0 + Cfg::MT * (p.D / 2) > 512) return -3;
   CUtensorMap map;
   const uint64_t dims[5] = {static_cast<uint64_t>(p.D), static_cast<uint64_t>(p.N), static_cast<uint64_t>(CT::GW),
@@ -496,8 +496,9 @@ int launch_fwd(const FwdParams& p, const void* wx, cudaStream_t stream) {
   const uint32_t box[5] = {static_cast<uint32_t>(U), 1u, static_cast<uint32_t>(CT::GW), 1u, static_cast<uint32_t>(p.wx_box_b)};
   if (make_tensor_map(&map, wx, Cfg::WX_ES, 5, dims, box) != 0) return -4;
   auto kern = frnn_fwd_kernel<CELL, BV, U, WX_BF16, XG>;
-  cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, smem);
-  if (e != cudaSuccess) return static_cast<int>(e);
+  const int fit = fit_tmem_budget(kern, kFwdThreads, tmem_cols_pow2(Cfg::A_COL0 + Cfg::MT * (p.D / 2), 32u), &smem);
+  if (fit != 0) return fit;
+  cudaError_t e = cudaSuccess;
   if (p.C > 8 && !XG) {
     e = cudaFuncSetAttribute(kern, cudaFuncAttributeNonPortableClusterSizeAllowed, 1);
     if (e != cudaSuccess) return static_cast<int>(e);

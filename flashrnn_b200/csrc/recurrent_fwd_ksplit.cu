@@ -448,15 +448,16 @@ int launch_fwd_ks(const FwdParams& p, const void* wx, cudaStream_t stream, int* 
   if (capacity_only == nullptr && p.xg_data == nullptr) return -2;
   const int Kc = p.D / KS;
   const int hbuf_bytes = Cfg::BT * Kc * 2;
-  const int smem = ((2 * hbuf_bytes + 2 * Cfg::PART_BYTES + 127) & ~127) + kWxStages * Cfg::WX_STAGE_BYTES;
+  int smem = ((2 * hbuf_bytes + 2 * Cfg::PART_BYTES + 127) & ~127) + kWxStages * Cfg::WX_STAGE_BYTES;
   CUtensorMap map;
   const uint64_t dims[5] = {static_cast<uint64_t>(p.D), static_cast<uint64_t>(p.N), static_cast<uint64_t>(CT::GW),
                             static_cast<uint64_t>(p.T), static_cast<uint64_t>(p.B)};
   const uint32_t box[5] = {static_cast<uint32_t>(Cfg::UO), 1u, static_cast<uint32_t>(CT::GW), 1u, static_cast<uint32_t>(p.wx_box_b)};
   if (capacity_only == nullptr && make_tensor_map(&map, wx, Cfg::WX_ES, 5, dims, box) != 0) return -4;
   auto kern = frnn_fwd_ks_kernel<CELL, BV, KS, WX_BF16>;
-  cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, smem);
-  if (e != cudaSuccess) return static_cast<int>(e);
+  const int fit = fit_tmem_budget(kern, kThreads, tmem_cols_pow2(Cfg::A_COL0 + Kc / 2, 64u), &smem);
+  if (fit != 0) return fit;
+  cudaError_t e = cudaSuccess;
   const int n_btiles = (p.B + BV - 1) / BV;
   cudaLaunchConfig_t cfg = {};
   cfg.gridDim = dim3(static_cast<unsigned>(p.N * n_btiles * (p.D / 32) * KS));

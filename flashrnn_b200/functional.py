@@ -71,6 +71,12 @@ class _Recurrence(torch.autograd.Function):
 
     @staticmethod
     def forward(ctx, wx, recurrent, bias, initial, cell: str, zero_first: bool):
+        # the C ABI plans for and launches on the current device: make the tensors' device current
+        with torch.cuda.device(wx.device):
+            return _Recurrence._forward(ctx, wx, recurrent, bias, initial, cell, zero_first)
+
+    @staticmethod
+    def _forward(ctx, wx, recurrent, bias, initial, cell: str, zero_first: bool):
         lib = _lib.load()
         poll_errors()
         B, T, _, N, D = wx.shape
@@ -113,6 +119,11 @@ class _Recurrence(torch.autograd.Function):
 
     @staticmethod
     def backward(ctx, d_history, d_carry):
+        with torch.cuda.device(ctx.saved_tensors[2].device):
+            return _Recurrence._backward(ctx, d_history, d_carry)
+
+    @staticmethod
+    def _backward(ctx, d_history, d_carry):
         lib = _lib.load()
         poll_errors()
         r_bf, init32, history, cache, hbf = ctx.saved_tensors
@@ -131,8 +142,10 @@ class _Recurrence(torch.autograd.Function):
         dgr = torch.empty(plan.dgr_bytes // 2, dtype=torch.bfloat16, device=dev)
         d_initial = torch.empty((S, B, 1, N, D), dtype=torch.float32, device=dev)
         db_part = torch.empty(plan.dbpart_bytes // 4, dtype=torch.float32, device=dev)
-        dR = torch.empty((gr, N, D, D), dtype=torch.float32, device=dev)
-        db = torch.empty((gb, N, D), dtype=torch.float32, device=dev)
+        # dR and db are neighbours in one allocation so that a batch-sharded caller sums both with one all-reduce
+        wflat = torch.empty(gr * N * D * D + gb * N * D, dtype=torch.float32, device=dev)
+        dR = wflat[:gr * N * D * D].view(gr, N, D, D)
+        db = wflat[gr * N * D * D:].view(gb, N, D)
         work = None
         if plan.wgrad_work_bytes:
             work = torch.empty(plan.wgrad_work_bytes // 4, dtype=torch.float32, device=dev)
@@ -175,6 +188,11 @@ def _pad_width(t: torch.Tensor, pad: int, dims) -> torch.Tensor:
 def _run(wx, recurrent, bias, initial, cell: str, zero_normalizer: Optional[bool] = None):
     if not wx.is_cuda:
         raise RuntimeError("flashrnn_b200 runs on CUDA devices only (sm_100a); there is no CPU path")
+    with torch.cuda.device(wx.device):
+        return _run_on_current_device(wx, recurrent, bias, initial, cell, zero_normalizer)
+
+
+def _run_on_current_device(wx, recurrent, bias, initial, cell: str, zero_normalizer: Optional[bool]):
     D = wx.shape[-1]
     if cell != "slstm":
         zero_first = False
@@ -241,13 +259,16 @@ def _rows_per_launch(cell: str, B: int, T: int, N: int, D: int) -> int:
     return B
 
 
-def flashrnn_torch(wx, recurrent, bias, initial, *, cell: str = "lstm", numerics: str = "fp32_state_bf16_mma",
+def flashrnn_torch(wx, recurrent, bias, initial, *, cell: str = "lstm", numerics: str = "mathematical",
                    zero_normalizer: Optional[bool] = None):
     """Return full history ``[S,B,T,H,D]`` and carry ``[S,B,1,H,D]`` (both fp32).
 
-    Same argument checks as flashrnn/flashrnn2/torch_backend.py:36-58. The only numerical policy
-    this backend implements is ``fp32_state_bf16_mma``; fp32 inputs follow the reference contract
-    exactly, bf16 inputs (Wx, R, b, initial rounded by the caller) are accepted as an extension.
+    Same signature, defaults and argument checks as flashrnn/flashrnn2/torch_backend.py:12-58. The only
+    numerical policy this backend implements is ``fp32_state_bf16_mma`` (tensor cores take bf16 operands);
+    the reference's default ``"mathematical"`` (unrounded fp32 contraction) is kept as the default of the
+    signature and rejected with a message that names the policy to pass, so that a caller who switches the
+    import never gets different arithmetic without asking for it. fp32 inputs follow the reference
+    contract exactly, bf16 inputs (Wx, R, b, initial rounded by the caller) are accepted as an extension.
     ``zero_normalizer`` (sLSTM only) overrides the "all initial n == 0" predicate of the first step; a
     batch/head shard passes the predicate of the unsharded call (state_contract.py:81-97).
     """
@@ -255,7 +276,8 @@ def flashrnn_torch(wx, recurrent, bias, initial, *, cell: str = "lstm", numerics
         raise ValueError(f"unsupported cell: {cell}")
     if numerics != "fp32_state_bf16_mma":
         if numerics == "mathematical":
-            raise ValueError("the B200 backend implements numerics='fp32_state_bf16_mma' only")
+            raise ValueError("the B200 backend has no unrounded fp32 contraction: pass numerics='fp32_state_bf16_mma' "
+                             "(fp32 state, R and the recurrent hidden operand rounded to bf16)")
         raise ValueError(f"unsupported numerical policy: {numerics}")
     tensors = (wx, recurrent, bias, initial)
     if any(t.layout != torch.strided for t in tensors):

@@ -4,7 +4,7 @@ Batch rows and heads are independent in the time loop (block-diagonal R, referen
 rank simply runs the kernels on its slice. What has to be shared:
 
 * under batch sharding every rank holds all of R and b, so dR/db are partial sums that are
-  all-reduced once per backward (the only collective of the path);
+  all-reduced once per backward, both in one call (the only collective of the path);
 * the sLSTM first-step predicate "all of the initial n is zero" is a reduction over the
   UNSHARDED initial state (state_contract.py:52-58, tests/flashrnn2/test_persistent_contract.py:67-133)
   and must be computed before slicing and handed to every rank.
@@ -49,32 +49,56 @@ def shard_inputs(Wx, R, b, states, world: int, rank: int, axis: Optional[str] = 
     return Wx[lo:hi], R, b, states[:, lo:hi], axis
 
 
+def _flat_view(dR: torch.Tensor, db: torch.Tensor) -> Optional[torch.Tensor]:
+    """One 1-D tensor covering dR followed by db when the two are adjacent pieces of one allocation (the backward
+    of the recurrence hands them out that way), else None."""
+    if (dR.dtype != db.dtype or not dR.is_contiguous() or not db.is_contiguous() or dR.device != db.device
+            or dR.untyped_storage().data_ptr() != db.untyped_storage().data_ptr()
+            or db.storage_offset() != dR.storage_offset() + dR.numel()):
+        return None
+    return torch.as_strided(dR, (dR.numel() + db.numel(),), (1,), dR.storage_offset())
+
+
 def allreduce_weight_grads(dR: torch.Tensor, db: torch.Tensor, axis: str, group=None) -> None:
-    """Sum dR/db over the ranks of a batch-sharded call (in place). A no-op for head sharding."""
+    """Sum dR/db over the ranks of a batch-sharded call (in place) with ONE all-reduce: the two gradients
+    travel as one flat buffer (no copy when they already are neighbours in memory). A no-op for head sharding."""
     import torch.distributed as dist
 
     if axis != "batch" or not dist.is_initialized() or dist.get_world_size(group) == 1:
         return
-    dist.all_reduce(dR, group=group)
-    dist.all_reduce(db, group=group)
+    flat = _flat_view(dR, db)
+    if flat is not None:
+        dist.all_reduce(flat, group=group)
+        return
+    flat = torch.cat((dR.reshape(-1), db.reshape(-1).to(dR.dtype)))
+    dist.all_reduce(flat, group=group)
+    dR.copy_(flat[:dR.numel()].view_as(dR))
+    db.copy_(flat[dR.numel():].view_as(db))
 
 
-class _SumGradOverRanks(torch.autograd.Function):
-    """Identity in forward; all-reduce (sum) of the gradient in backward."""
+class _SumWeightGrads(torch.autograd.Function):
+    """Identity on (R, b) in forward; one all-reduce (sum) of both gradients in backward."""
 
     @staticmethod
-    def forward(ctx, t, group):
+    def forward(ctx, R, b, group):
         ctx.group = group
-        return t.view_as(t)
+        return R.view_as(R), b.view_as(b)
 
     @staticmethod
-    def backward(ctx, grad):
-        import torch.distributed as dist
+    def backward(ctx, gR, gb):
+        if gR is None or gb is None:  # only one of the two is wanted: nothing to fuse
+            import torch.distributed as dist
 
-        grad = grad.contiguous()
-        if dist.is_initialized() and dist.get_world_size(ctx.group) > 1:
-            dist.all_reduce(grad, group=ctx.group)
-        return grad, None
+            for g in (gR, gb):
+                if g is not None and dist.is_initialized() and dist.get_world_size(ctx.group) > 1:
+                    dist.all_reduce(g, group=ctx.group)
+            return gR, gb, None
+        if not gR.is_contiguous():
+            gR = gR.contiguous()
+        if not gb.is_contiguous():
+            gb = gb.contiguous()
+        allreduce_weight_grads(gR, gb, "batch", ctx.group)
+        return gR, gb, None
 
 
 def flashrnn_sharded(Wx, R, b, states=None, function: str = "lstm", dtype: str = "bfloat16", axis: Optional[str] = None,
@@ -83,7 +107,7 @@ def flashrnn_sharded(Wx, R, b, states=None, function: str = "lstm", dtype: str =
 
     ``Wx`` / ``states`` are this rank's slice along ``axis`` ("batch" or "heads", see ``shard_inputs``).
     Under batch sharding ``R`` and ``b`` are the full replicated weights and their gradients are
-    summed over the ranks during backward (one NCCL all-reduce each, no collective in the time loop);
+    summed over the ranks during backward (ONE NCCL all-reduce of dR and db together, no collective in the time loop);
     under head sharding ``R`` and ``b`` are this rank's head slice and nothing is exchanged.
     For sLSTM pass ``zero_normalizer = slstm_zero_normalizer(unsharded initial state)``.
     Returns this rank's slice of ``(states[S,B,T,N,D], last[S,B,1,N,D])``.
@@ -93,8 +117,7 @@ def flashrnn_sharded(Wx, R, b, states=None, function: str = "lstm", dtype: str =
     if axis is None:
         raise ValueError("say along which axis this rank's tensors were sliced: 'batch' or 'heads'")
     if axis == "batch":
-        R = _SumGradOverRanks.apply(R, group)
-        b = _SumGradOverRanks.apply(b, group)
+        R, b = _SumWeightGrads.apply(R, b, group)
     elif axis != "heads":
         raise ValueError("axis must be 'batch' or 'heads'")
     return flashrnn(Wx, R, b, states, function=function, backend="b200", dtype=dtype, zero_normalizer=zero_normalizer)

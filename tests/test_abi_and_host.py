@@ -52,21 +52,28 @@ def test_plan_describes_the_headline_workload():
 def test_argument_checks_mirror_the_reference():
     wx, R, b, init = make_inputs("lstm", 2, 3, 2, 16, 0)
     with pytest.raises(ValueError, match="unsupported cell"):
-        flashrnn_torch(wx, R, b, init, cell="rnn")
-    with pytest.raises(ValueError, match="numerical policy|fp32_state_bf16_mma"):
+        flashrnn_torch(wx, R, b, init, cell="rnn", numerics="fp32_state_bf16_mma")
+    # the reference's default policy ("mathematical", unrounded fp32) is not implemented: the default call says
+    # which policy to pass instead of silently computing something else
+    with pytest.raises(ValueError, match="numerics='fp32_state_bf16_mma'"):
+        flashrnn_torch(wx, R, b, init)
+    with pytest.raises(ValueError, match="numerics='fp32_state_bf16_mma'"):
         flashrnn_torch(wx, R, b, init, numerics="mathematical")
+    with pytest.raises(ValueError, match="unsupported numerical policy"):
+        flashrnn_torch(wx, R, b, init, numerics="fp16")
+    k = dict(numerics="fp32_state_bf16_mma")
     with pytest.raises(ValueError, match="ranks"):
-        flashrnn_torch(wx[0], R, b, init)
+        flashrnn_torch(wx[0], R, b, init, **k)
     with pytest.raises(ValueError, match="same dtype"):
-        flashrnn_torch(wx, R.double(), b, init)
+        flashrnn_torch(wx, R.double(), b, init, **k)
     with pytest.raises(ValueError, match="gate count"):
-        flashrnn_torch(wx[:, :, :3], R, b, init)
+        flashrnn_torch(wx[:, :, :3], R, b, init, **k)
     with pytest.raises(ValueError, match=r"\[G,N,D,P\]"):
-        flashrnn_torch(wx, R[:, :1], b, init)
+        flashrnn_torch(wx, R[:, :1], b, init, **k)
     with pytest.raises(ValueError, match="bias"):
-        flashrnn_torch(wx, R, b[:3], init)
+        flashrnn_torch(wx, R, b[:3], init, **k)
     with pytest.raises(ValueError, match=r"\[S,B,1,N,D\]"):
-        flashrnn_torch(wx, R, b, init[:1])
+        flashrnn_torch(wx, R, b, init[:1], **k)
     with pytest.raises(ValueError, match="Unknown backend"):
         flashrnn(wx, R, b, backend="cuda_fused")
     with pytest.raises(ValueError, match="Unknown function"):
@@ -76,7 +83,7 @@ def test_argument_checks_mirror_the_reference():
 def test_there_is_no_cpu_path():
     wx, R, b, init = make_inputs("lstm", 2, 3, 2, 16, 0)
     with pytest.raises(RuntimeError, match="CUDA devices only"):
-        flashrnn_torch(wx, R, b, init)
+        flashrnn_torch(wx, R, b, init, numerics="fp32_state_bf16_mma")
 
 
 def test_wide_head_batches_are_split_over_launches():

@@ -14,6 +14,7 @@ from tests import _golden
 pytestmark = pytest.mark.gpu
 
 ATOL, RTOL_SCALED = 2e-2, 1e-2
+BF16_MMA = "fp32_state_bf16_mma"  # the only numerical policy of this backend; the reference's default "mathematical" is rejected
 
 
 def _check(name, key, got, ref, log):
@@ -127,9 +128,9 @@ def test_carry_continuation_is_exact(cuda_device):
 
     for cell in ("lstm", "slstm", "gru", "elman"):
         wx, R, b, initial = (t.to(cuda_device) for t in make_inputs(cell, 8, 32, 2, 64, 40, cell == "slstm"))
-        full, full_c = flashrnn_torch(wx, R, b, initial, cell=cell)
-        h1, c1 = flashrnn_torch(wx[:, :13], R, b, initial, cell=cell)
-        h2, c2 = flashrnn_torch(wx[:, 13:], R, b, c1, cell=cell)
+        full, full_c = flashrnn_torch(wx, R, b, initial, cell=cell, numerics=BF16_MMA)
+        h1, c1 = flashrnn_torch(wx[:, :13], R, b, initial, cell=cell, numerics=BF16_MMA)
+        h2, c2 = flashrnn_torch(wx[:, 13:], R, b, c1, cell=cell, numerics=BF16_MMA)
         assert torch.equal(torch.cat((h1, h2), dim=2), full), cell
         assert torch.equal(c2, full_c), cell
         assert torch.equal(full[:, :, -1:], full_c), cell
@@ -142,23 +143,23 @@ def test_bf16_inputs_and_flashrnn_entry(cuda_device):
 
     wx, R, b, initial = (t.to(cuda_device) for t in make_inputs("lstm", 8, 16, 3, 256, 41, True))
     h_a, c_a = flashrnn(wx, R, b, None, function="lstm", backend="b200", dtype="bfloat16")
-    h_b, c_b = flashrnn_torch(wx.bfloat16().float(), R, b, initial, cell="lstm")
+    h_b, c_b = flashrnn_torch(wx.bfloat16().float(), R, b, initial, cell="lstm", numerics=BF16_MMA)
     assert h_a.shape == (2, 8, 16, 3, 256) and c_a.shape == (2, 8, 1, 3, 256)
     assert torch.equal(h_a, h_b) and torch.equal(c_a, c_b)
     with pytest.raises(ValueError):
         flashrnn(wx, R, b, None, function="lstm", backend="cuda_fused")
 
 
-@pytest.mark.parametrize("cell", ["lstm", "elman"])
+@pytest.mark.parametrize("cell", ["lstm", "gru", "elman"])
 def test_matches_cudnn_layer(cell, cuda_device):
-    """Single head against torch.nn.LSTM / RNN (cuDNN, fp32) fed with the same precomputed Wx."""
+    """Single head against torch.nn.LSTM / GRU / RNN (cuDNN, fp32) fed with the same precomputed Wx."""
     from flashrnn_b200 import flashrnn_torch
     from flashrnn_b200.cudnn_baseline import torch_layer_from
     from flashrnn_b200.workloads import make_inputs
 
     B, T, D = 4, 12, 64
     wx, R, b, initial = (t.to(cuda_device) for t in make_inputs(cell, B, T, 1, D, 61))
-    hist, carry = flashrnn_torch(wx, R, b, initial, cell=cell)
+    hist, carry = flashrnn_torch(wx, R, b, initial, cell=cell, numerics=BF16_MMA)
     layer = torch_layer_from(R, b, cell)
     h0 = initial[0, :, 0, 0].unsqueeze(0).contiguous()
     state = (h0, initial[1, :, 0, 0].unsqueeze(0).contiguous()) if cell == "lstm" else h0
@@ -203,7 +204,7 @@ def test_repeatable_views_and_read_only_inputs(cuda_device):
     outs = []
     for _ in range(2):
         leaves = [t.detach().requires_grad_(True) for t in (wx_view, R, b, initial)]
-        h, c = flashrnn_torch(*leaves, cell=cell)
+        h, c = flashrnn_torch(*leaves, cell=cell, numerics=BF16_MMA)
         (h.square().sum() + c.sum()).backward()
         outs.append([h.detach(), c.detach()] + [t.grad for t in leaves])
     for a, bb in zip(*outs):
@@ -211,7 +212,7 @@ def test_repeatable_views_and_read_only_inputs(cuda_device):
     assert not wx_view.is_contiguous()
     for t, c in zip((wx_view, R, b, initial), copies):
         assert torch.equal(t, c)
-    h_ref, _ = flashrnn_torch(wx, R, b, initial, cell=cell)
+    h_ref, _ = flashrnn_torch(wx, R, b, initial, cell=cell, numerics=BF16_MMA)
     assert torch.equal(h_ref, outs[0][0])
 
 
@@ -247,7 +248,7 @@ def test_random_shapes_with_a_loss_on_the_hidden_state(cuda_device):
         d_carry[0] = torch.randn((B, 1, N, D), generator=gen)
         ref_h, ref_c, ref_g = port.forward_backward(wx, R, b, initial, cell, d_history, d_carry)
         leaves = [t.to(cuda_device).requires_grad_(True) for t in (wx, R, b, initial)]
-        h, c = flashrnn_torch(*leaves, cell=cell)
+        h, c = flashrnn_torch(*leaves, cell=cell, numerics=BF16_MMA)
         ((h * d_history.to(cuda_device)).sum() + (c * d_carry.to(cuda_device)).sum()).backward()
         torch.cuda.synchronize()
         poll_errors(block=True)

@@ -8,6 +8,7 @@ import pytest
 import torch
 
 pytestmark = pytest.mark.gpu
+BF16_MMA = "fp32_state_bf16_mma"
 
 
 def _inputs(cell, B, T, N, D, seed, dev, zero=False, dtype=torch.float32):
@@ -26,7 +27,7 @@ def test_output_modes_match_the_full_call(shape, cuda_device):
     cell, B, T, N, D = shape
     for zero in ((False, True) if cell == "slstm" else (False,)):
         wx, R, b, init = _inputs(cell, B, T, N, D, 71, cuda_device, zero)
-        ref_h, ref_c = flashrnn_torch(wx, R, b, init, cell=cell)
+        ref_h, ref_c = flashrnn_torch(wx, R, b, init, cell=cell, numerics=BF16_MMA)
         for mode in ("full", "hidden", "last"):
             seq = PreparedSequence(wx, R, b, init, cell, output_mode=mode)
             out, final = seq.run()
@@ -46,7 +47,7 @@ def test_captured_graph_replays_on_updated_inputs(shape, cuda_device):
     seq = PreparedSequence(wx, R, b, init, cell, output_mode="hidden").capture()
     out, final = seq.run()
     seq.check()
-    ref_h, ref_c = flashrnn_torch(wx.float(), R, b, init, cell=cell)
+    ref_h, ref_c = flashrnn_torch(wx.float(), R, b, init, cell=cell, numerics=BF16_MMA)
     assert torch.equal(out, ref_h[0]) and torch.equal(final, ref_c)
     # new inputs and a non-zero normaliser, written into the bound tensors: the replay must pick both up
     wx2, _, _, init2 = _inputs(cell, B, T, N, D, 73, cuda_device, zero=False, dtype=torch.bfloat16)
@@ -54,7 +55,7 @@ def test_captured_graph_replays_on_updated_inputs(shape, cuda_device):
     seq.initial.copy_(init2)
     out, final = seq.run()
     seq.check()
-    ref_h, ref_c = flashrnn_torch(wx2.float(), R, b, init2, cell=cell)
+    ref_h, ref_c = flashrnn_torch(wx2.float(), R, b, init2, cell=cell, numerics=BF16_MMA)
     assert torch.equal(out, ref_h[0]) and torch.equal(final, ref_c)
     with pytest.raises(ValueError):
         seq.capture()
