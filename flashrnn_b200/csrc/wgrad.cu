@@ -109,7 +109,12 @@ __global__ void __launch_bounds__(kThreads, 1) wgrad_kernel(const WgradParams p)
     ++issued;
     if (!ok) break;
   }
-  if (!ok && tid == 0) atomicCAS(p.err, 0, kErrWaitMma);
+  if (!ok && tid == 0) {
+    atomicCAS(p.err, 0, kErrWaitMma);
+    // the chunk whose commit was not seen may still be on the tensor core: wait for it once more (no abort
+    // flag: the commit completes by itself) before the tensor memory is released below
+    mbar_wait_bounded<false, true>(smem_u32(&s_bar), (issued - 1) & 1, 2000000000ull, nullptr);
+  }
   tc_fence_after_sync();
   // epilogue: accumulator rows -> global (row = (g, o), contiguous along p)
   {
@@ -245,7 +250,13 @@ wgrad_tma_kernel(const WgradParams p, const __grid_constant__ CUtensorMap dgr_ma
         }
         umma_commit(smem_u32(&s_empty[s]));  // the stage is free once these MMAs have read it
       }
-      if (ok) umma_commit(smem_u32(&s_acc));
+      // One commit covers every MMA this thread has issued, also after a failed wait. The issuing thread then
+      // waits for it itself (the commit completes without any other party, hence no abort flag) so that the
+      // tensor memory and the stages are never released while an MMA still runs.
+      if (n_chunks > 0) {
+        umma_commit(smem_u32(&s_acc));
+        mbar_wait_bounded<false, true>(smem_u32(&s_acc), 0, kLimit, nullptr);
+      }
     }
   } else {
     const int q = warp & 3;  // TMEM lane quarter this warp may read

@@ -64,7 +64,7 @@ def test_cuda_matches_reference_vectors(name, cuda_device):
 # (cell, B, T, N, D, seed, zero_initial): shapes that exercise every launch plan
 SHAPES = [
     ("lstm", 8, 48, 3, 256, 21, False),    # headline geometry: cluster of 8, batch tile 8
-    ("lstm", 16, 20, 2, 128, 22, False),   # batch tile 16
+    ("lstm", 16, 20, 2, 128, 22, False),   # two 8-row tiles per head (16-row tiles: tests/test_gpu_full_length.py)
     ("lstm", 20, 12, 1, 64, 23, False),    # two batch tiles, the second ragged (4 rows)
     ("lstm", 3, 17, 2, 48, 24, False),     # unit 16, cluster of 3, ragged batch
     ("lstm", 4, 10, 1, 384, 25, False),    # cluster of 12 (non-portable size)
