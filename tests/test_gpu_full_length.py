@@ -148,8 +148,11 @@ def test_sixteen_row_tiles_on_the_cluster_path(shape, cuda_device):
     if cell == "slstm":  # gradient through h only (the normaliser clamp is discontinuous, see the fixed shapes)
         d_history[1:] = 0
         d_carry[1:] = 0
-    ref_h, ref_c, ref_g = port.forward_backward(wx, R, b, init, cell, d_history, d_carry)
     for dtype in (torch.float32, torch.bfloat16):
+        # the bf16 arm is compared with the oracle on the same rounded Wx (kernel error alone: at T = 4 ... 32 one
+        # flipped sLSTM clamp decision from input rounding would otherwise dominate the few-step gradients)
+        wx_seen = wx if dtype == torch.float32 else _bf(wx)
+        ref_h, ref_c, ref_g = port.forward_backward(wx_seen, R, b, init, cell, d_history, d_carry)
         leaves = [t.to(cuda_device).requires_grad_(True) for t in (wx.to(dtype), R, b, init)]
         if dtype == torch.bfloat16:
             from flashrnn_b200 import flashrnn
@@ -162,4 +165,4 @@ def test_sixteen_row_tiles_on_the_cluster_path(shape, cuda_device):
         poll_errors(block=True)
         got = [h.detach().cpu(), c.detach().cpu()] + [t.grad.float().cpu() for t in leaves]
         _compare(f"tile16 {cell} B{B} T{T} N{N} D{D} {str(dtype)[6:]}", got, [ref_h, ref_c] + list(ref_g),
-                 "fp32 originals")
+                 "fp32 originals" if dtype == torch.float32 else "rounded inputs")
