@@ -28,6 +28,8 @@ ERROR_TEXT = {
     105: "epilogue barrier timed out",
     106: "partial sums of a peer CTA never arrived",
     107: "dg operand barrier timed out",
+    108: "a peer rank never announced that its exchange buffer is ready",
+    109: "a stage of the streamed weight operand never arrived or was never released",
 }
 
 
@@ -41,6 +43,26 @@ class Plan(ctypes.Structure):
         ("cache_bytes", c_int64), ("hbf_bytes", c_int64), ("dgr_bytes", c_int64), ("dbpart_bytes", c_int64),
         ("wgrad_work_bytes", c_int64), ("wgrad_ksplit", c_int), ("exchange", c_int), ("xchg_bytes", c_int64),
         ("fwd_ksplit", c_int), ("fwd_ctas", c_int), ("bwd_ksplit", c_int), ("fwd_batch_tile", c_int),
+    ]
+
+
+class MgShard(ctypes.Structure):
+    """Mirror of ``frnn_b200_mg_shard_t``."""
+
+    _fields_ = [("P", c_int), ("rank", c_int), ("ranks_here", c_int), ("epoch", c_int), ("k_tmem_max", c_int),
+                ("ring_stages_max", c_int), ("buffers", c_void_p * 8), ("ready", c_void_p * 8)]
+
+
+class MgPlan(ctypes.Structure):
+    """Mirror of ``frnn_b200_mg_plan_t``."""
+
+    _fields_ = [
+        ("supported", c_int), ("local_width", c_int), ("fwd_ksplit", c_int), ("fwd_ctas", c_int),
+        ("fwd_k_tmem", c_int), ("fwd_ring_chunks", c_int), ("fwd_ring_stages", c_int), ("fwd_resident", c_int),
+        ("bwd_ksplit", c_int), ("bwd_ctas", c_int),
+        ("bwd_k_tmem", c_int), ("bwd_ring_chunks", c_int), ("bwd_ring_stages", c_int), ("bwd_resident", c_int),
+        ("hbf_bytes", c_int64), ("dgr_bytes", c_int64), ("cache_bytes", c_int64), ("r_cols_bytes", c_int64),
+        ("dbpart_bytes", c_int64),
     ]
 
 
@@ -61,6 +83,20 @@ SIGNATURES = {
                                 c_int, c_int, c_void_p, c_void_p]),
     "frnn_b200_wgrad_noalloc": (c_int, [c_int, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_int, c_int,
                                         c_int, c_void_p, c_void_p]),
+    "frnn_b200_mg_plan": (c_int, [c_int, c_int, c_int, c_int, c_int, POINTER(MgShard), POINTER(MgPlan)]),
+    "frnn_b200_mg_forward": (c_int, [c_int, c_void_p, c_int, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p,
+                                     POINTER(MgShard), c_int, c_int, c_int, c_int, c_int, c_void_p, c_void_p]),
+    "frnn_b200_mg_gather_columns": (c_int, [c_int, POINTER(c_void_p), c_void_p, POINTER(MgShard), c_int, c_void_p]),
+    "frnn_b200_mg_backward": (c_int, [c_int, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_int,
+                                      c_void_p, c_void_p, POINTER(MgShard), c_int, c_int, c_int, c_int, c_int, c_void_p,
+                                      c_void_p]),
+    "frnn_b200_mg_wgrad": (c_int, [c_int, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, POINTER(MgShard), c_int, c_int,
+                                   c_int, c_int, c_void_p, c_void_p]),
+    "frnn_b200_peer_alloc": (c_int, [ctypes.c_size_t, POINTER(c_void_p)]),
+    "frnn_b200_peer_free": (c_int, [c_void_p]),
+    "frnn_b200_peer_export": (c_int, [c_void_p, ctypes.c_char_p]),
+    "frnn_b200_peer_open": (c_int, [ctypes.c_char_p, POINTER(c_void_p)]),
+    "frnn_b200_peer_close": (c_int, [c_void_p]),
 }
 
 _lib = None

@@ -19,7 +19,8 @@ PKG = Path(__file__).resolve().parent
 CSRC = PKG / "csrc"
 LIB_DIR = PKG / "lib"
 LIB_PATH = LIB_DIR / "libflashrnn_b200.so"
-SOURCES = ("capi.cu", "recurrent_fwd.cu", "recurrent_fwd_ksplit.cu", "recurrent_bwd.cu", "recurrent_bwd_ksplit.cu", "wgrad.cu")
+SOURCES = ("capi.cu", "capi_mg.cu", "recurrent_fwd.cu", "recurrent_fwd_ksplit.cu", "recurrent_bwd.cu", "recurrent_bwd_ksplit.cu",
+           "recurrent_mg_fwd.cu", "recurrent_mg_bwd.cu", "wgrad.cu")
 NVCC_FLAGS = (
     "-gencode", "arch=compute_100a,code=sm_100a", "-O3", "-std=c++17", "-lineinfo",
     "-Xcompiler", "-fPIC",
@@ -60,7 +61,7 @@ def build(force: bool = False, verbose: bool = False) -> Path:
         if verbose and res.stderr:
             print(res.stderr, file=sys.stderr)
 
-    with concurrent.futures.ThreadPoolExecutor(max_workers=4) as pool:
+    with concurrent.futures.ThreadPoolExecutor(max_workers=8) as pool:
         list(pool.map(run, jobs))
     objs = [str(obj_dir / (s + ".o")) for s in sources]
     if jobs or not LIB_PATH.exists():

@@ -93,7 +93,7 @@ bool cell_counts(int cell, CellCounts* c) {
 }  // namespace
 
 int make_tensor_map(CUtensorMap* map, const void* base, int elem_bytes, int rank, const uint64_t* dims,
-                    const uint32_t* box, bool swizzle128) {
+                    const uint32_t* box, bool swizzle128, const uint64_t* stride_dims) {
   EncodeTiledFn fn = encode_tiled_fn();
   if (fn == nullptr) return -4;
   cuuint64_t gdims[5];
@@ -104,7 +104,7 @@ int make_tensor_map(CUtensorMap* map, const void* base, int elem_bytes, int rank
     gdims[i] = dims[i];
     gbox[i] = box[i];
     estr[i] = 1;
-    stride *= dims[i];
+    stride *= stride_dims != nullptr ? stride_dims[i] : dims[i];
     if (i < rank - 1) gstrides[i] = stride;
   }
   const CUtensorMapDataType dt = elem_bytes == 4 ? CU_TENSOR_MAP_DATA_TYPE_FLOAT32 : CU_TENSOR_MAP_DATA_TYPE_BFLOAT16;

@@ -21,6 +21,8 @@ enum : int {
   kErrWaitEpi = 105,    // epilogue-internal barrier
   kErrWaitPart = 106,   // partial sums of a peer CTA never arrived
   kErrWaitDg = 107,     // backward: dg operand barrier
+  kErrWaitReady = 108,  // multi-GPU: a peer never announced that its exchange buffer is ready
+  kErrWaitRing = 109,   // multi-GPU: a stage of the streamed weight operand never arrived / was never released
 };
 
 struct FwdParams {
@@ -156,7 +158,9 @@ inline uint32_t tmem_cols_pow2(int needed, uint32_t minimum) {
 }
 
 // Host: build a tiled tensor map (no swizzle, no interleave). dims/box innermost first.
+// `stride_dims` (optional): extents the strides are computed from when the described tensor is a window of a
+// larger dense array (e.g. the first T of T + 1 time slots).
 int make_tensor_map(CUtensorMap* map, const void* base, int elem_bytes, int rank, const uint64_t* dims,
-                    const uint32_t* box, bool swizzle128 = false);
+                    const uint32_t* box, bool swizzle128 = false, const uint64_t* stride_dims = nullptr);
 
 }  // namespace frnn

@@ -240,6 +240,20 @@ __device__ __forceinline__ uint64_t umma_smem_desc_mn_sw128(uint32_t smem_addr, 
   return d;
 }
 
+// Descriptor for K-major operand tiles written by TMA with the 128-byte swizzle: every row holds 64
+// bf16 (128 B) along K, 8 rows form a 1024-byte swizzle atom, atoms of consecutive 8-row groups are
+// 1024 B apart. The tile base must be 1024-byte aligned; a K offset inside the 128-byte row is
+// added to the start address (16 k = 32 B).
+__device__ __forceinline__ uint64_t umma_smem_desc_k_sw128(uint32_t smem_addr) {
+  uint64_t d = 0;
+  d |= static_cast<uint64_t>((smem_addr & 0x3FFFFu) >> 4);
+  d |= static_cast<uint64_t>(1u) << 16;                       // leading byte offset: unused with swizzled K-major
+  d |= static_cast<uint64_t>((1024u >> 4) & 0x3FFFu) << 32;  // stride byte offset between 8-row groups
+  d |= 1ull << 46;
+  d |= 2ull << 61;  // SWIZZLE_128B
+  return d;
+}
+
 // Instruction descriptor: bf16 x bf16 -> fp32, dense. `a_mn` / `b_mn` select MN-major operands.
 __host__ __device__ constexpr uint32_t umma_idesc_bf16(int m, int n, bool a_mn, bool b_mn) {
   return (1u << 4)      // accumulator format F32
@@ -329,6 +343,36 @@ __device__ __forceinline__ void st_async_v4_b32(uint32_t cluster_addr, uint32_t 
       : "memory");
 }
 
+
+__device__ __forceinline__ void st_async_v2_b32(uint32_t cluster_addr, uint32_t a, uint32_t b, uint32_t cluster_bar) {
+  asm volatile("st.async.weak.shared::cluster.mbarrier::complete_tx::bytes.v2.b32 [%0], {%1, %2}, [%3];" ::"r"(
+                   cluster_addr),
+               "r"(a), "r"(b), "r"(cluster_bar)
+               : "memory");
+}
+
+// System-scope variants for exchange buffers that GPUs of one node write into each other's memory
+// (peer stores over NVLink): the receiver polls its OWN memory, the sender stores to the peer's.
+__device__ __forceinline__ uint4 ld_relaxed_sys_v4(const void* p) {
+  uint4 v;
+  asm volatile("ld.relaxed.sys.global.v4.u32 {%0, %1, %2, %3}, [%4];"
+               : "=r"(v.x), "=r"(v.y), "=r"(v.z), "=r"(v.w)
+               : "l"(p)
+               : "memory");
+  return v;
+}
+__device__ __forceinline__ void st_relaxed_sys_v4(void* p, uint4 v) {
+  asm volatile("st.relaxed.sys.global.v4.u32 [%0], {%1, %2, %3, %4};" ::"l"(p), "r"(v.x), "r"(v.y), "r"(v.z), "r"(v.w)
+               : "memory");
+}
+__device__ __forceinline__ int ld_acquire_sys_s32(const int* p) {
+  int v;
+  asm volatile("ld.acquire.sys.global.s32 %0, [%1];" : "=r"(v) : "l"(p) : "memory");
+  return v;
+}
+__device__ __forceinline__ void st_release_sys_s32(int* p, int v) {
+  asm volatile("st.release.sys.global.s32 [%0], %1;" ::"l"(p), "r"(v) : "memory");
+}
 
 // Relaxed (strong, gpu scope) 16-byte global accesses of the flag-in-data exchange: the receiver
 // polls the data words themselves, every 32-bit word carries its own "arrived" information (it

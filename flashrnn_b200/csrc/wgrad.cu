@@ -27,6 +27,10 @@ struct WgradParams {
   int ksplit;
   int chunks_per_split;
   int pack;     // heads that share one 64-wide TMA box (narrow heads, D = 16 or 32), else 1
+  // Row window (TMA kernel, pack == 1): the contraction produces only the rows o in [m_off, m_off + Dm) of every
+  // gate (a rank's units of a row-sharded head) and writes them as [GR][N][out_rows][D] starting at `out`.
+  // Dm = out_rows = D and m_off = 0 describe the whole matrix.
+  int Dm, m_off, out_rows;
 };
 
 // Both operands are MN-major (the contraction index is the slow one in memory). Un-swizzled
@@ -167,7 +171,8 @@ wgrad_tma_kernel(const WgradParams p, const __grid_constant__ CUtensorMap dgr_ma
   const int mtile = blockIdx.x / npt, ptile = blockIdx.x % npt;
   const int n = blockIdx.y, split = blockIdx.z;
   const int m0 = mtile * 128, p0 = ptile * NP;
-  const int M = GR * D;
+  const int Dm = p.Dm;
+  const int M = GR * Dm;
   // Narrow heads (pack > 1): one box spans `pack` neighbouring heads of one gate, so the 128 x 64
   // tile holds pack x pack head blocks per gate of which only the diagonal ones are kept;
   // blockIdx.x = gate pair, blockIdx.y = head group.
@@ -220,7 +225,7 @@ wgrad_tma_kernel(const WgradParams p, const __grid_constant__ CUtensorMap dgr_ma
         if (pack == 1) {
           for (int h = 0; h < 2; ++h) {
             const int m = m0 + 64 * h;
-            tma_load_5d(sa + h * 8192u, &dgr_map, bar, m % D, n, m / D, t0, b);
+            tma_load_5d(sa + h * 8192u, &dgr_map, bar, p.m_off + m % Dm, n, m / Dm, t0, b);
           }
           for (int j = 0; j < NP / 64; ++j) tma_load_4d(sb + j * 8192u, &hbf_map, bar, p0 + 64 * j, n, t0, b);
         } else {
@@ -270,8 +275,9 @@ wgrad_tma_kernel(const WgradParams p, const __grid_constant__ CUtensorMap dgr_ma
     if (pack == 1) {
       float* dst = nullptr;
       if (m < M) {
-        const int g = m / D, o = m % D;
-        dst = p.out + static_cast<size_t>(split) * GR * p.N * D * D + ((static_cast<size_t>(g) * p.N + n) * D + o) * D + p0;
+        const int g = m / Dm, o = m % Dm;
+        dst = p.out + static_cast<size_t>(split) * GR * p.N * p.out_rows * D +
+              ((static_cast<size_t>(g) * p.N + n) * p.out_rows + o) * D + p0;
       }
       for (int c8 = 0; c8 < NP; c8 += 8) {
         uint32_t r[8] = {0u, 0u, 0u, 0u, 0u, 0u, 0u, 0u};
@@ -327,6 +333,19 @@ __global__ void reduce_parts_kernel(const float* __restrict__ parts, float* __re
   *reinterpret_cast<float4*>(out + i) = acc;
 }
 
+// out[i] = sum over parts of parts[part * part_stride + i], i < n (n a multiple of 4)
+__global__ void reduce_parts_strided_kernel(const float* __restrict__ parts, float* __restrict__ out, int n,
+                                            long long part_stride, int nparts) {
+  const int i = (blockIdx.x * blockDim.x + threadIdx.x) * 4;
+  if (i >= n) return;
+  float4 acc = *reinterpret_cast<const float4*>(parts + i);
+  for (int s = 1; s < nparts; ++s) {
+    const float4 v = *reinterpret_cast<const float4*>(parts + s * part_stride + i);
+    acc.x += v.x; acc.y += v.y; acc.z += v.z; acc.w += v.w;
+  }
+  *reinterpret_cast<float4*>(out + i) = acc;
+}
+
 }  // namespace
 
 // The TMA kernel needs whole 64-element boxes along both output dimensions; heads of 16 or 32
@@ -370,6 +389,7 @@ int wgrad_launch(int gr, int gb, const __nv_bfloat16* dgr, const __nv_bfloat16* 
   p.err = err;
   p.B = B; p.T = T; p.N = N; p.D = D; p.GR = gr;
   p.NP = np; p.ksplit = ksplit; p.chunks_per_split = cps;
+  p.Dm = D; p.m_off = 0; p.out_rows = D;
   const int pack = wgrad_pack(D);
   p.pack = pack;
   const int mtiles = pack > 1 ? (gr + 1) / 2 : (gr * D + 127) / 128;
@@ -419,6 +439,46 @@ int wgrad_launch(int gr, int gb, const __nv_bfloat16* dgr, const __nv_bfloat16* 
   }
   const long long nb = static_cast<long long>(gb) * N * D;
   reduce_parts_kernel<<<static_cast<unsigned>((nb / 4 + 255) / 256), 256, 0, s>>>(db_part, db, nb, n_btiles);
+  return static_cast<int>(cudaGetLastError());
+}
+
+// Row-sharded wide head (one head, N = 1): dR[g, o, p] for the rows o in [m_off, m_off + Dm) only, from this
+// rank's full-width histories dgr [B][T][GR][D] and hbf [B][T+1][D]; slot T of hbf is never read (the tensor map
+// ends at T, reads beyond it are filled with zeros), so it need not be written. db = sum of `n_parts` partial rows
+// db_part [n_parts][GB][ldb] -> db [GB][ldb] restricted to the window [x0, x0 + Dm).
+int wgrad_launch_rows(int gr, int gb, const __nv_bfloat16* dgr, const __nv_bfloat16* hbf, const float* db_part, int n_parts,
+                      float* dR, float* db, int* err, int B, int T, int D, int Dm, int m_off, int out_rows, int ldb, int x0,
+                      cudaStream_t s) {
+  if (D % 256 != 0 || Dm % 128 != 0 || m_off % 64 != 0) return -2;
+  WgradParams p{};
+  p.dgr = dgr; p.hbf = hbf; p.out = dR; p.err = err;
+  p.B = B; p.T = T; p.N = 1; p.D = D; p.GR = gr;
+  p.NP = 256; p.ksplit = 1;
+  p.chunks_per_split = B * ((T + kKC - 1) / kKC);
+  p.pack = 1;
+  p.Dm = Dm; p.m_off = m_off; p.out_rows = out_rows;
+  CUtensorMap dgr_map, hbf_map;
+  const uint64_t ddims[5] = {static_cast<uint64_t>(D), 1u, static_cast<uint64_t>(gr), static_cast<uint64_t>(T),
+                             static_cast<uint64_t>(B)};
+  const uint32_t dbox[5] = {64u, 1u, 1u, static_cast<uint32_t>(kKC), 1u};
+  const uint64_t hdims[4] = {static_cast<uint64_t>(D), 1u, static_cast<uint64_t>(T), static_cast<uint64_t>(B)};
+  const uint64_t hstride[4] = {static_cast<uint64_t>(D), 1u, static_cast<uint64_t>(T + 1), static_cast<uint64_t>(B)};
+  const uint32_t hbox[4] = {64u, 1u, static_cast<uint32_t>(kKC), 1u};
+  if (make_tensor_map(&dgr_map, dgr, 2, 5, ddims, dbox, true) != 0) return -4;
+  if (make_tensor_map(&hbf_map, hbf, 2, 4, hdims, hbox, true, hstride) != 0) return -4;
+  const int smem = kTmaStages * (16384 + 256 * 128) + 1024;
+  cudaError_t e = cudaFuncSetAttribute(wgrad_tma_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, smem);
+  if (e != cudaSuccess) return static_cast<int>(e);
+  dim3 grid(static_cast<unsigned>((gr * Dm / 128) * (D / 256)), 1u, 1u);
+  wgrad_tma_kernel<<<grid, kTmaThreads, smem, s>>>(p, dgr_map, hbf_map);
+  e = cudaGetLastError();
+  if (e != cudaSuccess) return static_cast<int>(e);
+  // db: the window of every gate row is reduced separately (the rows are ldb apart)
+  for (int g = 0; g < gb; ++g) {
+    reduce_parts_strided_kernel<<<static_cast<unsigned>((Dm / 4 + 127) / 128), 128, 0, s>>>(
+        db_part + static_cast<size_t>(g) * ldb + x0, db + static_cast<size_t>(g) * ldb + x0, Dm,
+        static_cast<long long>(gb) * ldb, n_parts);
+  }
   return static_cast<int>(cudaGetLastError());
 }
 

@@ -145,6 +145,89 @@ int frnn_b200_wgrad_noalloc(int cell, const void* dgr, const void* hbf, const fl
                             float* dR, float* db, int B, int T, int N, int D, int* err,
                             void* stream);
 
+/* ------------------------------------------------------------------------------------------------
+ * One WIDE head (N = 1, D a multiple of 256) whose recurrent matrix is split over P GPUs of a node:
+ * rank r owns the hidden units [r*Dl, (r+1)*Dl), Dl = D/P (a multiple of 128): the rows R[g, o in slice, :] in the
+ * forward pass and the columns R[g, :, p in slice] in the backward pass; the per-step operand (round_bf16(h_t),
+ * round_bf16(dG_t)) is exchanged by peer stores issued inside the kernels, receivers poll their own memory.
+ * Counterparts in the reference: flashrnn/flashrnn2/multi_gpu.py:87-297 (forward; peer stores and counters
+ * :224-238, bounded waits :30-32,62-73, address tables before the first launch :429) and the `_mg` entry point
+ * flashrnn/flashrnn2/hybrid_bw2d.cu:645-661 (backward with peer tables, rank, np).
+ *
+ * Local tensors of a rank are dense with row length Dl: Wx[B,T,GW,Dl], R rows [GR,Dl,D], R columns [GR,D,Dl],
+ * b[GB,Dl], states [S,B,T|1,Dl], dR rows [GR,Dl,D]. With ranks_here == P all ranks run as ONE launch on one GPU
+ * (how the multi-rank arithmetic is tested on a single device): the local tensors then are the full-width ones
+ * (row length D) and rank r works on the columns [r*Dl, (r+1)*Dl) of them.
+ * At most 32 batch rows per call. Every wait inside the kernels is bounded by wait_limit_ms (0 = 10 s: ranks
+ * start their kernels at different times); a wait that runs out is reported through err[0..2] of that rank
+ * (108: a peer never became ready, 109: weight stage) and the kernel returns. */
+typedef struct frnn_b200_mg_shard {
+  int P;               /* ranks the head is split over, 1..8                                              */
+  int rank;            /* this rank (the first rank of the launch)                                        */
+  int ranks_here;      /* 1: one rank per launch (one process per GPU); P: all ranks in one launch        */
+  int epoch;           /* identical on all ranks, larger in every later call that uses the same `ready`   */
+  int k_tmem_max;      /* 0 = default; caps the weight columns kept in tensor memory (tuning / tests)     */
+  int ring_stages_max; /* 0 = default; caps the shared-memory stages of the weight operand                */
+  void* buffers[8];    /* every rank's exchange buffer of this call, as addresses valid on THIS device:
+                          forward  bf16 [B][T+1][D]   (plan.hbf_bytes), afterwards operand of the dR contraction
+                          backward bf16 [B][T][GR][D] (plan.dgr_bytes), likewise. The call fills the buffers of
+                          its own rank(s) with 0xFF bytes before the launch.                             */
+  int* ready[8];       /* every rank's int[8] flag array (zeroed once when allocated); unused when
+                          ranks_here == P                                                                 */
+} frnn_b200_mg_shard_t;
+
+typedef struct frnn_b200_mg_plan {
+  int supported;
+  int local_width;                 /* Dl */
+  int fwd_ksplit, fwd_ctas;        /* CTAs per row tile (cluster width) and per launch                     */
+  int fwd_k_tmem, fwd_ring_chunks, fwd_ring_stages, fwd_resident;
+  int bwd_ksplit, bwd_ctas;
+  int bwd_k_tmem, bwd_ring_chunks, bwd_ring_stages, bwd_resident;
+  int64_t hbf_bytes, dgr_bytes;    /* one rank's exchange buffers                                          */
+  int64_t cache_bytes;             /* fp32 [B][T][GC][row length]                                          */
+  int64_t r_cols_bytes;            /* bf16 [GR][D][row length]                                             */
+  int64_t dbpart_bytes;            /* fp32 [bwd_ksplit][GB][row length]                                    */
+} frnn_b200_mg_plan_t;
+
+int frnn_b200_mg_plan(int cell, int B, int T, int D, int wx_bf16, const frnn_b200_mg_shard_t* shard,
+                      frnn_b200_mg_plan_t* out);
+
+/* Forward (multi_gpu.py:87-297). sh->buffers = the ranks' h histories. Outputs: history [S,B,T,Dl], carry [S,B,1,Dl],
+ * cache (NULL for inference). The h history of this rank holds round_bf16(h) of ALL units afterwards (slots 0..T-1). */
+int frnn_b200_mg_forward(int cell, const void* wx, int wx_bf16, const void* r_rows, const float* bias,
+                         const float* initial, float* history, float* carry, float* cache,
+                         const frnn_b200_mg_shard_t* shard, int B, int T, int D, int slstm_zero_first,
+                         int wait_limit_ms, int* err, void* stream);
+
+/* r_cols[g, o, pl] = R[g, o, rank*Dl + pl] from the ranks' row slices (r_rows_all[q] = rank q's [GR,Dl,D], addresses
+ * valid on this device; plain peer loads). Once per call of the backward (hybrid_bw2d.cu:645-661 takes the
+ * column slice as an input). */
+int frnn_b200_mg_gather_columns(int cell, const void* const* r_rows_all, void* r_cols,
+                                const frnn_b200_mg_shard_t* shard, int D, void* stream);
+
+/* Backward (hybrid_bw2d.cu:507-552,645-661). sh->buffers = the ranks' dG histories. Outputs: dwx [B,T,GW,Dl] in the
+ * Wx dtype, d_initial [S,B,1,Dl], db_part [plan.bwd_ksplit][GB][Dl]. */
+int frnn_b200_mg_backward(int cell, const float* cache, const float* history, const float* initial,
+                          const void* r_cols, const float* d_history, const float* d_carry, void* dwx, int wx_bf16,
+                          float* d_initial, float* db_part, const frnn_b200_mg_shard_t* shard, int B, int T, int D,
+                          int slstm_zero_first, int wait_limit_ms, int* err, void* stream);
+
+/* dR rows [GR,Dl,D] of this rank's units and db [GB,Dl] from this rank's two histories: disjoint slices, no
+ * reduction over ranks (the reference gathers dG on rank 0 instead, flashrnn/flashrnn2/hybrid_bw.py:280-286). */
+int frnn_b200_mg_wgrad(int cell, const void* dgr_all, const void* hbf_all, const float* db_part, float* dR_rows,
+                       float* db, const frnn_b200_mg_shard_t* shard, int B, int T, int D, int bwd_ksplit, int* err,
+                       void* stream);
+
+/* Buffers that other processes of the node can address (cudaMalloc + CUDA IPC; no multicast object is created).
+ * Set-up calls, never used on the hot path: alloc / free in the owning process, export there, open / close in
+ * the peers (open enables peer access). The reference builds its peer address tables the same way before the
+ * first launch (flashrnn/flashrnn2/multi_gpu.py:313-335,429). */
+int frnn_b200_peer_alloc(size_t bytes, void** ptr);
+int frnn_b200_peer_free(void* ptr);
+int frnn_b200_peer_export(void* ptr, unsigned char handle[64]);
+int frnn_b200_peer_open(const unsigned char handle[64], void** ptr);
+int frnn_b200_peer_close(void* ptr);
+
 #ifdef __cplusplus
 }
 #endif

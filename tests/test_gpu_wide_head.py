@@ -1,0 +1,151 @@
+"""The row-sharded wide head (one head split over P ranks, per-step exchange by stores into every rank's history
+buffer) against the CPU oracle.
+
+On one GPU all P ranks run as ONE cooperative launch over slices of full-width tensors (`emulate_ranks`): the same
+kernels, index arithmetic and exchange protocol as one process per GPU, without kernels that wait on one another
+being separate launches on one device. The two-GPU case runs one process per GPU with real peer stores.
+"""
+
+import os
+import socket
+
+import pytest
+import torch
+
+from oracle import recurrence_port as port
+from tests import _golden
+
+pytestmark = pytest.mark.gpu
+
+ATOL, RTOL_SCALED = 2e-2, 1e-2
+KEYS = ("history", "carry", "dwx", "dR", "db", "d_initial")
+
+
+def _inputs(cell, B, T, D, seed):
+    from flashrnn_b200.workloads import make_inputs
+
+    wx, R, b, init = make_inputs(cell, B, T, 1, D, seed, zero_initial=(cell == "slstm"))
+    S = port.SIZES[cell][3]
+    gen = torch.Generator().manual_seed(seed + 500)
+    d_history = torch.randn((S, B, T, 1, D), generator=gen)
+    d_carry = torch.randn((S, B, 1, 1, D), generator=gen)
+    if cell == "slstm":   # gradient through h only (the normaliser clamp is discontinuous in the forward values)
+        d_history[1:] = 0
+        d_carry[1:] = 0
+    return wx, R, b, init, d_history, d_carry
+
+
+def _check(name, got, ref):
+    rows = [_golden.report(k, g.detach().float().cpu(), r) for k, g, r in zip(KEYS, got, ref)]
+    print(name, " ".join(f"{r['name']}: {r['max_abs']:.2e}/{r['scaled']:.2e}" for r in rows))
+    for r, g in zip(rows, got):
+        assert torch.isfinite(g).all(), (name, r["name"])
+        assert r["max_abs"] <= ATOL or r["scaled"] <= RTOL_SCALED, (name, r)
+
+
+# (cell, B, T, D, P, k_tmem_max, ring_stages_max, bf16 Wx)
+EMULATED = [
+    ("lstm", 8, 12, 256, 1, 0, 0, False),
+    ("lstm", 5, 9, 256, 2, 0, 0, True),      # ragged batch, two ranks
+    ("lstm", 32, 6, 512, 4, 0, 0, False),    # full 32-row tile, four ranks
+    ("lstm", 3, 7, 1024, 8, 0, 0, True),     # eight ranks of 128 units
+    ("slstm", 6, 10, 512, 2, 0, 0, False),
+    ("gru", 7, 8, 512, 4, 0, 0, True),
+    ("elman", 4, 11, 256, 2, 0, 0, False),
+    ("lstm", 8, 6, 2048, 1, 0, 0, True),     # one GPU, D = 2048: 960 weight columns in tensor memory + a resident stage
+    ("lstm", 4, 5, 2048, 1, 64, 3, False),   # the same with the weights streamed through a three-stage ring every step
+    ("gru", 4, 5, 2048, 2, 128, 4, True),    # streamed, two ranks
+]
+
+
+@pytest.mark.parametrize("case", EMULATED, ids=lambda c: f"{c[0]}-B{c[1]}-T{c[2]}-D{c[3]}-P{c[4]}-kt{c[5]}-rs{c[6]}-{'bf16' if c[7] else 'f32'}")
+def test_all_ranks_in_one_launch_match_the_oracle(case, cuda_device):
+    from flashrnn_b200 import poll_errors
+    from flashrnn_b200.wide_head import WideHead
+
+    cell, B, T, D, P, kt, rs, bf = case
+    wx, R, b, init, d_history, d_carry = _inputs(cell, B, T, D, 700 + D + P)
+    wx_seen = wx.bfloat16().float() if bf else wx
+    ref_h, ref_c, ref_g = port.forward_backward(wx_seen, R, b, init, cell, d_history, d_carry)
+    head = WideHead(cell, B, T, D, emulate_ranks=P, device=cuda_device, wx_dtype=torch.bfloat16 if bf else torch.float32,
+                    k_tmem_max=kt, ring_stages_max=rs, wait_limit_ms=3000)
+    try:
+        if kt:
+            assert head.plan.fwd_ring_chunks > 0 and head.plan.bwd_ring_chunks > 0
+        if rs:
+            assert not head.plan.fwd_resident and not head.plan.bwd_resident
+        for _ in range(2):   # the second call reuses the exchange buffers (refilled by the call) with the next epochs
+            leaves = [t.to(cuda_device).requires_grad_(True) for t in (wx.bfloat16() if bf else wx, R, b, init)]
+            h, c = head(*leaves)
+            ((h * d_history.to(cuda_device)).sum() + (c * d_carry.to(cuda_device)).sum()).backward()
+            torch.cuda.synchronize()
+            poll_errors(block=True)
+            _check(str(case), [h, c] + [t.grad for t in leaves], [ref_h, ref_c] + list(ref_g))
+    finally:
+        head.close()
+
+
+def _free_port():
+    with socket.socket() as s:
+        s.bind(("127.0.0.1", 0))
+        return s.getsockname()[1]
+
+
+def _worker(rank, world, port_no, cell, B, T, D, bf, out):
+    import torch.distributed as dist
+
+    from flashrnn_b200 import poll_errors
+    from flashrnn_b200.wide_head import WideHead
+
+    os.environ.update(MASTER_ADDR="127.0.0.1", MASTER_PORT=str(port_no), NCCL_NVLS_ENABLE="0")
+    torch.cuda.set_device(rank)
+    dev = torch.device("cuda", rank)
+    dist.init_process_group("nccl", rank=rank, world_size=world, device_id=dev)
+    ok, msg = False, ""
+    head = None
+    try:
+        wx, R, b, init, d_history, d_carry = _inputs(cell, B, T, D, 900 + D)
+        wx_seen = wx.bfloat16().float() if bf else wx
+        ref_h, ref_c, (r_dwx, r_dR, r_db, r_dinit) = port.forward_backward(wx_seen, R, b, init, cell, d_history, d_carry)
+        Dl = D // world
+        sl = slice(rank * Dl, (rank + 1) * Dl)
+        head = WideHead(cell, B, T, D, wx_dtype=torch.bfloat16 if bf else torch.float32, wait_limit_ms=20000)
+        for _ in range(2):
+            leaves = [t.contiguous().to(dev).requires_grad_(True)
+                      for t in ((wx.bfloat16() if bf else wx)[..., sl], R[:, :, sl, :], b[..., sl], init[..., sl])]
+            h, c = head(*leaves)
+            ((h * d_history[..., sl].to(dev)).sum() + (c * d_carry[..., sl].to(dev)).sum()).backward()
+            torch.cuda.synchronize()
+            poll_errors(block=True)
+            _check(f"rank {rank}", [h, c] + [t.grad for t in leaves],
+                   [ref_h[..., sl], ref_c[..., sl], r_dwx[..., sl], r_dR[:, :, sl, :], r_db[..., sl], r_dinit[..., sl]])
+        ok = True
+    except Exception as exc:  # reported to the parent; the other rank runs into its wait limit and reports too
+        msg = repr(exc)
+    finally:
+        out.put((rank, ok, msg))
+        try:
+            dist.barrier()
+            if head is not None:
+                head.close()
+        finally:
+            dist.destroy_process_group()
+
+
+@pytest.mark.parametrize("cell,B,T,D,bf", [("lstm", 6, 10, 512, True), ("slstm", 4, 8, 256, False)])
+def test_two_gpus_one_process_each(cell, B, T, D, bf):
+    if not torch.cuda.is_available() or torch.cuda.device_count() < 2:
+        pytest.skip("needs two GPUs")
+    import torch.multiprocessing as mp
+
+    ctx = mp.get_context("spawn")
+    out = ctx.Queue()
+    port_no = _free_port()
+    procs = [ctx.Process(target=_worker, args=(r, 2, port_no, cell, B, T, D, bf, out)) for r in range(2)]
+    for p in procs:
+        p.start()
+    results = [out.get(timeout=300) for _ in procs]
+    for p in procs:
+        p.join(timeout=120)
+        assert p.exitcode == 0
+    assert all(ok for _, ok, _ in results), results
