@@ -1,8 +1,9 @@
 """Per-kernel timing of the recurrence on arbitrary shapes (CUDA events, through the C ABI).
 
-    python -m flashrnn_b200.timing                 # the benchmark configurations that fit one GPU
-    python -m flashrnn_b200.timing lstm 16 1024 3 256
-    torchrun ... -m flashrnn_b200.timing config5b   # N32 D128 B256 T2048, heads sharded over the ranks
+    python bench_shapes.py                 # the benchmark configurations that fit one GPU
+    python bench_shapes.py lstm 16 1024 3 256
+    torchrun ... bench_shapes.py config5b   # N32 D128 B256 T2048, heads sharded over the ranks
+    [torchrun ...] bench_shapes.py wide [T [D [B]]]   # one head of D (4096) units row-sharded over the ranks
 
 The head-dimension sweep mirrors the reference's published one
 (flashrnn/speed_experiments/kernel_speed_benchmark.py:104-127: N*D = 768, B = 16, T = 1024).
@@ -13,11 +14,14 @@ in-kernel phase timers of CTA 0.
 from __future__ import annotations
 
 import sys
+from pathlib import Path
 
 import torch
 
-from . import _lib
-from .workloads import HEAD_DIM_SWEEP, SIZES, make_inputs
+sys.path.insert(0, str(Path(__file__).resolve().parent))
+
+from flashrnn_b200 import _lib  # noqa: E402
+from flashrnn_b200.workloads import HEAD_DIM_SWEEP, SIZES, make_inputs  # noqa: E402
 
 
 def time_shape(cell: str, B: int, T: int, N: int, D: int, reps: int = 5, device: str = "cuda:0") -> dict:
@@ -112,14 +116,14 @@ def time_config5b_sharded(B: int = 256, T: int = 2048, steps: int = 5, warmup: i
 
     Run under torchrun, one process per GPU (4 or 8 ranks: one GPU's share must fit its memory):
         python -m torch.distributed.run --nnodes=1 --nproc-per-node 8 --master-addr 127.0.0.1 \
-            -m flashrnn_b200.timing config5b
+            bench_shapes.py config5b
     Heads are independent, so the time loop has no collective and the weight gradients stay sharded;
     the reported time is the maximum over the ranks, the rate is B*T of the whole job over that time."""
     import os
 
     import torch.distributed as dist
 
-    from .sharding import flashrnn_sharded, shard_range
+    from flashrnn_b200.sharding import flashrnn_sharded, shard_range
 
     rank, world = int(os.environ.get("RANK", "0")), int(os.environ.get("WORLD_SIZE", "1"))
     local = int(os.environ.get("LOCAL_RANK", "0"))
@@ -164,7 +168,84 @@ def time_config5b_sharded(B: int = 256, T: int = 2048, steps: int = 5, warmup: i
         dist.destroy_process_group()
 
 
+def time_wide_head(T: int = 512, D: int = 4096, B: int = 32, cell: str = "lstm", steps: int = 3, warmup: int = 1,
+                   quiet: bool = False):
+    """fwd+bwd of ONE head of D units (LSTM, bf16 Wx) row-sharded over the ranks (1 rank: the same kernels on one GPU).
+
+    Under torchrun one process per GPU; the ranks exchange round(h_t) / round(dG_t) by peer stores inside the
+    kernels, no collective. CUDA events around the forward call and around backward (loss = sum(h)), maximum over
+    the ranks. Returns a dict (rank 0) with ms and the launch plan."""
+    import os
+
+    import torch.distributed as dist
+
+    from flashrnn_b200 import poll_errors
+    from flashrnn_b200.wide_head import WideHead
+
+    rank, world = int(os.environ.get("RANK", "0")), int(os.environ.get("WORLD_SIZE", "1"))
+    local = int(os.environ.get("LOCAL_RANK", "0"))
+    torch.cuda.set_device(local)
+    dev = torch.device("cuda", local)
+    own_pg = False
+    if world > 1 and not dist.is_initialized():
+        dist.init_process_group("nccl", device_id=dev)
+        own_pg = True
+    head = WideHead(cell, B, T, D, wx_dtype=torch.bfloat16) if world > 1 else \
+        WideHead(cell, B, T, D, emulate_ranks=1, device=dev, wx_dtype=torch.bfloat16)
+    gr, gw, gb, S = SIZES[cell]
+    Dl = D // world
+    gen = torch.Generator(device=dev).manual_seed(4 + rank)
+    wx = torch.randn((B, T, gw, 1, Dl), generator=gen, device=dev, dtype=torch.bfloat16)
+    R = torch.randn((gr, 1, Dl, D), generator=gen, device=dev) * D ** -0.5
+    b = torch.randn((gb, 1, Dl), generator=gen, device=dev) * 0.1
+    init = torch.randn((S, B, 1, 1, Dl), generator=gen, device=dev) * 0.5
+    tf, tb = [], []
+    for i in range(warmup + steps):
+        leaves = [t.detach().requires_grad_(True) for t in (wx, R, b, init)]
+        torch.cuda.synchronize()
+        if world > 1:
+            dist.barrier()
+        e0, e1, e2 = (torch.cuda.Event(enable_timing=True) for _ in range(3))
+        e0.record()
+        hist, _ = head(*leaves)
+        e1.record()
+        hist[0].sum().backward()
+        e2.record()
+        e2.synchronize()
+        poll_errors(block=True)
+        if i >= warmup:
+            tf.append(e0.elapsed_time(e1))
+            tb.append(e1.elapsed_time(e2))
+        del hist, leaves
+    ms = torch.tensor([sum(tf) / len(tf), sum(tb) / len(tb)], dtype=torch.float64, device=dev)
+    if world > 1:
+        dist.all_reduce(ms, op=dist.ReduceOp.MAX)
+    plan = head.plan
+    out = None
+    if rank == 0:
+        f, bw = (float(v) for v in ms.tolist())
+        out = {"workload": f"{cell} bf16 N1 D{D} B{B} T{T}, rows of R over {world} GPU(s)", "fwd_ms": f, "bwd_ms": bw,
+               "fwd_us_per_step": f * 1e3 / T, "bwd_us_per_step": bw * 1e3 / T, "value": B * T / (f + bw) * 1e3,
+               "unit": "(B*T)/s",
+               "fwd_plan": f"{plan.fwd_ctas} CTAs, K split {plan.fwd_ksplit}, {plan.fwd_k_tmem} weight columns in tensor memory + "
+                           f"{plan.fwd_ring_chunks} x 64 in {'resident' if plan.fwd_resident else 'streamed'} shared-memory stages ({plan.fwd_ring_stages})",
+               "bwd_plan": f"{plan.bwd_ctas} CTAs, K split {plan.bwd_ksplit}, {plan.bwd_k_tmem} + {plan.bwd_ring_chunks} x 64 "
+                           f"{'resident' if plan.bwd_resident else 'streamed'} ({plan.bwd_ring_stages})"}
+        if not quiet:
+            print(f"| {world} | {T} | {f:.2f} | {bw:.2f} | {f * 1e3 / T:.2f} / {bw * 1e3 / T:.2f} | {out['value'] / 1e3:.1f} k | "
+                  f"{out['fwd_plan']} | {out['bwd_plan']} |", flush=True)
+    if world > 1:
+        dist.barrier()
+    head.close()
+    if own_pg:
+        dist.destroy_process_group()
+    return out
+
+
 def main(argv) -> None:
+    if argv and argv[0] == "wide":  # optionally followed by T, D, B
+        time_wide_head(*map(int, argv[1:4]))
+        return
     if argv and argv[0] == "config5b":  # optionally followed by B and T (defaults: the configuration's 256 and 2048)
         return time_config5b_sharded(*map(int, argv[1:3]))
     if len(argv) == 5:
@@ -179,7 +260,7 @@ def main(argv) -> None:
         shapes += [(cell, 16, 1024, n, d) for d, n in HEAD_DIM_SWEEP]
     shapes += [("lstm", 16, 1024, 1, 1024), ("gru", 16, 1024, 1, 1024), ("lstm", 8, 512, 1, 1536)]  # wider than the sweep
     shapes += [("lstm", 256, 2048, 4, 128)]  # one GPU's share of N32 D128 B256 T2048 with the 32 heads split over 8 GPUs
-    from .cudnn_baseline import time_cudnn
+    from flashrnn_b200.cudnn_baseline import time_cudnn
 
     print(HEADER_LIB)
     for s in shapes:

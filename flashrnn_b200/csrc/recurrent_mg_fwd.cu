@@ -527,20 +527,15 @@ int launch_fwd_mg(const MgFwdParams& p, const void* wx, cudaStream_t stream, int
   attr[1].val.clusterDim.y = 1;
   attr[1].val.clusterDim.z = 1;
   cfg.attrs = attr;
-  cfg.numAttrs = KS > 1 ? 2 : 1;
+  // The cluster attribute is given for a cluster of one as well: the kernel scatters with st.async into
+  // shared::cluster addresses, which a launch without cluster dimensions rejects as an illegal instruction.
+  cfg.numAttrs = 2;
   int capacity = 0;
-  if (KS > 1) {
+  {
     int max_clusters = 0;
     e = cudaOccupancyMaxActiveClusters(&max_clusters, kern, &cfg);
     if (e != cudaSuccess) return static_cast<int>(e);
     capacity = max_clusters * KS;
-  } else {
-    int per_sm = 0, dev = 0, sms = 0;
-    e = cudaOccupancyMaxActiveBlocksPerMultiprocessor(&per_sm, kern, kMgThreads, static_cast<size_t>(smem));
-    if (e != cudaSuccess) return static_cast<int>(e);
-    if (cudaGetDevice(&dev) != cudaSuccess || cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev) != cudaSuccess)
-      return -2;
-    capacity = per_sm * sms;
   }
   if (capacity_only != nullptr) {
     *capacity_only = capacity;
