@@ -84,6 +84,7 @@ SIGNATURES = {
     "frnn_b200_wgrad_noalloc": (c_int, [c_int, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_int, c_int,
                                         c_int, c_void_p, c_void_p]),
     "frnn_b200_mg_plan": (c_int, [c_int, c_int, c_int, c_int, c_int, POINTER(MgShard), POINTER(MgPlan)]),
+    "frnn_b200_mg_capacity": (c_int, [c_int, c_int, c_int, c_int, c_int, c_int]),
     "frnn_b200_mg_forward": (c_int, [c_int, c_void_p, c_int, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p,
                                      POINTER(MgShard), c_int, c_int, c_int, c_int, c_int, c_void_p, c_void_p]),
     "frnn_b200_mg_gather_columns": (c_int, [c_int, POINTER(c_void_p), c_void_p, POINTER(MgShard), c_int, c_void_p]),

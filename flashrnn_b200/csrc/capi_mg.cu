@@ -146,6 +146,15 @@ extern "C" int frnn_b200_mg_plan(int cell, int B, int T, int D, int wx_bf16, con
   return 0;
 }
 
+extern "C" int frnn_b200_mg_capacity(int cell, int forward, int ksplit, int D, int P, int wx_bf16) {
+  Counts c;
+  if (!counts(cell, &c) || P < 1 || D % P != 0) return -5;
+  const int Kc = (forward ? D : c.gr * D) / ksplit;
+  const Residency r = residency(Kc, forward ? forward_mg_fixed_smem(cell, ksplit, D, wx_bf16) : backward_mg_fixed_smem(cell, ksplit, D, wx_bf16), 0, 0);
+  if (!r.ok) return 0;
+  return forward ? capacity_fwd(cell, ksplit, D, D / P, wx_bf16, r) : capacity_bwd(cell, ksplit, D, D / P, wx_bf16, r);
+}
+
 extern "C" int frnn_b200_mg_forward(int cell, const void* wx, int wx_bf16, const void* r_rows, const float* bias,
                                     const float* initial, float* history, float* carry, float* cache,
                                     const frnn_b200_mg_shard_t* sh, int B, int T, int D, int slstm_zero_first,

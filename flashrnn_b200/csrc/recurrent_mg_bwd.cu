@@ -184,7 +184,8 @@ frnn_bwd_mg_kernel(const MgBwdParams p, const __grid_constant__ CUtensorMap cach
       const uint32_t idesc_ts = umma_idesc_bf16(128, BT, false, false);
       const uint32_t idesc_ss = umma_idesc_bf16(128, BT, true, false);  // ring stages hold R^T MN-major
       int committed = 0;
-      long long ring_pos = 0;
+      int ring_stage = 0;        // next stage of the weight ring to consume, and the phase its barrier is in
+      uint32_t ring_phase = 0;
       bool ok = true;
       for (int it = 0; it < T && ok; ++it) {
         for (int sc = 0; sc < NSC && ok; ++sc) {
@@ -197,31 +198,40 @@ frnn_bwd_mg_kernel(const MgBwdParams p, const __grid_constant__ CUtensorMap cach
           }
           fence_proxy_async_smem();
           tc_fence_after_sync();
-          const uint32_t db = smem_u32(dgbuf + buf * dg_bytes);
-          for (int kk = 0; kk < SCK / 16; ++kk) {
-            const int k = sc * SCK + kk * 16;
-            const uint64_t bdesc = umma_smem_desc(db + kk * 2 * (BT * 16), BT * 16, 128);
-            if (k < k_tmem) {
-              umma_bf16_ts(tbase, tbase + BT + k / 2, bdesc, idesc_ts, k > 0 ? 1u : 0u);
-            } else {
-              const int kr = k - k_tmem, jr = kr / kMgRingK, kin = kr % kMgRingK;
-              const int stage = resident ? jr : static_cast<int>(ring_pos % NA);
-              if (kin == 0 && (!resident || it == 0)) {
-                const uint32_t ph = resident ? 0u : static_cast<uint32_t>((ring_pos / NA) & 1);
-                if (!mbar_wait_bounded<false, true>(smem_u32(&s_afull[stage]), ph, limit, abort_flag)) {
-                  mg_report(p.err, kErrWaitRing, it);
-                  ok = false;
-                  break;
-                }
-                tc_fence_after_sync();
+          // Descriptors advance by constants: 16 k = two 512-byte k-groups of the operand (64 in units of 16 B),
+          // eight 32-bit columns of tensor memory, 16 k rows of 128 B (2048 B) inside each box of a stage.
+          uint64_t bdesc = umma_smem_desc(smem_u32(dgbuf + buf * dg_bytes), BT * 16, 128);
+          const int k0 = sc * SCK;
+          int n_ts = (k_tmem - k0) / 16;
+          n_ts = n_ts < 0 ? 0 : (n_ts > SCK / 16 ? SCK / 16 : n_ts);
+          uint32_t acol = tbase + BT + k0 / 2;
+          int kk = 0;
+#pragma unroll 4
+          for (; kk < n_ts; ++kk) {
+            umma_bf16_ts(tbase, acol, bdesc, idesc_ts, (k0 | kk) != 0 ? 1u : 0u);
+            acol += 8;
+            bdesc += 64;
+          }
+          for (; kk < SCK / 16; kk += kMgRingK / 16) {
+            if (!resident || it == 0) {
+              if (!mbar_wait_bounded<false, true>(smem_u32(&s_afull[ring_stage]), ring_phase, limit, abort_flag)) {
+                mg_report(p.err, kErrWaitRing, it);
+                ok = false;
+                break;
               }
-              // [64 k][128 p] as two 64-wide boxes: 16 k rows = 2048 B further into each box
-              const uint64_t adesc = umma_smem_desc_mn_sw128(smem_u32(ring + stage * kMgRingBytes) + (kin / 16) * 2048u, 8192u);
-              umma_bf16_ss(tbase, adesc, bdesc, idesc_ss, k > 0 ? 1u : 0u);
-              if (kin == kMgRingK - 16) {
-                if (!resident) umma_commit(smem_u32(&s_aempty[stage]));
-                ++ring_pos;
-              }
+              tc_fence_after_sync();
+            }
+            uint64_t adesc = umma_smem_desc_mn_sw128(smem_u32(ring + ring_stage * kMgRingBytes), 8192u);
+#pragma unroll
+            for (int i = 0; i < kMgRingK / 16; ++i) {
+              umma_bf16_ss(tbase, adesc, bdesc, idesc_ss, (k0 | kk | i) != 0 ? 1u : 0u);
+              adesc += 128;
+              bdesc += 64;
+            }
+            if (!resident) umma_commit(smem_u32(&s_aempty[ring_stage]));
+            if (++ring_stage == NA) {
+              ring_stage = 0;
+              ring_phase ^= 1u;
             }
           }
           if (!ok) break;
@@ -276,19 +286,24 @@ frnn_bwd_mg_kernel(const MgBwdParams p, const __grid_constant__ CUtensorMap cach
       if (resident) {
         for (int j = 0; j < n_ring; ++j) load_stage(j, j);
       } else {
-        long long pos = 0;
-        bool ok = true;
+        int stage = 0;
+        uint32_t phase = 1;  // parity of the release this stage's next refill waits for (none before the first lap)
+        bool first_lap = true, ok = true;
         for (int it = 0; it < T && ok; ++it) {
-          for (int j = 0; j < n_ring; ++j, ++pos) {
-            const int stage = static_cast<int>(pos % NA);
-            if (pos >= NA && !mbar_wait_bounded<false>(smem_u32(&s_aempty[stage]), static_cast<uint32_t>(((pos / NA) - 1) & 1),
-                                                       limit, abort_flag)) {
+          for (int j = 0; j < n_ring; ++j) {
+            if (!first_lap && !mbar_wait_bounded<false, true>(smem_u32(&s_aempty[stage]), phase, limit, abort_flag)) {
               mg_report(p.err, kErrWaitRing, it);
               ok = false;
               break;
             }
-            if (*abort_flag != 0) { ok = false; break; }
+            // (a bounded wait that returned true saw no abort; the flag itself is read only once per step)
+            if (j == 0 && *abort_flag != 0) { ok = false; break; }
             load_stage(stage, j);
+            if (++stage == NA) {
+              stage = 0;
+              phase ^= 1u;
+              first_lap = false;
+            }
           }
         }
       }
@@ -307,7 +322,7 @@ frnn_bwd_mg_kernel(const MgBwdParams p, const __grid_constant__ CUtensorMap cach
         const long long q = static_cast<long long>(it) * NSC + sc;
         const int buf = static_cast<int>(q & 1);
         if (q >= 2 && !dead &&
-            !mbar_wait_bounded<false>(smem_u32(&s_dgfree[buf]), static_cast<uint32_t>(((q >> 1) - 1) & 1), limit, abort_flag)) {
+            !mbar_wait_bounded<false, true>(smem_u32(&s_dgfree[buf]), static_cast<uint32_t>(((q >> 1) - 1) & 1), limit, abort_flag)) {
           mg_report(p.err, kErrWaitMma, it);
           dead = true;
         }
@@ -355,7 +370,7 @@ frnn_bwd_mg_kernel(const MgBwdParams p, const __grid_constant__ CUtensorMap cach
       const int t = T - 1 - it;
       const int pb = it & 1;
       if (it >= 1 && !dead &&
-          !mbar_wait_bounded<true, false>(smem_u32(&s_part_bar[pb]), ((it - 1) >> 1) & 1, limit, abort_flag)) {
+          !mbar_wait_bounded<true, true>(smem_u32(&s_part_bar[pb]), ((it - 1) >> 1) & 1, limit, abort_flag)) {
         mg_report(p.err, kErrWaitPart, it);
         dead = true;
       }
@@ -457,7 +472,7 @@ frnn_bwd_mg_kernel(const MgBwdParams p, const __grid_constant__ CUtensorMap cach
         }
       }
       fetch(it, t);
-      if (!dead && !mbar_wait_bounded<false>(smem_u32(&s_mma_bar), it & 1, limit, abort_flag)) {
+      if (!dead && !mbar_wait_bounded<false, true>(smem_u32(&s_mma_bar), it & 1, limit, abort_flag)) {
         mg_report(p.err, kErrWaitMma, it);
         dead = true;
       }

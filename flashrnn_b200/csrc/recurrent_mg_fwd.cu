@@ -175,43 +175,60 @@ frnn_fwd_mg_kernel(const MgFwdParams p, const __grid_constant__ CUtensorMap wx_m
     if (lane == 0 && ready_ok) {
       const uint32_t idesc = umma_idesc_bf16(128, BT, false, false);
       int committed = 0;
-      long long ring_pos = 0;  // stages consumed so far (streaming ring)
+      int ring_stage = 0;        // next stage of the weight ring to consume, and the phase its barrier is in
+      uint32_t ring_phase = 0;
       bool ok = true;
+      const bool prof = p.err[3] != 0 && blockIdx.x == 0;  // phase timers of CTA 0 (SM clock cycles, summed over all steps)
+      long long pf_h = 0, pf_a = 0, pf_tot = prof ? clock64() : 0;
       for (int t = 0; t < T && ok; ++t) {
         for (int sc = 0; sc < NSC && ok; ++sc) {
           const long long q = static_cast<long long>(t) * NSC + sc;
           const int buf = static_cast<int>(q & 1);
+          const long long w0 = prof ? clock64() : 0;
           if (!mbar_wait_bounded<false, true>(smem_u32(&s_hbar[buf]), static_cast<uint32_t>((q >> 1) & 1), limit, abort_flag)) {
             mg_report(p.err, kErrWaitH, t);
             ok = false;
             break;
           }
+          if (prof) pf_h += clock64() - w0;
           fence_proxy_async_smem();
           tc_fence_after_sync();
-          const uint32_t hb = smem_u32(hbuf + buf * hb_bytes);
-          for (int kk = 0; kk < SCK / 16; ++kk) {
-            const int k = sc * SCK + kk * 16;  // position inside the K-chunk
-            const uint64_t bdesc = umma_smem_desc(hb + kk * 2 * (BT * 16), BT * 16, 128);
-            if (k < k_tmem) {
-              umma_bf16_ts(tbase, tbase + BT + k / 2, bdesc, idesc, k > 0 ? 1u : 0u);
-            } else {
-              const int kr = k - k_tmem, jr = kr / kMgRingK, kin = kr % kMgRingK;
-              const int stage = resident ? jr : static_cast<int>(ring_pos % NA);
-              if (kin == 0 && (!resident || t == 0)) {
-                const uint32_t ph = resident ? 0u : static_cast<uint32_t>((ring_pos / NA) & 1);
-                if (!mbar_wait_bounded<false, true>(smem_u32(&s_afull[stage]), ph, limit, abort_flag)) {
-                  mg_report(p.err, kErrWaitRing, t);
-                  ok = false;
-                  break;
-                }
-                tc_fence_after_sync();
+          // Descriptors advance by constants: 16 k = two 512-byte k-groups of the operand (64 in units of 16 B),
+          // eight 32-bit columns of tensor memory, 32 B inside a 128-byte swizzled row.
+          uint64_t bdesc = umma_smem_desc(smem_u32(hbuf + buf * hb_bytes), BT * 16, 128);
+          const int k0 = sc * SCK;
+          int n_ts = (k_tmem - k0) / 16;
+          n_ts = n_ts < 0 ? 0 : (n_ts > SCK / 16 ? SCK / 16 : n_ts);
+          uint32_t acol = tbase + BT + k0 / 2;
+          int kk = 0;
+#pragma unroll 4
+          for (; kk < n_ts; ++kk) {
+            umma_bf16_ts(tbase, acol, bdesc, idesc, (k0 | kk) != 0 ? 1u : 0u);
+            acol += 8;
+            bdesc += 64;
+          }
+          for (; kk < SCK / 16; kk += kMgRingK / 16) {
+            if (!resident || t == 0) {
+              const long long w1 = prof ? clock64() : 0;
+              if (!mbar_wait_bounded<false, true>(smem_u32(&s_afull[ring_stage]), ring_phase, limit, abort_flag)) {
+                mg_report(p.err, kErrWaitRing, t);
+                ok = false;
+                break;
               }
-              const uint64_t adesc = umma_smem_desc_k_sw128(smem_u32(ring + stage * kMgRingBytes) + kin * 2);
-              umma_bf16_ss(tbase, adesc, bdesc, idesc, k > 0 ? 1u : 0u);
-              if (kin == kMgRingK - 16) {
-                if (!resident) umma_commit(smem_u32(&s_aempty[stage]));
-                ++ring_pos;
-              }
+              if (prof) pf_a += clock64() - w1;
+              tc_fence_after_sync();
+            }
+            uint64_t adesc = umma_smem_desc_k_sw128(smem_u32(ring + ring_stage * kMgRingBytes));
+#pragma unroll
+            for (int i = 0; i < kMgRingK / 16; ++i) {
+              umma_bf16_ss(tbase, adesc, bdesc, idesc, (k0 | kk | i) != 0 ? 1u : 0u);
+              adesc += 2;
+              bdesc += 64;
+            }
+            if (!resident) umma_commit(smem_u32(&s_aempty[ring_stage]));
+            if (++ring_stage == NA) {
+              ring_stage = 0;
+              ring_phase ^= 1u;
             }
           }
           if (!ok) break;
@@ -228,6 +245,11 @@ frnn_fwd_mg_kernel(const MgFwdParams p, const __grid_constant__ CUtensorMap wx_m
         ++committed;
       }
       if (committed > 0) mbar_wait_bounded<false, true>(smem_u32(&s_mma_bar), (committed - 1) & 1, limit, nullptr);
+      if (prof) {  // err[16]: operand wait, err[17]: weight-stage wait, err[18]: whole loop (all in units of 1024 cycles)
+        p.err[16] = static_cast<int>(pf_h >> 10);
+        p.err[17] = static_cast<int>(pf_a >> 10);
+        p.err[18] = static_cast<int>((clock64() - pf_tot) >> 10);
+      }
     }
   } else if (warp == 5) {
     if (lane == 0 && ready_ok) {
@@ -254,22 +276,32 @@ frnn_fwd_mg_kernel(const MgFwdParams p, const __grid_constant__ CUtensorMap wx_m
           tma_load_3d(smem_u32(ring + j * kMgRingBytes), &r_map, smem_u32(&s_afull[j]), k_base + j * kMgRingK, xu, 0);
         }
       } else {
-        long long pos = 0;
-        bool ok = true;
+        int stage = 0;
+        uint32_t phase = 1;  // parity of the release this stage's next refill waits for (none before the first lap)
+        bool first_lap = true, ok = true;
+        const bool prof = p.err[3] != 0 && blockIdx.x == 0;
+        long long pf_e = 0;
         for (int t = 0; t < T && ok; ++t) {
-          for (int j = 0; j < n_ring; ++j, ++pos) {
-            const int stage = static_cast<int>(pos % NA);
-            if (pos >= NA && !mbar_wait_bounded<false>(smem_u32(&s_aempty[stage]), static_cast<uint32_t>(((pos / NA) - 1) & 1),
-                                                       limit, abort_flag)) {
+          for (int j = 0; j < n_ring; ++j) {
+            const long long w0 = prof ? clock64() : 0;
+            if (!first_lap && !mbar_wait_bounded<false, true>(smem_u32(&s_aempty[stage]), phase, limit, abort_flag)) {
               mg_report(p.err, kErrWaitRing, t);
               ok = false;
               break;
             }
-            if (*abort_flag != 0) { ok = false; break; }
+            if (prof) pf_e += clock64() - w0;
+            // (a bounded wait that returned true saw no abort; the flag itself is read only once per step)
+            if (j == 0 && *abort_flag != 0) { ok = false; break; }
             mbar_arrive_expect_tx(smem_u32(&s_afull[stage]), static_cast<uint32_t>(Cfg::ROWS) * kMgRingK * 2u);
             tma_load_3d(smem_u32(ring + stage * kMgRingBytes), &r_map, smem_u32(&s_afull[stage]), k_base + j * kMgRingK, xu, 0);
+            if (++stage == NA) {
+              stage = 0;
+              phase ^= 1u;
+              first_lap = false;
+            }
           }
         }
+        if (prof) p.err[19] = static_cast<int>(pf_e >> 10);  // producer: waiting for released stages
       }
     }
   } else if (ready_ok) {
@@ -303,15 +335,20 @@ frnn_fwd_mg_kernel(const MgFwdParams p, const __grid_constant__ CUtensorMap wx_m
       }
     };
     // this CTA's K-chunk of slot `slot` -> operand buffers, one sub-chunk at a time
+    const bool prof = p.err[3] != 0 && blockIdx.x == 0 && tid == 0;
+    long long pf_free = 0, pf_poll = 0, pf_mma = 0, pf_part = 0;
     auto fetch = [&](int slot) {
       for (int sc = 0; sc < NSC; ++sc) {
         const long long q = static_cast<long long>(slot) * NSC + sc;
         const int buf = static_cast<int>(q & 1);
+        const long long f0 = prof ? clock64() : 0;
         if (q >= 2 && !dead &&
-            !mbar_wait_bounded<false>(smem_u32(&s_hfree[buf]), static_cast<uint32_t>(((q >> 1) - 1) & 1), limit, abort_flag)) {
+            !mbar_wait_bounded<false, true>(smem_u32(&s_hfree[buf]), static_cast<uint32_t>(((q >> 1) - 1) & 1), limit, abort_flag)) {
           mg_report(p.err, kErrWaitMma, slot);
           dead = true;
         }
+        const long long f1 = prof ? clock64() : 0;
+        if (prof) pf_free += f1 - f0;
         const __nv_bfloat16* src = p.hbf[rank] + static_cast<size_t>(prow) * hrow + static_cast<size_t>(slot) * D +
                                    static_cast<size_t>(ks) * Kc + sc * SCK + warp * 8;
         uint8_t* dst = hbuf + buf * hb_bytes + warp * (BT * 16) + (prow >> 3) * 128 + (prow & 7) * 16;
@@ -348,6 +385,7 @@ frnn_fwd_mg_kernel(const MgFwdParams p, const __grid_constant__ CUtensorMap wx_m
         dead = __any_sync(0xffffffffu, dead);
         fence_proxy_async_smem();
         mbar_arrive(smem_u32(&s_hbar[buf]));
+        if (prof) pf_poll += clock64() - f1;
       }
     };
 
@@ -383,10 +421,12 @@ frnn_fwd_mg_kernel(const MgFwdParams p, const __grid_constant__ CUtensorMap wx_m
         }
       }
       mbar_arrive(smem_u32(&s_wx_empty[s]));
-      if (!dead && !mbar_wait_bounded<false>(smem_u32(&s_mma_bar), t & 1, limit, abort_flag)) {
+      const long long e0 = prof ? clock64() : 0;
+      if (!dead && !mbar_wait_bounded<false, true>(smem_u32(&s_mma_bar), t & 1, limit, abort_flag)) {
         mg_report(p.err, kErrWaitMma, t);
         dead = true;
       }
+      if (prof) pf_mma += clock64() - e0;
       tc_fence_after_sync();
       // partial gates of this row: batch columns [ks'*BO, (ks'+1)*BO) go to CTA ks' of the cluster
       {
@@ -416,10 +456,12 @@ frnn_fwd_mg_kernel(const MgFwdParams p, const __grid_constant__ CUtensorMap wx_m
           }
         }
       }
-      if (!dead && !mbar_wait_bounded<true, false>(smem_u32(&s_part_bar[pb]), (t >> 1) & 1, limit, abort_flag)) {
+      const long long e1 = prof ? clock64() : 0;
+      if (!dead && !mbar_wait_bounded<true, true>(smem_u32(&s_part_bar[pb]), (t >> 1) & 1, limit, abort_flag)) {
         mg_report(p.err, kErrWaitPart, t);
         dead = true;
       }
+      if (prof) pf_part += clock64() - e1;
       float ry[NI][CT::GR];
       {
         const float* pbuf = part + pb * Cfg::PART_FLOATS;
@@ -451,7 +493,7 @@ frnn_fwd_mg_kernel(const MgFwdParams p, const __grid_constant__ CUtensorMap wx_m
       }
       // slot T (h of the last step) has no reader: not the recurrence, and the dR contraction stops at slot T - 1
       publish(t + 1, hb16, !dead && t < mute_from && t + 1 < T);
-      if (t + 1 < T) fetch(t + 1);
+      // state stores first: they leave the SM while the packets of the other CTAs are still on their way
 #pragma unroll
       for (int j = 0; j < NI; ++j) {
         if (act[j]) {
@@ -464,6 +506,13 @@ frnn_fwd_mg_kernel(const MgFwdParams p, const __grid_constant__ CUtensorMap wx_m
           }
         }
       }
+      if (t + 1 < T) fetch(t + 1);
+    }
+    if (prof) {  // epilogue thread 0: err[8] buffer-free wait, [9] operand poll + copy, [10] tensor-core wait, [11] partner sums
+      p.err[8] = static_cast<int>(pf_free >> 10);
+      p.err[9] = static_cast<int>(pf_poll >> 10);
+      p.err[10] = static_cast<int>(pf_mma >> 10);
+      p.err[11] = static_cast<int>(pf_part >> 10);
     }
 #pragma unroll
     for (int j = 0; j < NI; ++j) {

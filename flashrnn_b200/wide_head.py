@@ -45,6 +45,8 @@ class WideHead:
         self.wait_limit_ms = wait_limit_ms
         self.group = group
         self._epoch = 0
+        self.profile = False   # True: CTA 0 of the forward adds up its in-kernel phase timers into last_err[8..19]
+        self.last_err = None
         self._owned = []      # cudaMalloc'ed slabs of this process
         self._opened = []     # peer mappings
         gr = SIZES[cell][0]
@@ -218,6 +220,9 @@ class _WideRecurrence(torch.autograd.Function):
             train = any(ctx.needs_input_grad[:4])
             cache = torch.empty(head.plan.cache_bytes // 4, dtype=torch.float32, device=dev) if train and head.plan.cache_bytes else None
             err = torch.zeros(32, dtype=torch.int32, device=dev)
+            if head.profile:
+                err[3] = 1
+                head.last_err = err
             sh = head._shard("hbf", head.next_epoch())
             rc = lib.frnn_b200_mg_forward(
                 _lib.CELLS[head.cell], wx_c.data_ptr(), head.wx_bf16, head.r_stage.data_ptr(), b32.data_ptr(), init32.data_ptr(),

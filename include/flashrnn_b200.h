@@ -192,6 +192,11 @@ typedef struct frnn_b200_mg_plan {
 int frnn_b200_mg_plan(int cell, int B, int T, int D, int wx_bf16, const frnn_b200_mg_shard_t* shard,
                       frnn_b200_mg_plan_t* out);
 
+/* How many CTAs of the forward (forward != 0) or backward launch with `ksplit` CTAs per tile the current device
+ * holds at once (thread-block clusters are placed inside one GPC, so this can be less than the SM count); the
+ * counterpart of the reference's frnn_hybrid_fw2d_ctas() query (flashrnn/flashrnn2/hybrid_fw2d.cu:404-419). */
+int frnn_b200_mg_capacity(int cell, int forward, int ksplit, int D, int P, int wx_bf16);
+
 /* Forward (multi_gpu.py:87-297). sh->buffers = the ranks' h histories. Outputs: history [S,B,T,Dl], carry [S,B,1,Dl],
  * cache (NULL for inference). The h history of this rank holds round_bf16(h) of ALL units afterwards (slots 0..T-1). */
 int frnn_b200_mg_forward(int cell, const void* wx, int wx_bf16, const void* r_rows, const float* bias,
