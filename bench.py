@@ -467,9 +467,17 @@ def head_sharded_config(dev, dist, rank, world, steps=3, warmup=2):
 
 
 def wide_head_sharded(dev, dist, rank, world):
-    """Extra keys: the row-sharded wide head (one head of D = 4096 split over the ranks with the per-step exchange
-    done by peer stores inside the kernels). Filled in by the multi-GPU kernels when they are present."""
-    return None
+    """Extra keys: the row-sharded wide head (LSTM, ONE head of D = 4096, B = 32, bf16 Wx) with the rows of R split
+    over the ranks and round(h_t) / round(dG_t) exchanged every step by peer stores inside the kernels (no
+    collective). T is reduced to 256 steps to keep the run short (the configuration's T is 4096; time is linear
+    in T). At one rank the same kernels run with R streamed from HBM / L2 every step (128 MiB does not fit one
+    GPU's tensor + shared memory); from 4 ranks on R stays on the SMs, hence the super-linear step."""
+    import bench_shapes
+
+    try:
+        return bench_shapes.time_wide_head(T=256, steps=2, warmup=1, quiet=True)
+    except (ValueError, RuntimeError) as exc:   # reported, never fatal for the headline line
+        return {"error": repr(exc)[:300]} if rank == 0 else None
 
 
 def kernel_breakdown(_lib, dev, d_wx, d_R, d_b, d_init, flush, reps):
