@@ -46,6 +46,13 @@ class Plan(ctypes.Structure):
     ]
 
 
+class Options(ctypes.Structure):
+    """Mirror of ``frnn_b200_options_t``."""
+
+    _fields_ = [("forward_clipval", ctypes.c_float), ("gradient_recurrent_clipval", ctypes.c_float),
+                ("gradient_recurrent_cut", c_int), ("slstm_v1_gradient", c_int)]
+
+
 class MgShard(ctypes.Structure):
     """Mirror of ``frnn_b200_mg_shard_t``."""
 
@@ -76,6 +83,15 @@ SIGNATURES = {
     "frnn_b200_forward_prepared": (c_int, [c_int, c_void_p, c_int, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p,
                                            c_void_p, c_int, c_int, c_int, c_int, c_int, c_void_p, c_int, c_void_p,
                                            c_void_p]),
+    "frnn_b200_forward_ex": (c_int, [c_int, c_void_p, c_int, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p,
+                                     c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_int, c_int, c_void_p,
+                                     c_void_p, POINTER(Options)]),
+    "frnn_b200_backward_ex": (c_int, [c_int, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p,
+                                      c_int, c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_int,
+                                      c_int, c_void_p, c_void_p, POINTER(Options)]),
+    "frnn_b200_forward_chunk": (c_int, [c_int, c_void_p, c_int, c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_void_p,
+                                        c_void_p, c_int, c_int, c_int, c_int, c_int, c_int, c_int, c_void_p, c_int,
+                                        c_void_p, c_void_p]),
     "frnn_b200_backward": (c_int, [c_int, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p,
                                    c_int, c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_int,
                                    c_int, c_void_p, c_void_p]),

@@ -244,7 +244,7 @@ namespace {
 int forward_common(int cell, const void* wx, int wx_bf16, const void* r_bf16, const float* bias, const float* initial,
                    float* history, float* carry, float* cache, void* hbf, void* xchg, int B, int T, int N, int D,
                    int slstm_zero_first, const int* zero_first_dev, int output_mode, int wait_limit_ms, int* err,
-                   void* stream) {
+                   void* stream, int T_total = 0, int t0 = 0, int out_bf16 = 0, const frnn_b200_options_t* opt = nullptr) {
   frnn_b200_plan_t plan;
   const int rc = frnn_b200_plan(cell, B, T, N, D, &plan);
   if (rc != 0) return rc;
@@ -265,6 +265,12 @@ int forward_common(int cell, const void* wx, int wx_bf16, const void* r_bf16, co
   p.slstm_zero_first = slstm_zero_first;
   p.zero_first_dev = zero_first_dev;
   p.output_mode = output_mode;
+  p.T_total = T_total > 0 ? T_total : T;
+  p.t0 = t0;
+  p.out_bf16 = out_bf16;
+  p.fwd_clip = opt != nullptr ? opt->forward_clipval : 0.0f;
+  if (t0 < 0 || t0 + T > p.T_total) return -5;
+  if ((cache != nullptr || hbf != nullptr) && (t0 != 0 || p.T_total != T || out_bf16)) return -5;
   p.wait_limit_ns = (wait_limit_ms > 0 ? static_cast<unsigned long long>(wait_limit_ms) : 2000ull) * 1000000ull;
   if (plan.exchange) {
     if (!xchg) return -5;
@@ -289,20 +295,46 @@ extern "C" int frnn_b200_forward(int cell, const void* wx, int wx_bf16, const vo
                         slstm_zero_first, nullptr, 0, wait_limit_ms, err, stream);
 }
 
+extern "C" int frnn_b200_forward_ex(int cell, const void* wx, int wx_bf16, const void* r_bf16, const float* bias,
+                                    const float* initial, float* history, float* carry, float* cache, void* hbf,
+                                    void* xchg, int B, int T, int N, int D, int slstm_zero_first, int wait_limit_ms,
+                                    int* err, void* stream, const frnn_b200_options_t* options) {
+  return forward_common(cell, wx, wx_bf16, r_bf16, bias, initial, history, carry, cache, hbf, xchg, B, T, N, D,
+                        slstm_zero_first, nullptr, 0, wait_limit_ms, err, stream, 0, 0, 0, options);
+}
+
 extern "C" int frnn_b200_forward_prepared(int cell, const void* wx, int wx_bf16, const void* r_bf16, const float* bias,
-                                          const float* initial, float* output, float* carry, void* xchg, int B, int T,
+                                          const float* initial, void* output, float* carry, void* xchg, int B, int T,
                                           int N, int D, int output_mode, const int* slstm_zero_first_dev,
                                           int wait_limit_ms, int* err, void* stream) {
-  if (output_mode < 0 || output_mode > 2) return -5;
+  return frnn_b200_forward_chunk(cell, wx, wx_bf16, r_bf16, bias, initial, output, 0, carry, xchg, B, T, 0, T, N, D,
+                                 output_mode, slstm_zero_first_dev, wait_limit_ms, err, stream);
+}
+
+extern "C" int frnn_b200_forward_chunk(int cell, const void* wx, int wx_bf16, const void* r_bf16, const float* bias,
+                                       const float* initial, void* output, int output_bf16, float* carry, void* xchg, int B,
+                                       int T_total, int t_start, int steps, int N, int D, int output_mode,
+                                       const int* slstm_zero_first_dev, int wait_limit_ms, int* err, void* stream) {
+  if (output_mode < 0 || output_mode > 2 || steps < 1) return -5;
   if (cell == kSLSTM && slstm_zero_first_dev == nullptr) return -5;
-  return forward_common(cell, wx, wx_bf16, r_bf16, bias, initial, output, carry, nullptr, nullptr, xchg, B, T, N, D, 0,
-                        cell == kSLSTM ? slstm_zero_first_dev : nullptr, output_mode, wait_limit_ms, err, stream);
+  return forward_common(cell, wx, wx_bf16, r_bf16, bias, initial, static_cast<float*>(output), carry, nullptr, nullptr, xchg, B,
+                        steps, N, D, 0, cell == kSLSTM ? slstm_zero_first_dev : nullptr, output_mode, wait_limit_ms, err,
+                        stream, T_total, t_start, output_bf16 != 0);
 }
 
 extern "C" int frnn_b200_backward(int cell, const float* cache, const float* history, const float* initial,
                                   const void* r_bf16, const float* d_history, const float* d_carry, void* dwx,
                                   int wx_bf16, void* dgr, float* d_initial, float* db_part, void* xchg, int B, int T,
                                   int N, int D, int slstm_zero_first, int wait_limit_ms, int* err, void* stream) {
+  return frnn_b200_backward_ex(cell, cache, history, initial, r_bf16, d_history, d_carry, dwx, wx_bf16, dgr, d_initial,
+                               db_part, xchg, B, T, N, D, slstm_zero_first, wait_limit_ms, err, stream, nullptr);
+}
+
+extern "C" int frnn_b200_backward_ex(int cell, const float* cache, const float* history, const float* initial,
+                                     const void* r_bf16, const float* d_history, const float* d_carry, void* dwx,
+                                     int wx_bf16, void* dgr, float* d_initial, float* db_part, void* xchg, int B, int T,
+                                     int N, int D, int slstm_zero_first, int wait_limit_ms, int* err, void* stream,
+                                     const frnn_b200_options_t* options) {
   frnn_b200_plan_t plan;
   const int rc = frnn_b200_plan(cell, B, T, N, D, &plan);
   if (rc != 0) return rc;
@@ -322,6 +354,11 @@ extern "C" int frnn_b200_backward(int cell, const float* cache, const float* his
   p.C = plan.cluster;
   p.box_b = plan.batch_tile;  // rows past B are filled with zeros by TMA
   p.slstm_zero_first = slstm_zero_first;
+  if (options != nullptr) {
+    p.grad_clip = options->gradient_recurrent_clipval;
+    p.cut_recurrent = options->gradient_recurrent_cut != 0;
+    p.slstm_v1 = options->slstm_v1_gradient != 0;
+  }
   p.wait_limit_ns = (wait_limit_ms > 0 ? static_cast<unsigned long long>(wait_limit_ms) : 2000ull) * 1000000ull;
   if (plan.exchange) {
     if (!xchg) return -5;

@@ -114,10 +114,13 @@ __device__ __forceinline__ void cell_forward(const float* ry, const float* wx, c
 // slstm: follows autograd exactly, i.e. the stabiliser m carries a gradient and max(., 1) /
 // max(i, logf) split a tie 0.5 / 0.5 as torch.maximum does.
 // ---------------------------------------------------------------------------------------------
+// slstm_v1 selects the gradient convention of the reference's own kernels instead (flashrnn/flashrnn2/
+// grad_reference.py:1-13, flashrnn/flashrnn/vanilla_fwbw/bw.py:147-190): m carries no gradient (neither m_t nor the
+// m_{t-1} inside log f, so d(initial m) = 0) and the clamp n = max(., 1) passes its gradient straight through.
 template <int CELL>
 __device__ __forceinline__ void cell_backward(const float* cache, const float* sp, const float* sn,
                                               float* ds, float* dgr, float* dgw, float* dgb,
-                                              bool slstm_take_i) {
+                                              bool slstm_take_i, bool slstm_v1 = false) {
   if constexpr (CELL == kLSTM) {
     const float si = cache[0], sf = cache[1], tz = cache[2], so = cache[3];
     const float tc = tanh_f(sn[1]);
@@ -148,14 +151,14 @@ __device__ __forceinline__ void cell_backward(const float* cache, const float* s
     const float dn = ds[2] - dh * so * c_n * inv_n * inv_n;
     const float d_o = dh * (c_n * inv_n) * so * (1.0f - so);
     const float pre_n = fg * n_p + ig;
-    const float mask = pre_n > 1.0f ? 1.0f : (pre_n == 1.0f ? 0.5f : 0.0f);
+    const float mask = slstm_v1 ? 1.0f : (pre_n > 1.0f ? 1.0f : (pre_n == 1.0f ? 0.5f : 0.0f));
     const float dpre = dn * mask;
     const float d_ig = dc * tz + dpre;
     const float d_fg = dc * c_p + dpre * n_p;
     const float d_z = dc * ig * (1.0f - tz * tz);
     float d_i = d_ig * ig;
     float d_logf = d_fg * fg;
-    const float dm = ds[3] - d_i - d_logf;
+    const float dm = slstm_v1 ? 0.0f : ds[3] - d_i - d_logf;
     if (slstm_take_i) {
       d_i += dm;
     } else if (i > logf) {
@@ -170,7 +173,7 @@ __device__ __forceinline__ void cell_backward(const float* cache, const float* s
     ds[0] = 0.0f;
     ds[1] = dc * fg;
     ds[2] = dpre * fg;
-    ds[3] = d_logf;
+    ds[3] = slstm_v1 ? 0.0f : d_logf;
     dgr[0] = d_i; dgr[1] = d_f; dgr[2] = d_z; dgr[3] = d_o;
     dgw[0] = d_i; dgw[1] = d_f; dgw[2] = d_z; dgw[3] = d_o;
     dgb[0] = d_i; dgb[1] = d_f; dgb[2] = d_z; dgb[3] = d_o;
@@ -192,5 +195,14 @@ __device__ __forceinline__ void cell_backward(const float* cache, const float* s
     dgr[0] = d; dgw[0] = d; dgb[0] = d;
   }
 }
+
+// Options of the reference's v1 configuration (flashrnn/flashrnn/flashrnn.py:128-133), applied as its fused kernels
+// apply them (flashrnn/flashrnn/fused/lstm_fused_pointwise.cuh:76-81,116-122): the new hidden state is clipped to
+// [-forward_clipval, forward_clipval] before it is stored and fed back (the backward pass treats the clip as the
+// identity); the gradient that reaches h_t from step t+1 (the R path plus the cell's direct h term) is clipped to
+// [-gradient_recurrent_clipval, ...] before the external gradient of h_t is added; with gradient_recurrent_cut the R
+// path contributes nothing at all (flashrnn/flashrnn/fused/flashrnn_fused_backward_cut.cu:90). Values <= 0 switch a
+// clip off.
+__device__ __forceinline__ float clip_sym(float x, float c) { return c > 0.0f ? fminf(fmaxf(x, -c), c) : x; }
 
 }  // namespace frnn

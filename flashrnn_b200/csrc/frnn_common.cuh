@@ -44,6 +44,12 @@ struct FwdParams {
   // [B][T][N][D], 2 only the last hidden state [B][1][N][D].
   const int* zero_first_dev;
   int output_mode;
+  // A call may cover the steps [t0, t0 + T) of a longer sequence of T_total steps whose Wx and output tensors
+  // are laid out for the whole sequence (chunked execution of a prepared sequence); T_total = T and t0 = 0
+  // otherwise. The gate cache and the bf16 copy of h are only written by whole-sequence calls.
+  int T_total, t0;
+  int out_bf16;            // 1: the state history is stored as bf16 snapshots (forward-only calls)
+  float fwd_clip;          // > 0: h_t is clipped to [-fwd_clip, fwd_clip] (see clip_sym in cells.cuh)
   unsigned long long wait_limit_ns;
   // Exchange through global memory (groups wider than a cluster), null for cluster exchange:
   // per group four slots of the bf16 operand (the data words double as arrival flags).
@@ -62,6 +68,9 @@ struct BwdParams {
   int C;
   int box_b;
   int slstm_zero_first;
+  float grad_clip;          // > 0: the gradient carried into h_t from step t+1 is clipped to [-grad_clip, grad_clip]
+  int cut_recurrent;        // 1: the R path of the hidden-state gradient is dropped
+  int slstm_v1;             // 1: sLSTM gradient convention of the reference's own kernels (see cell_backward)
   unsigned long long wait_limit_ns;
   // Exchange through global memory, null for cluster exchange: per group two slots of the
   // partial-dh blocks [dest CTA][source CTA][batch][unit] (1-D backward, phase bit in every word) or
@@ -101,6 +110,12 @@ __device__ __forceinline__ void st_f32_vec(float* p, const float* v) {
 #pragma unroll
     for (int i = 0; i < N; ++i) p[i] = v[i];
   }
+}
+template <int N>
+__device__ __forceinline__ void st_bf16_vec(__nv_bfloat16* p, const float* v) {
+  static_assert(N % 2 == 0, "pairs");
+#pragma unroll
+  for (int i = 0; i < N; i += 2) *reinterpret_cast<__nv_bfloat162*>(p + i) = __floats2bfloat162_rn(v[i], v[i + 1]);
 }
 template <int N>
 __device__ __forceinline__ void ld_bf16_vec(const __nv_bfloat16* p, float* v) {

@@ -101,6 +101,7 @@ frnn_bwd_kernel(const BwdParams p, const __grid_constant__ CUtensorMap cache_map
   // test hook: with err[4] = 1 no CTA scatters partial dh from iteration err[5] on, so the next wait runs out
   const int mute_from = p.err[4] != 0 ? p.err[5] : 0x7fffffff;
   const bool prof = p.err[3] != 0 && blockIdx.x == 0 && lane == 0 && (warp == 0 || warp == 4);
+  const bool cut = p.cut_recurrent != 0;
 
   if (tid == 0) {
     mbar_init(smem_u32(&s_part_bar[0]), 1);
@@ -277,6 +278,9 @@ frnn_bwd_kernel(const BwdParams p, const __grid_constant__ CUtensorMap cache_map
 #pragma unroll
         for (int j = 0; j < IPT; ++j) ds[q][j] = dcar[q][j];
       float cache[CT::GC][IPT], sn[S][IPT], sp[S][IPT];
+      float dh_ext[IPT];
+#pragma unroll
+      for (int j = 0; j < IPT; ++j) dh_ext[j] = 0.0f;
       if (it < T) {
         const int s = it % Cfg::NST;
         if (!dead && !mbar_wait_bounded<false>(smem_u32(&s_full[s]), (it / Cfg::NST) & 1, limit, abort_flag)) {
@@ -300,7 +304,10 @@ frnn_bwd_kernel(const BwdParams p, const __grid_constant__ CUtensorMap cache_map
             float dhv[IPT];
             ld_f32_vec<IPT>(q + k * sbu + ib * U + ul, dhv);
 #pragma unroll
-            for (int j = 0; j < IPT; ++j) ds[k][j] += dhv[j];
+            for (int j = 0; j < IPT; ++j) {
+              if (k == 0) dh_ext[j] = dhv[j];  // added after the recurrent part (which may be clipped) is complete
+              else ds[k][j] += dhv[j];
+            }
           }
         }
         mbar_arrive(smem_u32(&s_empty[s]));
@@ -361,7 +368,7 @@ frnn_bwd_kernel(const BwdParams p, const __grid_constant__ CUtensorMap cache_map
                 }
               }
             }
-            if (active && !dead) {
+            if (active && !dead && !cut) {
 #pragma unroll
               for (int k = 0; k < SB; ++k)
                 if (s0 + k < C) {
@@ -379,7 +386,7 @@ frnn_bwd_kernel(const BwdParams p, const __grid_constant__ CUtensorMap cache_map
           dead = true;
         }
         if (prof && !xg) pc5 += clock64() - c1;
-        if (active && !xg) {
+        if (active && !xg && !cut) {
           const float* pbuf = part + static_cast<size_t>(pb) * (part_bytes / 4) + ib * U + ul;
           // fixed summation order; the loads of eight sources are issued together before the adds
           for (int s0 = 0; s0 < C; s0 += 8) {
@@ -400,6 +407,9 @@ frnn_bwd_kernel(const BwdParams p, const __grid_constant__ CUtensorMap cache_map
           }
         }
       }
+      // the gradient carried into h_t from step t + 1 is complete here: clip it, then add the external one
+#pragma unroll
+      for (int j = 0; j < IPT; ++j) ds[0][j] = (it >= 1 ? clip_sym(ds[0][j], p.grad_clip) : ds[0][j]) + dh_ext[j];
       const long long c2 = prof ? clock64() : 0;
       if (it == T) {
         if (active) {
@@ -420,7 +430,7 @@ frnn_bwd_kernel(const BwdParams p, const __grid_constant__ CUtensorMap cache_map
           for (int g = 0; g < GCL; ++g) cj[g] = cache[g][j];
 #pragma unroll
           for (int q = 0; q < S; ++q) { snj[q] = sn[q][j]; spj[q] = sp[q][j]; dsj[q] = ds[q][j]; }
-          cell_backward<CELL>(cj, spj, snj, dsj, gr, gw, gb, take_i);
+          cell_backward<CELL>(cj, spj, snj, dsj, gr, gw, gb, take_i, p.slstm_v1 != 0);
 #pragma unroll
           for (int q = 0; q < S; ++q) dcar[q][j] = dsj[q];
 #pragma unroll

@@ -316,7 +316,7 @@ frnn_bwd_ks_kernel(const BwdParams p, const __grid_constant__ CUtensorMap cache_
 #pragma unroll
       for (int j = 0; j < NI; ++j)
 #pragma unroll
-        for (int q = 0; q < S; ++q) ds[j][q] = dcar[j][q] + (it < T ? dhs[j][q] : 0.0f);
+        for (int q = 0; q < S; ++q) ds[j][q] = dcar[j][q] + ((it < T && q > 0) ? dhs[j][q] : 0.0f);
       if (it >= 1) {
         // partial dh of this step from the KS CTAs of the cluster
         if (!dead && !mbar_wait_bounded<true, false>(smem_u32(&s_part_bar[pb]), ((it - 1) >> 1) & 1, limit, abort_flag)) {
@@ -327,13 +327,19 @@ frnn_bwd_ks_kernel(const BwdParams p, const __grid_constant__ CUtensorMap cache_
 #pragma unroll
         for (int j = 0; j < NI; ++j) {
           const int ib = (ib0 + j * RPP) % BV;
+          if (p.cut_recurrent == 0) {
 #pragma unroll
-          for (int src = 0; src < KS; ++src) ds[j][0] += pbuf[(src * BV + ib) * UO + ul];
+            for (int src = 0; src < KS; ++src) ds[j][0] += pbuf[(src * BV + ib) * UO + ul];
+          }
         }
         // the buffer of this parity is free again: arm its barrier for iteration it + 2 (only a barrier
         // whose phase has completed may be armed again, hence not after a failed wait)
         if (tid == 0 && !dead && it + 2 <= T) mbar_arrive_expect_tx(smem_u32(&s_part_bar[pb]), part_tx);
       }
+      // the gradient carried into h_t from step t + 1 is complete here: clip it, then add the external one
+#pragma unroll
+      for (int j = 0; j < NI; ++j)
+        ds[j][0] = (it >= 1 ? clip_sym(ds[j][0], p.grad_clip) : ds[j][0]) + (it < T ? dhs[j][0] : 0.0f);
       const long long c1 = prof ? clock64() : 0;
       if (it == T) {
 #pragma unroll
@@ -351,7 +357,7 @@ frnn_bwd_ks_kernel(const BwdParams p, const __grid_constant__ CUtensorMap cache_
 #pragma unroll
       for (int j = 0; j < NI; ++j) {
         float gb[CT::GB];
-        cell_backward<CELL>(cache[j], sp[j], sn[j], ds[j], gr[j], gw[j], gb, take_i);
+        cell_backward<CELL>(cache[j], sp[j], sn[j], ds[j], gr[j], gw[j], gb, take_i, p.slstm_v1 != 0);
 #pragma unroll
         for (int q = 0; q < S; ++q) dcar[j][q] = ds[j][q];
         if (!act[j]) {

@@ -147,7 +147,8 @@ frnn_fwd_kernel(const FwdParams p, const __grid_constant__ CUtensorMap wx_map) {
   const int d0 = rank * U + ul;     // unit offset inside the head
   float st[CT::S][IPT];
   float bias[CT::GB][IPT];
-  const size_t sBTND = static_cast<size_t>(B) * T * N * D;
+  const int Tt = p.T_total, t0 = p.t0;
+  const size_t sBTND = static_cast<size_t>(B) * Tt * N * D;
   const size_t item_bn = (static_cast<size_t>(b0 + ib) * N + n) * D + d0;  // into [B][1][N][D]
   if (active) {
 #pragma unroll
@@ -240,11 +241,13 @@ frnn_fwd_kernel(const FwdParams p, const __grid_constant__ CUtensorMap wx_map) {
         // is set before any thread skips a wait, so checking it after the wait above is enough.
         if (*abort_flag != 0) break;
         mbar_arrive_expect_tx(smem_u32(&s_wx_full[s]), stage_tx);
-        tma_load_5d(smem_u32(wxs + s * Cfg::WX_STAGE_BYTES), &wx_map, smem_u32(&s_wx_full[s]), rank * U, n, 0, t, b0);
+        tma_load_5d(smem_u32(wxs + s * Cfg::WX_STAGE_BYTES), &wx_map, smem_u32(&s_wx_full[s]), rank * U, n, 0, t0 + t, b0);
       }
     }
   } else {
-    float* hist = p.history + (static_cast<size_t>(b0 + ib) * T * N + n) * D + d0;
+    const size_t hist_off = ((static_cast<size_t>(b0 + ib) * Tt + t0) * N + n) * D + d0;  // elements, fp32 or bf16
+    float* hist = p.history + hist_off;
+    __nv_bfloat16* hist16 = reinterpret_cast<__nv_bfloat16*>(p.history) + hist_off;
     float* cache = p.cache == nullptr ? nullptr : p.cache + ((static_cast<size_t>(b0 + ib) * T * CT::GC) * N + n) * D + d0;
     __nv_bfloat16* hbf = p.hbf == nullptr ? nullptr : p.hbf + ((static_cast<size_t>(b0 + ib) * (T + 1) + 1) * N + n) * D + d0;
     const uint32_t h_off = kmajor_offset(BT, ib, d0);
@@ -323,7 +326,7 @@ frnn_fwd_kernel(const FwdParams p, const __grid_constant__ CUtensorMap wx_map) {
         float ry[CT::GR][IPT];
 #pragma unroll
         for (int g = 0; g < CT::GR; ++g) ld_f32_vec<IPT>(gbuf + ib * Cfg::GROW + g * U + ul, ry[g]);
-        const bool take_i = CELL == kSLSTM && t == 0 && zero_first;
+        const bool take_i = CELL == kSLSTM && t0 + t == 0 && zero_first;
 #pragma unroll
         for (int j = 0; j < IPT; ++j) {
           float ryj[CT::GR], wxj[CT::GW], bj[CT::GB], sj[CT::S], cj[CT::GC];
@@ -336,6 +339,7 @@ frnn_fwd_kernel(const FwdParams p, const __grid_constant__ CUtensorMap wx_map) {
 #pragma unroll
           for (int q = 0; q < CT::S; ++q) sj[q] = st[q][j];
           cell_forward<CELL>(ryj, wxj, bj, sj, cj, take_i);
+          sj[0] = clip_sym(sj[0], p.fwd_clip);
 #pragma unroll
           for (int q = 0; q < CT::S; ++q) st[q][j] = sj[q];
 #pragma unroll
@@ -443,8 +447,12 @@ frnn_fwd_kernel(const FwdParams p, const __grid_constant__ CUtensorMap wx_map) {
       }
       if (active) {
 #pragma unroll
-        for (int q = 0; q < CT::S; ++q)
-          if (q < hist_states) st_f32_vec<IPT>(hist + q * sBTND + t * ND, st[q]);
+        for (int q = 0; q < CT::S; ++q) {
+          if (q < hist_states) {
+            if (p.out_bf16) st_bf16_vec<IPT>(hist16 + q * sBTND + t * ND, st[q]);
+            else st_f32_vec<IPT>(hist + q * sBTND + t * ND, st[q]);
+          }
+        }
         if (cache != nullptr && CELL != kElman) {
 #pragma unroll
           for (int q = 0; q < CT::GC; ++q) st_f32_vec<IPT>(cache + (static_cast<size_t>(t) * CT::GC + q) * ND, cv[q]);
@@ -467,7 +475,10 @@ frnn_fwd_kernel(const FwdParams p, const __grid_constant__ CUtensorMap wx_map) {
     if (active) {
 #pragma unroll
       for (int q = 0; q < CT::S; ++q) st_f32_vec<IPT>(p.carry + static_cast<size_t>(q) * B * N * D + item_bn, st[q]);
-      if (p.output_mode == 2) st_f32_vec<IPT>(p.history + item_bn, st[0]);  // "last": h_{T-1} as [B][1][N][D]
+      if (p.output_mode == 2) {  // "last": h of the final step as [B][1][N][D]
+        if (p.out_bf16) st_bf16_vec<IPT>(reinterpret_cast<__nv_bfloat16*>(p.history) + item_bn, st[0]);
+        else st_f32_vec<IPT>(p.history + item_bn, st[0]);
+      }
     }
   }
 
@@ -492,7 +503,7 @@ int launch_fwd(const FwdParams& p, const void* wx, cudaStream_t stream) {
   if (Cfg::A_COL0 + Cfg::MT * (p.D / 2) > 512) return -3;
   CUtensorMap map;
   const uint64_t dims[5] = {static_cast<uint64_t>(p.D), static_cast<uint64_t>(p.N), static_cast<uint64_t>(CT::GW),
-                            static_cast<uint64_t>(p.T), static_cast<uint64_t>(p.B)};
+                            static_cast<uint64_t>(p.T_total), static_cast<uint64_t>(p.B)};
   const uint32_t box[5] = {static_cast<uint32_t>(U), 1u, static_cast<uint32_t>(CT::GW), 1u, static_cast<uint32_t>(p.wx_box_b)};
   if (make_tensor_map(&map, wx, Cfg::WX_ES, 5, dims, box) != 0) return -4;
   auto kern = frnn_fwd_kernel<CELL, BV, U, WX_BF16, XG>;

@@ -149,7 +149,8 @@ frnn_fwd_ks_kernel(const FwdParams p, const __grid_constant__ CUtensorMap wx_map
   float st[NI][CT::S];
   float bias[CT::GB];
   bool act[NI];
-  const size_t sBTND = static_cast<size_t>(B) * T * N * D;
+  const int Tt = p.T_total, t0 = p.t0;
+  const size_t sBTND = static_cast<size_t>(B) * Tt * N * D;
   const size_t ND = static_cast<size_t>(N) * D;
 #pragma unroll
   for (int j = 0; j < NI; ++j) {
@@ -225,7 +226,7 @@ frnn_fwd_ks_kernel(const FwdParams p, const __grid_constant__ CUtensorMap wx_map
         // is set before any thread skips a wait, so checking it after the wait above is enough.
         if (*abort_flag != 0) break;
         mbar_arrive_expect_tx(smem_u32(&s_wx_full[s]), stage_tx);
-        tma_load_5d(smem_u32(wxs + s * Cfg::WX_STAGE_BYTES), &wx_map, smem_u32(&s_wx_full[s]), rt * 32 + ks * UO, n, 0, t, b0);
+        tma_load_5d(smem_u32(wxs + s * Cfg::WX_STAGE_BYTES), &wx_map, smem_u32(&s_wx_full[s]), rt * 32 + ks * UO, n, 0, t0 + t, b0);
       }
     }
   } else {
@@ -321,10 +322,11 @@ frnn_fwd_ks_kernel(const FwdParams p, const __grid_constant__ CUtensorMap wx_map
       if (tid == 0 && !dead && t + 2 < T) mbar_arrive_expect_tx(smem_u32(&s_part_bar[pb]), part_tx);
       float cv[NI][CT::GC];
       uint32_t hb16[NI];
-      const bool take_i = CELL == kSLSTM && t == 0 && zero_first;
+      const bool take_i = CELL == kSLSTM && t0 + t == 0 && zero_first;
 #pragma unroll
       for (int j = 0; j < NI; ++j) {
         cell_forward<CELL>(ry[j], wx[j], bias, st[j], cv[j], take_i);
+        st[j][0] = clip_sym(st[j][0], p.fwd_clip);
         hb16[j] = act[j] ? static_cast<uint32_t>(__bfloat16_as_ushort(__float2bfloat16_rn(st[j][0]))) : 0u;
       }
       const long long c5 = prof ? clock64() : 0;
@@ -394,10 +396,15 @@ frnn_fwd_ks_kernel(const FwdParams p, const __grid_constant__ CUtensorMap wx_map
 #pragma unroll
       for (int j = 0; j < NI; ++j) {
         if (act[j]) {
-          const size_t row = (static_cast<size_t>(b0 + ib0 + j * RPP) * T + t);
+          const size_t row = (static_cast<size_t>(b0 + ib0 + j * RPP) * T + t);       // cache / hbf: whole-sequence calls only
+          const size_t hrow = (static_cast<size_t>(b0 + ib0 + j * RPP) * Tt + t0 + t);
 #pragma unroll
-          for (int q = 0; q < CT::S; ++q)
-            if (q < hist_states) p.history[q * sBTND + row * ND + n * D + d0] = st[j][q];
+          for (int q = 0; q < CT::S; ++q) {
+            if (q < hist_states) {
+              if (p.out_bf16) reinterpret_cast<__nv_bfloat16*>(p.history)[q * sBTND + hrow * ND + n * D + d0] = __float2bfloat16_rn(st[j][q]);
+              else p.history[q * sBTND + hrow * ND + n * D + d0] = st[j][q];
+            }
+          }
           if (p.cache != nullptr && CELL != kElman) {
 #pragma unroll
             for (int q = 0; q < CT::GC; ++q) p.cache[(row * CT::GC + q) * ND + n * D + d0] = cv[j][q];
@@ -422,8 +429,11 @@ frnn_fwd_ks_kernel(const FwdParams p, const __grid_constant__ CUtensorMap wx_map
 #pragma unroll
         for (int q = 0; q < CT::S; ++q)
           p.carry[static_cast<size_t>(q) * B * ND + static_cast<size_t>(b0 + ib0 + j * RPP) * ND + n * D + d0] = st[j][q];
-        if (p.output_mode == 2)  // "last": h_{T-1} as [B][1][N][D]
-          p.history[static_cast<size_t>(b0 + ib0 + j * RPP) * ND + n * D + d0] = st[j][0];
+        if (p.output_mode == 2) {  // "last": h of the final step as [B][1][N][D]
+          const size_t at = static_cast<size_t>(b0 + ib0 + j * RPP) * ND + n * D + d0;
+          if (p.out_bf16) reinterpret_cast<__nv_bfloat16*>(p.history)[at] = __float2bfloat16_rn(st[j][0]);
+          else p.history[at] = st[j][0];
+        }
       }
     }
   }
@@ -451,7 +461,7 @@ int launch_fwd_ks(const FwdParams& p, const void* wx, cudaStream_t stream, int* 
   int smem = ((2 * hbuf_bytes + 2 * Cfg::PART_BYTES + 127) & ~127) + kWxStages * Cfg::WX_STAGE_BYTES;
   CUtensorMap map;
   const uint64_t dims[5] = {static_cast<uint64_t>(p.D), static_cast<uint64_t>(p.N), static_cast<uint64_t>(CT::GW),
-                            static_cast<uint64_t>(p.T), static_cast<uint64_t>(p.B)};
+                            static_cast<uint64_t>(p.T_total), static_cast<uint64_t>(p.B)};
   const uint32_t box[5] = {static_cast<uint32_t>(Cfg::UO), 1u, static_cast<uint32_t>(CT::GW), 1u, static_cast<uint32_t>(p.wx_box_b)};
   if (capacity_only == nullptr && make_tensor_map(&map, wx, Cfg::WX_ES, 5, dims, box) != 0) return -4;
   auto kern = frnn_fwd_ks_kernel<CELL, BV, KS, WX_BF16>;
@@ -525,6 +535,7 @@ int forward_ksplit_dispatch(int cell, const FwdParams& p, const void* wx, int wx
 int forward_ksplit_capacity(int cell, int bv, int ksplit, int D) {
   FwdParams p{};
   p.B = bv; p.T = 1; p.N = 1; p.D = D;
+  p.T_total = 1;
   p.wx_box_b = bv;
   int cap = 0;
   const int rc = forward_ksplit_dispatch(cell, p, nullptr, 1, bv, ksplit, nullptr, &cap);

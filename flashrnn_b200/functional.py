@@ -70,13 +70,13 @@ class _Recurrence(torch.autograd.Function):
     """One fused forward launch; backward = one BPTT launch + the dR/db contraction."""
 
     @staticmethod
-    def forward(ctx, wx, recurrent, bias, initial, cell: str, zero_first: bool):
+    def forward(ctx, wx, recurrent, bias, initial, cell: str, zero_first: bool, options=None):
         # the C ABI plans for and launches on the current device: make the tensors' device current
         with torch.cuda.device(wx.device):
-            return _Recurrence._forward(ctx, wx, recurrent, bias, initial, cell, zero_first)
+            return _Recurrence._forward(ctx, wx, recurrent, bias, initial, cell, zero_first, options)
 
     @staticmethod
-    def _forward(ctx, wx, recurrent, bias, initial, cell: str, zero_first: bool):
+    def _forward(ctx, wx, recurrent, bias, initial, cell: str, zero_first: bool, options):
         lib = _lib.load()
         poll_errors()
         B, T, _, N, D = wx.shape
@@ -102,10 +102,10 @@ class _Recurrence(torch.autograd.Function):
             hbf = torch.empty(plan.hbf_bytes // 2, dtype=torch.bfloat16, device=dev)
         xchg = torch.empty(plan.xchg_bytes, dtype=torch.uint8, device=dev) if plan.xchg_bytes else None
         err = torch.zeros(32, dtype=torch.int32, device=dev)
-        rc = lib.frnn_b200_forward(
+        rc = lib.frnn_b200_forward_ex(
             _lib.CELLS[cell], wx_c.data_ptr(), int(wx_c.dtype == torch.bfloat16), r_bf.data_ptr(), b32.data_ptr(),
             init32.data_ptr(), history.data_ptr(), carry.data_ptr(), _ptr(cache), _ptr(hbf), _ptr(xchg), B, T, N, D,
-            int(zero_first), 0, err.data_ptr(), _stream(dev),
+            int(zero_first), 0, err.data_ptr(), _stream(dev), _options_struct(options),
         )
         _lib.check(rc, "frnn_b200_forward")
         _track(err, "frnn_b200_forward")
@@ -115,6 +115,7 @@ class _Recurrence(torch.autograd.Function):
             ctx.shape = (B, T, N, D)
             ctx.dtypes = (wx.dtype, recurrent.dtype, bias.dtype, initial.dtype)
             ctx.plan = plan
+            ctx.options = options
         return history, carry
 
     @staticmethod
@@ -152,12 +153,12 @@ class _Recurrence(torch.autograd.Function):
         xchg = torch.empty(plan.xchg_bytes, dtype=torch.uint8, device=dev) if plan.xchg_bytes else None
         err = torch.zeros(32, dtype=torch.int32, device=dev)
         stream = _stream(dev)
-        rc = lib.frnn_b200_backward(
+        rc = lib.frnn_b200_backward_ex(
             _lib.CELLS[cell], _ptr(cache) if cache.numel() else None, history.data_ptr(), init32.data_ptr(),
             r_bf.data_ptr(), d_history.data_ptr(), d_carry.data_ptr(), dwx.data_ptr(),
             int(wx_dtype == torch.bfloat16), dgr.data_ptr(), d_initial.data_ptr(), db_part.data_ptr(), _ptr(xchg),
             B, T, N, D,
-            int(ctx.zero_first), 0, err.data_ptr(), stream,
+            int(ctx.zero_first), 0, err.data_ptr(), stream, _options_struct(ctx.options),
         )
         _lib.check(rc, "frnn_b200_backward")
         rc = lib.frnn_b200_wgrad(
@@ -174,7 +175,22 @@ class _Recurrence(torch.autograd.Function):
             d_initial.to(ctx.dtypes[3]) if need[3] else None,
             None,
             None,
+            None,
         )
+
+
+def _options_struct(options):
+    """``(forward_clipval, gradient_recurrent_clipval, gradient_recurrent_cut, slstm_v1)`` -> ctypes pointer or None."""
+    if options is None or not any(options):
+        return None
+    import ctypes
+
+    o = _lib.Options()
+    o.forward_clipval = float(options[0] or 0.0)
+    o.gradient_recurrent_clipval = float(options[1] or 0.0)
+    o.gradient_recurrent_cut = int(bool(options[2]))
+    o.slstm_v1_gradient = int(bool(options[3]))
+    return ctypes.byref(o)
 
 
 def _pad_width(t: torch.Tensor, pad: int, dims) -> torch.Tensor:
@@ -185,14 +201,14 @@ def _pad_width(t: torch.Tensor, pad: int, dims) -> torch.Tensor:
     return torch.nn.functional.pad(t, spec)
 
 
-def _run(wx, recurrent, bias, initial, cell: str, zero_normalizer: Optional[bool] = None):
+def _run(wx, recurrent, bias, initial, cell: str, zero_normalizer: Optional[bool] = None, options=None):
     if not wx.is_cuda:
         raise RuntimeError("flashrnn_b200 runs on CUDA devices only (sm_100a); there is no CPU path")
     with torch.cuda.device(wx.device):
-        return _run_on_current_device(wx, recurrent, bias, initial, cell, zero_normalizer)
+        return _run_on_current_device(wx, recurrent, bias, initial, cell, zero_normalizer, options)
 
 
-def _run_on_current_device(wx, recurrent, bias, initial, cell: str, zero_normalizer: Optional[bool]):
+def _run_on_current_device(wx, recurrent, bias, initial, cell: str, zero_normalizer: Optional[bool], options=None):
     D = wx.shape[-1]
     if cell != "slstm":
         zero_first = False
@@ -217,7 +233,7 @@ def _run_on_current_device(wx, recurrent, bias, initial, cell: str, zero_normali
     B, T, _, N, Dp = wx.shape
     heads, rows = _launch_split(cell, B, T, N, Dp)
     if heads >= N and rows >= B:
-        history, carry = _Recurrence.apply(wx, recurrent, bias, initial, cell, zero_first)
+        history, carry = _Recurrence.apply(wx, recurrent, bias, initial, cell, zero_first, options)
     else:
         # Wide heads run with all CTAs of a launch resident at once, which bounds the heads and batch
         # rows one launch can take; more go through several launches (heads and batch rows are
@@ -227,7 +243,7 @@ def _run_on_current_device(wx, recurrent, bias, initial, cell: str, zero_normali
             n1 = min(N, n0 + heads)
             wx_h = wx if heads >= N else wx[:, :, :, n0:n1].contiguous()
             pieces = [_Recurrence.apply(wx_h[i:i + rows], recurrent[:, n0:n1], bias[:, n0:n1],
-                                        initial[:, i:i + rows, :, n0:n1], cell, zero_first)
+                                        initial[:, i:i + rows, :, n0:n1], cell, zero_first, options)
                       for i in range(0, B, rows)]
             per_head.append((torch.cat([h for h, _ in pieces], dim=1), torch.cat([c for _, c in pieces], dim=1)))
         history = torch.cat([h for h, _ in per_head], dim=3)
@@ -308,14 +324,36 @@ def flashrnn_torch(wx, recurrent, bias, initial, *, cell: str = "lstm", numerics
 
 @dataclass
 class FlashRNNConfig:
-    """The fields of the reference's FlashRNNConfig (flashrnn.py:121-170) this backend honours."""
+    """The fields of the reference's FlashRNNConfig (flashrnn/flashrnn/flashrnn.py:121-170) this backend honours.
+
+    ``gradient_recurrent_cut`` / ``gradient_recurrent_clipval`` / ``forward_clipval`` behave as in the reference's
+    fused kernels (flashrnn/flashrnn/fused/lstm_fused_pointwise.cuh:76-81,116-122, flashrnn_fused_backward_cut.cu):
+    h_t is clipped before it is stored and fed back (the backward treats the clip as the identity); the gradient
+    carried into h_t from step t+1 is clipped before the external gradient of h_t is added; with the cut the R path
+    contributes nothing to the hidden-state gradient. ``slstm_gradient="v1"`` selects the gradient convention of the
+    reference's own kernels (m without gradient, normaliser clamp straight-through: flashrnn2/grad_reference.py:1-13)
+    instead of what autograd gives for the forward formulas (the default, ``"autograd"``)."""
 
     function: str = "lstm"
     backend: str = BACKEND
     dtype: str = "bfloat16"
+    gradient_recurrent_cut: bool = False
+    gradient_recurrent_clipval: Optional[float] = None
+    forward_clipval: Optional[float] = None
+    slstm_gradient: str = "autograd"
     head_dim: int = -1
     num_heads: int = -1
     batch_size: int = -1
+
+    def options(self):
+        if self.slstm_gradient not in ("autograd", "v1"):
+            raise ValueError("slstm_gradient must be 'autograd' or 'v1'")
+        for name in ("gradient_recurrent_clipval", "forward_clipval"):
+            v = getattr(self, name)
+            if v is not None and not v > 0:
+                raise ValueError(f"{name} must be positive or None")
+        return (self.forward_clipval, self.gradient_recurrent_clipval, self.gradient_recurrent_cut,
+                self.slstm_gradient == "v1")
 
 
 def flashrnn(Wx, R, b, states=None, function: str = "lstm", config: Optional[FlashRNNConfig] = None,
@@ -325,8 +363,10 @@ def flashrnn(Wx, R, b, states=None, function: str = "lstm", config: Optional[Fla
     ``dtype`` is the operand dtype of the streamed input (``Wx`` is cast to it, R always goes to
     the tensor cores in bf16); bias and states keep fp32, and the returned states are fp32.
     """
+    options = None
     if config is not None:
         function, backend, dtype = config.function, config.backend, config.dtype
+        options = config.options()
     if backend != BACKEND:
         raise ValueError(f"Unknown backend {backend}: this library provides backend='{BACKEND}' only")
     if function not in SIZES:
@@ -343,4 +383,4 @@ def flashrnn(Wx, R, b, states=None, function: str = "lstm", config: Optional[Fla
         raise ValueError("states must have layout [S,B,1,N,D]")
     with torch.autocast("cuda", enabled=False):
         return _run(Wx.to(_DTYPES[dtype]), R, b.to(torch.float32), states.to(torch.float32), function,
-                    zero_normalizer)
+                    zero_normalizer, options)

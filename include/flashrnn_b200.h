@@ -95,6 +95,32 @@ int frnn_b200_forward(int cell, const void* wx, int wx_bf16, const void* r_bf16,
                       void* xchg, int B, int T, int N, int D, int slstm_zero_first, int wait_limit_ms,
                       int* err, void* stream);
 
+/* Options of the reference's v1 configuration (flashrnn/flashrnn/flashrnn.py:128-133), applied the way its fused
+ * kernels apply them (flashrnn/flashrnn/fused/lstm_fused_pointwise.cuh:76-81,116-122,
+ * flashrnn/flashrnn/fused/flashrnn_fused_backward_cut.cu:90), and the choice of the sLSTM gradient convention
+ * (flashrnn/flashrnn2/grad_reference.py:1-13). A NULL pointer or an all-zero struct means "none": the behaviour of
+ * frnn_b200_forward / frnn_b200_backward. */
+typedef struct frnn_b200_options {
+  float forward_clipval;             /* > 0: h_t is clipped to [-v, v] before it is stored and fed back; the
+                                        backward pass treats the clip as the identity                              */
+  float gradient_recurrent_clipval;  /* > 0: the gradient that reaches h_t from step t+1 is clipped to [-v, v]
+                                        before the external gradient of h_t is added                               */
+  int gradient_recurrent_cut;        /* 1: the R path contributes nothing to the hidden-state gradient              */
+  int slstm_v1_gradient;             /* 1: sLSTM stabiliser m carries no gradient, the normaliser clamp passes its
+                                        gradient straight through (0: exactly what autograd gives)                  */
+} frnn_b200_options_t;
+
+/* frnn_b200_forward / frnn_b200_backward with options. */
+int frnn_b200_forward_ex(int cell, const void* wx, int wx_bf16, const void* r_bf16, const float* bias,
+                         const float* initial, float* history, float* carry, float* cache, void* hbf, void* xchg,
+                         int B, int T, int N, int D, int slstm_zero_first, int wait_limit_ms, int* err, void* stream,
+                         const frnn_b200_options_t* options);
+int frnn_b200_backward_ex(int cell, const float* cache, const float* history, const float* initial,
+                          const void* r_bf16, const float* d_history, const float* d_carry, void* dwx, int wx_bf16,
+                          void* dgr, float* d_initial, float* db_part, void* xchg, int B, int T, int N, int D,
+                          int slstm_zero_first, int wait_limit_ms, int* err, void* stream,
+                          const frnn_b200_options_t* options);
+
 /* Forward-only variant for preallocated, replayable sequences (the reference's PreparedSequence,
  * flashrnn/flashrnn2/prepared.py:18-192, and the output modes of hybrid_fw2d.cu:52-66): no gate
  * cache and no bf16 copy of h are written.
@@ -106,9 +132,20 @@ int frnn_b200_forward(int cell, const void* wx, int wx_bf16, const void* r_bf16,
  *               host read is involved, so the call can be captured in a CUDA graph.
  * Everything else as frnn_b200_forward. */
 int frnn_b200_forward_prepared(int cell, const void* wx, int wx_bf16, const void* r_bf16, const float* bias,
-                               const float* initial, float* output, float* carry, void* xchg, int B, int T, int N,
+                               const float* initial, void* output, float* carry, void* xchg, int B, int T, int N,
                                int D, int output_mode, const int* slstm_zero_first_dev, int wait_limit_ms, int* err,
                                void* stream);
+
+/* One chunk [t_start, t_start + steps) of a prepared sequence of T_total steps (the chunked execution with
+ * alternating carries of flashrnn/flashrnn2/prepared.py:61-63,120-159): wx and output are the tensors of the WHOLE
+ * sequence, `initial` is the carry of the previous chunk (the sequence's initial state for the first one), `carry`
+ * receives this chunk's final state. With output_bf16 = 1 the state snapshots are stored as bf16 (prepared.py:21,
+ * 58-60 snapshot_dtype); carries stay fp32. The sLSTM word must hold the predicate of the sequence's initial state;
+ * it only takes effect in the chunk that contains step 0. output_mode 2 ("last") writes h of the chunk's last step. */
+int frnn_b200_forward_chunk(int cell, const void* wx, int wx_bf16, const void* r_bf16, const float* bias,
+                            const float* initial, void* output, int output_bf16, float* carry, void* xchg, int B,
+                            int T_total, int t_start, int steps, int N, int D, int output_mode,
+                            const int* slstm_zero_first_dev, int wait_limit_ms, int* err, void* stream);
 
 /* Reverse-time recurrence (flashrnn/flashrnn/fused/flashrnn.cc:147-247 backward();
  * gradient structure of flashrnn/flashrnn/vanilla_fwbw/bw.py:20-98).

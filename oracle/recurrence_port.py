@@ -35,11 +35,14 @@ def _bf(x: torch.Tensor, on: bool) -> torch.Tensor:
     return x.to(torch.bfloat16).to(x.dtype) if on else x
 
 
-def forward(wx, R, b, initial, cell="lstm", bf16_mma=True, zero_first=None):
+def forward(wx, R, b, initial, cell="lstm", bf16_mma=True, zero_first=None, forward_clipval=None):
     """Return (history [S,B,T,N,D], carry [S,B,1,N,D], tape). ``tape`` feeds ``backward``.
 
     ``zero_first`` overrides the sLSTM "all n == 0" predicate of the first step (a shard of a
     larger call must use the predicate of the whole call, state_contract.py:81-97).
+    ``forward_clipval`` (v1 option, flashrnn/flashrnn/fused/lstm_fused_pointwise.cuh:76-81): the new hidden state is
+    clipped to [-v, v] before it is stored and fed back. The reference implements its v1 options only in its CUDA
+    kernels, which cannot run here: this restatement of them is NOT pinned against reference outputs.
     """
     gr, gw, gb, S = SIZES[cell]
     B, T, G, N, D = wx.shape
@@ -85,6 +88,8 @@ def forward(wx, R, b, initial, cell="lstm", bf16_mma=True, zero_first=None):
             new = [torch.tanh(x[:, 0] + ry[:, 0] + b[0])]
         else:
             raise ValueError(cell)
+        if forward_clipval is not None:
+            new = [new[0].clamp(-forward_clipval, forward_clipval)] + list(new[1:])
         rec["new"] = new
         tape.append(rec)
         state = new
@@ -101,8 +106,14 @@ def _tie_mask(a: torch.Tensor, b: torch.Tensor) -> torch.Tensor:
     return torch.where(a > b, one, torch.where(a == b, half, zero))
 
 
-def backward(tape, d_history, d_carry):
-    """Gradients (dWx, dR, db, d_initial) of sum(history*d_history) + sum(carry*d_carry)."""
+def backward(tape, d_history, d_carry, gradient_recurrent_clipval=None, gradient_recurrent_cut=False, slstm_v1=False):
+    """Gradients (dWx, dR, db, d_initial) of sum(history*d_history) + sum(carry*d_carry).
+
+    v1 options (flashrnn/flashrnn/fused/lstm_fused_pointwise.cuh:116-122, flashrnn_fused_backward_cut.cu:90; not pinned,
+    see ``forward``): the gradient carried into h_t from step t+1 is clipped before the external one is added; with the
+    cut the R path contributes nothing; a forward clip counts as the identity. ``slstm_v1``: the gradient convention of
+    the reference's kernels and of flashrnn/flashrnn2/grad_reference.py:1-13 (pinned by a golden vector made from that
+    module): m carries no gradient, the normaliser clamp passes its gradient straight through."""
     cell, Rr, on = tape["cell"], tape["R"], tape["bf16_mma"]
     gr, gw, gb, S = SIZES[cell]
     B, T, N, D = tape["shape"]
@@ -114,7 +125,10 @@ def backward(tape, d_history, d_carry):
     for t in range(T - 1, -1, -1):
         rec = tape["steps"][t]
         prev, new = rec["prev"], rec["new"]
-        ds = [dcar[s] + d_history[s, :, t] for s in range(S)]
+        carried = dcar
+        if gradient_recurrent_clipval is not None and t < T - 1:
+            carried = [dcar[0].clamp(-gradient_recurrent_clipval, gradient_recurrent_clipval)] + list(dcar[1:])
+        ds = [carried[s] + d_history[s, :, t] for s in range(S)]
         if cell == "lstm":
             si, sf, tz, so, tc = rec["si"], rec["sf"], rec["tz"], rec["so"], rec["tc"]
             dh = ds[0]
@@ -134,13 +148,13 @@ def backward(tape, d_history, d_carry):
             dc = ds[1] + dh * so / n1
             dn = ds[2] - dh * so * c1 / (n1 * n1)
             d_o = dh * (c1 / n1) * so * (1 - so)
-            dpre = dn * _tie_mask(rec["pre_n"], torch.ones_like(n1))
+            dpre = dn if slstm_v1 else dn * _tie_mask(rec["pre_n"], torch.ones_like(n1))
             d_ig = dc * tz + dpre
             d_fg = dc * c0 + dpre * n0
             d_z = dc * ig * (1 - tz * tz)
             d_i = d_ig * ig
             d_logf = d_fg * fg
-            dm = ds[3] - d_i - d_logf
+            dm = torch.zeros_like(d_i) if slstm_v1 else ds[3] - d_i - d_logf
             if rec["zero"]:
                 d_i = d_i + dm
             else:
@@ -150,7 +164,7 @@ def backward(tape, d_history, d_carry):
             d_f = d_logf * (1 - torch.sigmoid(f))
             dg_r = torch.stack((d_i, d_f, d_z, d_o), dim=1)
             dg_w, dg_b = dg_r, dg_r
-            dprev = [torch.zeros_like(dh), dc * fg, dpre * fg, d_logf]
+            dprev = [torch.zeros_like(dh), dc * fg, dpre * fg, torch.zeros_like(dh) if slstm_v1 else d_logf]
         elif cell == "gru":
             cand, r, u, v = rec["cand"], rec["r"], rec["u"], rec["v"]
             dh = ds[0]
@@ -171,15 +185,17 @@ def backward(tape, d_history, d_carry):
         dwx[:, t] = dg_w
         db += dg_b.sum(dim=0)
         dR += _bf(torch.einsum("bgno,bnp->gnop", dg_r, rec["h_op"]), on)
-        dprev[0] = dprev[0] + _bf(torch.einsum("bgno,gnop->bnp", dg_r, Rr), on)
+        if not gradient_recurrent_cut:
+            dprev[0] = dprev[0] + _bf(torch.einsum("bgno,gnop->bnp", dg_r, Rr), on)
         dcar = dprev
     d_initial = torch.stack(dcar, dim=0).unsqueeze(2)
     return dwx, dR, db, d_initial
 
 
-def forward_backward(wx, R, b, initial, cell, d_history, d_carry, bf16_mma=True, zero_first=None):
+def forward_backward(wx, R, b, initial, cell, d_history, d_carry, bf16_mma=True, zero_first=None, forward_clipval=None,
+                     gradient_recurrent_clipval=None, gradient_recurrent_cut=False, slstm_v1=False):
     """Convenience: forward + backward, everything detached."""
     with torch.no_grad():
-        history, carry, tape = forward(wx, R, b, initial, cell, bf16_mma, zero_first)
-        grads = backward(tape, d_history, d_carry)
+        history, carry, tape = forward(wx, R, b, initial, cell, bf16_mma, zero_first, forward_clipval)
+        grads = backward(tape, d_history, d_carry, gradient_recurrent_clipval, gradient_recurrent_cut, slstm_v1)
     return history, carry, grads

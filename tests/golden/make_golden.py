@@ -90,7 +90,41 @@ def main(reference_root: str) -> None:
         print(f"{name}: wrote {sum(v.nbytes for v in out.values()) / 1024:.0f} KiB (uncompressed)")
 
 
+# sLSTM under the gradient convention of the reference's own kernels: float64 autograd of
+# flashrnn/flashrnn2/grad_reference.py (m without gradient, normaliser clamp straight-through), "mathematical" forward.
+V1_CASES = {"slstm_v1_zero_init": (3, 9, 2, 8, 21, True), "slstm_v1_nonzero_init": (2, 7, 1, 16, 22, False)}
+
+
+def main_v1(reference_root: str) -> None:
+    import importlib.util
+
+    pkg = Path(reference_root) / "flashrnn" / "flashrnn2"   # loaded as a package of its own: the top-level package pulls in CUDA JIT code
+    spec = importlib.util.spec_from_file_location("_ref_flashrnn2", pkg / "__init__.py", submodule_search_locations=[str(pkg)])
+    module = importlib.util.module_from_spec(spec)
+    sys.modules["_ref_flashrnn2"] = module
+    spec.loader.exec_module(module)
+    from _ref_flashrnn2 import grad_reference
+
+    out_dir = HERE / "v1"
+    out_dir.mkdir(exist_ok=True)
+    for name, (B, T, N, D, seed, zero) in V1_CASES.items():
+        wx, R, b, initial = (t.double() for t in make_inputs("slstm", B, T, N, D, seed, zero))
+        leaves = [t.clone().requires_grad_(True) for t in (wx, R, b, initial)]
+        history, carry = grad_reference.recurrence(*leaves, cell="slstm")
+        g = torch.Generator().manual_seed(seed + 1000)
+        d_history = torch.randn(history.shape, generator=g, dtype=torch.float64)
+        d_carry = torch.randn(carry.shape, generator=g, dtype=torch.float64)
+        ((history * d_history).sum() + (carry * d_carry).sum()).backward()
+        meta = dict(cell="slstm", B=B, T=T, N=N, D=D, seed=seed, zero_initial=zero, convention="v1", dtype="float64")
+        np.savez_compressed(out_dir / f"{name}.npz", meta=np.array(repr(meta)), wx=wx.numpy(), R=R.numpy(), b=b.numpy(),
+                            initial=initial.numpy(), d_history=d_history.numpy(), d_carry=d_carry.numpy(),
+                            history=history.detach().numpy(), carry=carry.detach().numpy(), dwx=leaves[0].grad.numpy(),
+                            dR=leaves[1].grad.numpy(), db=leaves[2].grad.numpy(), d_initial=leaves[3].grad.numpy())
+        print(f"v1/{name}: written")
+
+
 if __name__ == "__main__":
     if len(sys.argv) != 2:
         raise SystemExit("usage: python tests/golden/make_golden.py <path of a checkout of the reference (0z5a/flashrnn)>")
     main(sys.argv[1])
+    main_v1(sys.argv[1])

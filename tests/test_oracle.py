@@ -63,3 +63,22 @@ def test_port_backward_equals_autograd_in_float64(cell):
     _, _, grads = port.forward_backward(wx, R, b, initial, cell, d_history, d_carry, bf16_mma=False)
     for got, leaf in zip(grads, leaves):
         assert torch.allclose(got, leaf.grad, rtol=1e-10, atol=1e-11), cell
+
+
+@pytest.mark.parametrize("name", ["slstm_v1_zero_init", "slstm_v1_nonzero_init"])
+def test_port_v1_slstm_convention_matches_reference_vectors(name):
+    """The sLSTM gradient convention of the reference's own kernels (m without gradient, normaliser clamp
+    straight-through) against float64 vectors from autograd of the reference's flashrnn2/grad_reference.py."""
+    import ast
+
+    import numpy as np
+
+    z = np.load(_golden.GOLDEN / "v1" / f"{name}.npz")
+    meta = ast.literal_eval(str(z["meta"]))
+    assert meta["convention"] == "v1"
+    t = {k: torch.from_numpy(z[k]) for k in z.files if k != "meta"}
+    history, carry, (dwx, dR, db, d_initial) = port.forward_backward(
+        t["wx"], t["R"], t["b"], t["initial"], "slstm", t["d_history"], t["d_carry"], bf16_mma=False, slstm_v1=True)
+    for key, got in (("history", history), ("carry", carry), ("dwx", dwx), ("dR", dR), ("db", db), ("d_initial", d_initial)):
+        assert torch.allclose(got, t[key], rtol=1e-10, atol=1e-11), (name, key)
+    assert torch.count_nonzero(d_initial[3]) == 0   # d(initial m) = 0 under this convention
