@@ -409,7 +409,7 @@ frnn_bwd_kernel(const BwdParams p, const __grid_constant__ CUtensorMap cache_map
       }
       // the gradient carried into h_t from step t + 1 is complete here: clip it, then add the external one
 #pragma unroll
-      for (int j = 0; j < IPT; ++j) ds[0][j] = (it >= 1 ? clip_sym(ds[0][j], p.grad_clip) : ds[0][j]) + dh_ext[j];
+      for (int j = 0; j < IPT; ++j) ds[0][j] = ((it >= 1 && it < T) ? clip_sym(ds[0][j], p.grad_clip) : ds[0][j]) + dh_ext[j];
       const long long c2 = prof ? clock64() : 0;
       if (it == T) {
         if (active) {
@@ -471,12 +471,16 @@ frnn_bwd_kernel(const BwdParams p, const __grid_constant__ CUtensorMap cache_map
 #pragma unroll
           for (int j = 0; j < IPT; j += 2) *reinterpret_cast<uint32_t*>(dgr_g + g * ND + j) = dgp[g][j / 2];
         if constexpr (WX_BF16) {
-          __nv_bfloat16* dwx_g = static_cast<__nv_bfloat16*>(p.dwx) + (row * CT::GW * N + n) * D + d0;
+          // A caller may pass one buffer as dwx and dgr where the two hold the same values in the same layout
+          // (bf16 Wx, cells whose W-gates are their R-gates): written once.
+          if (CELL == kGRU || p.dwx != static_cast<void*>(p.dgr)) {
+            __nv_bfloat16* dwx_g = static_cast<__nv_bfloat16*>(p.dwx) + (row * CT::GW * N + n) * D + d0;
 #pragma unroll
-          for (int g = 0; g < CT::GW; ++g)
+            for (int g = 0; g < CT::GW; ++g)
 #pragma unroll
-            for (int j = 0; j < IPT; j += 2)
-              *reinterpret_cast<uint32_t*>(dwx_g + g * ND + j) = pack_bf16x2(dgw[g][j], dgw[g][j + 1]);
+              for (int j = 0; j < IPT; j += 2)
+                *reinterpret_cast<uint32_t*>(dwx_g + g * ND + j) = pack_bf16x2(dgw[g][j], dgw[g][j + 1]);
+          }
         } else {
           float* dwx_g = static_cast<float*>(p.dwx) + (row * CT::GW * N + n) * D + d0;
 #pragma unroll

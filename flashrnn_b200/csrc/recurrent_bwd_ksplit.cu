@@ -339,7 +339,7 @@ frnn_bwd_ks_kernel(const BwdParams p, const __grid_constant__ CUtensorMap cache_
       // the gradient carried into h_t from step t + 1 is complete here: clip it, then add the external one
 #pragma unroll
       for (int j = 0; j < NI; ++j)
-        ds[j][0] = (it >= 1 ? clip_sym(ds[j][0], p.grad_clip) : ds[j][0]) + (it < T ? dhs[j][0] : 0.0f);
+        ds[j][0] = ((it >= 1 && it < T) ? clip_sym(ds[j][0], p.grad_clip) : ds[j][0]) + (it < T ? dhs[j][0] : 0.0f);
       const long long c1 = prof ? clock64() : 0;
       if (it == T) {
 #pragma unroll
@@ -412,8 +412,9 @@ frnn_bwd_ks_kernel(const BwdParams p, const __grid_constant__ CUtensorMap cache_
           }
           const size_t off = ((static_cast<size_t>(b0 + b) * T + t) * CT::GR + g) * ND + n * D + u0 + u8 * 8;
           *reinterpret_cast<uint4*>(p.dgr + off) = pk;
-          if constexpr (WX_BF16 && CELL != kGRU)  // W-gate and R-gate gradients coincide, and so do the layouts
-            *reinterpret_cast<uint4*>(static_cast<__nv_bfloat16*>(p.dwx) + off) = pk;
+          if constexpr (WX_BF16 && CELL != kGRU) {  // W-gate and R-gate gradients coincide, and so do the layouts
+            if (p.dwx != static_cast<void*>(p.dgr)) *reinterpret_cast<uint4*>(static_cast<__nv_bfloat16*>(p.dwx) + off) = pk;
+          }
         }
       }
       if constexpr (WX_BF16 && CELL == kGRU) {

@@ -140,7 +140,9 @@ class _Recurrence(torch.autograd.Function):
         d_history = d_history.to(torch.float32).contiguous()
         d_carry = d_carry.to(torch.float32).contiguous()
         dwx = torch.empty((B, T, gw, N, D), dtype=wx_dtype, device=dev)
-        dgr = torch.empty(plan.dgr_bytes // 2, dtype=torch.bfloat16, device=dev)
+        # bf16 Wx and W-gates == R-gates: dWx doubles as the bf16 operand of the dR contraction (one buffer, one write)
+        shared = wx_dtype == torch.bfloat16 and cell != "gru"
+        dgr = dwx if shared else torch.empty(plan.dgr_bytes // 2, dtype=torch.bfloat16, device=dev)
         d_initial = torch.empty((S, B, 1, N, D), dtype=torch.float32, device=dev)
         db_part = torch.empty(plan.dbpart_bytes // 4, dtype=torch.float32, device=dev)
         # dR and db are neighbours in one allocation so that a batch-sharded caller sums both with one all-reduce

@@ -152,7 +152,9 @@ int frnn_b200_forward_chunk(int cell, const void* wx, int wx_bf16, const void* r
  *   cache, history, initial : as written / passed in the forward call
  *   d_history [S,B,T,N,D], d_carry [S,B,1,N,D] : incoming gradients, fp32
  *   dwx  : out, [B,T,GW,N,D] in the Wx dtype
- *   dgr  : out scratch, bf16 [B,T,GR,N,D] (operand of frnn_b200_wgrad)
+ *   dgr  : out scratch, bf16 [B,T,GR,N,D] (operand of frnn_b200_wgrad). With bf16 Wx and a cell whose Wx gates
+ *          are its recurrent gates (lstm, slstm, elman) dwx and dgr hold the same values in the same layout: the
+ *          caller may pass the SAME buffer for both, which is then written once (saves the second copy's traffic)
  *   d_initial : out fp32 [S,B,1,N,D];  db_part: out scratch fp32 [n_btiles,GB,N,D]    */
 int frnn_b200_backward(int cell, const float* cache, const float* history, const float* initial,
                        const void* r_bf16, const float* d_history, const float* d_carry, void* dwx,
