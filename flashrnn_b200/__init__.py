@@ -6,5 +6,7 @@ Public surface = the reference's: ``flashrnn``, ``FlashRNNConfig``, ``flashrnn_t
 
 from .functional import BACKEND, SIZES, FlashRNNConfig, flashrnn, flashrnn_torch, poll_errors
 from .prepared import PreparedSequence
+from .projection import flashrnn_projected, input_projection
 
-__all__ = ["BACKEND", "SIZES", "FlashRNNConfig", "PreparedSequence", "flashrnn", "flashrnn_torch", "poll_errors"]
+__all__ = ["BACKEND", "SIZES", "FlashRNNConfig", "PreparedSequence", "flashrnn", "flashrnn_projected", "flashrnn_torch",
+           "input_projection", "poll_errors"]

@@ -99,6 +99,8 @@ SIGNATURES = {
                                 c_int, c_int, c_void_p, c_void_p]),
     "frnn_b200_wgrad_noalloc": (c_int, [c_int, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_int, c_int,
                                         c_int, c_void_p, c_void_p]),
+    "frnn_b200_input_projection": (c_int, [c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_int,
+                                           c_void_p, c_void_p]),
     "frnn_b200_mg_plan": (c_int, [c_int, c_int, c_int, c_int, c_int, POINTER(MgShard), POINTER(MgPlan)]),
     "frnn_b200_mg_capacity": (c_int, [c_int, c_int, c_int, c_int, c_int, c_int]),
     "frnn_b200_mg_forward": (c_int, [c_int, c_void_p, c_int, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p,

@@ -20,7 +20,7 @@ CSRC = PKG / "csrc"
 LIB_DIR = PKG / "lib"
 LIB_PATH = LIB_DIR / "libflashrnn_b200.so"
 SOURCES = ("capi.cu", "capi_mg.cu", "recurrent_fwd.cu", "recurrent_fwd_ksplit.cu", "recurrent_bwd.cu", "recurrent_bwd_ksplit.cu",
-           "recurrent_mg_fwd.cu", "recurrent_mg_bwd.cu", "wgrad.cu")
+           "recurrent_mg_fwd.cu", "recurrent_mg_bwd.cu", "wgrad.cu", "input_proj.cu")
 NVCC_FLAGS = (
     "-gencode", "arch=compute_100a,code=sm_100a", "-O3", "-std=c++17", "-lineinfo",
     "-Xcompiler", "-fPIC",

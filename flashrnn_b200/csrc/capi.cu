@@ -22,6 +22,9 @@ int wgrad_plan(int gr, int B, int T, int N, int D, int* np_out, int* ksplit_out,
 int wgrad_launch(int gr, int gb, const __nv_bfloat16* dgr, const __nv_bfloat16* hbf, const float* db_part, int n_btiles,
                  float* dR, float* db, float* work, int* err, int B, int T, int N, int D, cudaStream_t s);
 
+int input_proj_launch(const void* x, const void* w, const float* bias, void* out, int out_bf16, long long M, int J, int I,
+                      int* err, cudaStream_t s);
+
 int wgrad_launch_static(int gr, int gb, const __nv_bfloat16* dgr, const __nv_bfloat16* hbf, const float* db_part,
                         int n_btiles, float* dR, float* db, int* err, int B, int T, int N, int D, cudaStream_t s);
 
@@ -396,4 +399,11 @@ extern "C" int frnn_b200_wgrad_noalloc(int cell, const void* dgr, const void* hb
   return wgrad_launch_static(plan.gates_r, plan.gates_b, static_cast<const __nv_bfloat16*>(dgr),
                              static_cast<const __nv_bfloat16*>(hbf), db_part, plan.n_btiles, dR, db, err, B, T, N, D,
                              static_cast<cudaStream_t>(stream));
+}
+
+extern "C" int frnn_b200_input_projection(const void* x_bf16, const void* w_bf16, const float* bias, void* wx, int wx_bf16,
+                                          int B, int T, int gates_times_width, int inputs, int* err, void* stream) {
+  if (!x_bf16 || !w_bf16 || !wx || !err || B < 1 || T < 1) return -5;
+  return input_proj_launch(x_bf16, w_bf16, bias, wx, wx_bf16 != 0, static_cast<long long>(B) * T, gates_times_width, inputs, err,
+                           static_cast<cudaStream_t>(stream));
 }
