@@ -65,7 +65,10 @@ def build(force: bool = False, verbose: bool = False) -> Path:
         list(pool.map(run, jobs))
     objs = [str(obj_dir / (s + ".o")) for s in sources]
     if jobs or not LIB_PATH.exists():
-        run([nvcc, "-shared", "-o", str(LIB_PATH), *objs])
+        # link next to the target, then rename: a reader (or a copy of the tree) never sees a half-written library
+        tmp = LIB_PATH.with_suffix(".so.tmp")
+        run([nvcc, "-shared", "-o", str(tmp), *objs])
+        os.replace(tmp, LIB_PATH)
     return LIB_PATH
 
 

@@ -76,7 +76,7 @@ frnn_bwd_mg_kernel(const MgBwdParams p, const __grid_constant__ CUtensorMap cach
   const int Kc = K / KS;
   const int SCK = Kc < kMgSubK ? Kc : kMgSubK;
   const int NSC = Kc / SCK;
-  const int dg_bytes = BT * SCK * 2;
+  const int dg_bytes = mg_operand_bytes(SCK);
   const int k_tmem = p.k_tmem, n_ring = p.n_ring, NA = p.ring_stages;
   const bool resident = p.resident != 0;
   uint8_t* const ring = smem;
@@ -198,9 +198,10 @@ frnn_bwd_mg_kernel(const MgBwdParams p, const __grid_constant__ CUtensorMap cach
           }
           fence_proxy_async_smem();
           tc_fence_after_sync();
-          // Descriptors advance by constants: 16 k = two 512-byte k-groups of the operand (64 in units of 16 B),
-          // eight 32-bit columns of tensor memory, 16 k rows of 128 B (2048 B) inside each box of a stage.
-          uint64_t bdesc = umma_smem_desc(smem_u32(dgbuf + buf * dg_bytes), BT * 16, 128);
+          // Descriptors advance by constants: 16 k = 32 B inside a 128-byte swizzled row of the operand (2 in units of
+          // 16 B), the next 64-k block is 4096 B further (256); eight 32-bit columns of tensor memory; 16 k rows of
+          // 128 B (2048 B = 128) inside each box of a weight stage.
+          const uint64_t bdesc0 = umma_smem_desc_k_sw128(smem_u32(dgbuf + buf * dg_bytes));
           const int k0 = sc * SCK;
           int n_ts = (k_tmem - k0) / 16;
           n_ts = n_ts < 0 ? 0 : (n_ts > SCK / 16 ? SCK / 16 : n_ts);
@@ -208,9 +209,8 @@ frnn_bwd_mg_kernel(const MgBwdParams p, const __grid_constant__ CUtensorMap cach
           int kk = 0;
 #pragma unroll 4
           for (; kk < n_ts; ++kk) {
-            umma_bf16_ts(tbase, acol, bdesc, idesc_ts, (k0 | kk) != 0 ? 1u : 0u);
+            umma_bf16_ts(tbase, acol, bdesc0 + (kk >> 2) * 256 + (kk & 3) * 2, idesc_ts, (k0 | kk) != 0 ? 1u : 0u);
             acol += 8;
-            bdesc += 64;
           }
           for (; kk < SCK / 16; kk += kMgRingK / 16) {
             if (!resident || it == 0) {
@@ -222,11 +222,12 @@ frnn_bwd_mg_kernel(const MgBwdParams p, const __grid_constant__ CUtensorMap cach
               tc_fence_after_sync();
             }
             uint64_t adesc = umma_smem_desc_mn_sw128(smem_u32(ring + ring_stage * kMgRingBytes), 8192u);
+            uint64_t bdesc = bdesc0 + (kk >> 2) * 256;
 #pragma unroll
             for (int i = 0; i < kMgRingK / 16; ++i) {
               umma_bf16_ss(tbase, adesc, bdesc, idesc_ss, (k0 | kk | i) != 0 ? 1u : 0u);
               adesc += 128;
-              bdesc += 64;
+              bdesc += 2;
             }
             if (!resident) umma_commit(smem_u32(&s_aempty[ring_stage]));
             if (++ring_stage == NA) {
@@ -312,8 +313,6 @@ frnn_bwd_mg_kernel(const MgBwdParams p, const __grid_constant__ CUtensorMap cach
     constexpr int sbu = BO * 128;
     const uint32_t part_local = smem_u32(part) + static_cast<uint32_t>((ks * 128 + tid) * BO) * 4u;
     bool dead = false;
-    constexpr int NPK = kMgSubK / 8 / 4;
-    const int prow = lane;
     __nv_bfloat16* const pubw = pub + CT::GR * BO * 128;
 
     // this CTA's K-chunk of dG of step `t` -> operand buffers, one sub-chunk at a time (iteration `it`)
@@ -326,38 +325,10 @@ frnn_bwd_mg_kernel(const MgBwdParams p, const __grid_constant__ CUtensorMap cach
           mg_report(p.err, kErrWaitMma, it);
           dead = true;
         }
-        const __nv_bfloat16* src = p.dgr[rank] + static_cast<size_t>(prow) * grow + static_cast<size_t>(t) * K +
-                                   static_cast<size_t>(ks) * Kc + sc * SCK + warp * 8;
-        uint8_t* dst = dgbuf + buf * dg_bytes + warp * (BT * 16) + (prow >> 3) * 128 + (prow & 7) * 16;
-        uint32_t pend = 0;
-        if (prow < B && !dead) {
-#pragma unroll
-          for (int j = 0; j < NPK; ++j)
-            if ((warp + 4 * j) * 8 < SCK) pend |= 1u << j;
-        }
-        uint64_t t0 = 0;
-        uint32_t rounds = 0;
-        while (pend != 0u) {
-          uint4 v[NPK];
-#pragma unroll
-          for (int j = 0; j < NPK; ++j)
-            if ((pend >> j) & 1u) v[j] = ld_relaxed_sys_v4(src + j * 32);
-#pragma unroll
-          for (int j = 0; j < NPK; ++j) {
-            if (((pend >> j) & 1u) && xg_arrived(v[j])) {
-              *reinterpret_cast<uint4*>(dst + j * 4 * (BT * 16)) = v[j];
-              pend &= ~(1u << j);
-            }
-          }
-          if (pend != 0u && (++rounds & 15u) == 0u) {
-            const uint64_t now = global_timer_ns();
-            if (t0 == 0) t0 = now;
-            if (*abort_flag != 0 || now - t0 > limit) {
-              mg_report(p.err, kErrWaitDg, it);
-              dead = true;
-              break;
-            }
-          }
+        if (!dead && !mg_fetch_subchunk(p.dgr[rank] + static_cast<size_t>(t) * K + static_cast<size_t>(ks) * Kc + sc * SCK, grow,
+                                        dgbuf + buf * dg_bytes, SCK, B, warp, lane, limit, abort_flag)) {
+          mg_report(p.err, kErrWaitDg, it);
+          dead = true;
         }
         dead = __any_sync(0xffffffffu, dead);
         fence_proxy_async_smem();
@@ -537,7 +508,7 @@ int launch_bwd_mg(const MgBwdParams& p, cudaStream_t stream, int* capacity_only)
   const int K = CT::GR * p.D;
   const int Kc = K / KS;
   const int SCK = Kc < kMgSubK ? Kc : kMgSubK;
-  int smem = p.ring_stages * kMgRingBytes + 2 * kMgBT * SCK * 2 + 2 * Cfg::PART_BYTES + ((Cfg::PUB_BYTES + 127) & ~127) +
+  int smem = p.ring_stages * kMgRingBytes + 2 * mg_operand_bytes(SCK) + 2 * Cfg::PART_BYTES + ((Cfg::PUB_BYTES + 127) & ~127) +
              Cfg::NST * Cfg::STAGE_BYTES;
   if (smem > 227 * 1024) return -2;
   CUtensorMap cache_map, hist_map, init_map, dhist_map, r_map;
@@ -665,7 +636,7 @@ int backward_mg_fixed_smem(int cell, int ksplit, int D, int wx_bf16) {
   const int stage = (gcl + 3 * s) * bo * 128 * 4;
   const int nst = stage * 4 <= 49152 ? 4 : (stage * 3 <= 65536 ? 3 : 2);
   const int pub = (gr + ((wx_bf16 && cell == kGRU) ? gw : 0)) * bo * 128 * 2;
-  return 2 * kMgBT * SCK * 2 + 2 * (ksplit * 128 * bo * 4) + ((pub + 127) & ~127) + nst * stage;
+  return 2 * mg_operand_bytes(SCK) + 2 * (ksplit * 128 * bo * 4) + ((pub + 127) & ~127) + nst * stage;
 }
 
 int gather_columns_launch(const void* const* rows, void* cols, int gr, int D, int Dl, int P, int rank0, int ranks_here,

@@ -103,4 +103,57 @@ __device__ __forceinline__ bool mg_handshake(int* const* ready, int rank, int P,
   return true;
 }
 
+// Shared-memory bytes of one staged sub-chunk of the exchanged operand: blocks of [32 batch rows x 64 k] bf16,
+// every row 128 bytes, K-major with the 128-byte swizzle (the layout TMA would write and tcgen05 reads).
+__host__ __device__ inline int mg_operand_bytes(int sub_k) { return ((sub_k + 63) / 64) * 4096; }
+
+// Copy `sub_k` (<= 512) consecutive k of the operand of up to 32 batch rows from this rank's history buffer into a
+// staged sub-chunk, waiting for every 16-byte packet to arrive (no word shows the fill pattern). `src` points at
+// (batch row 0, first k of the sub-chunk), rows are `row_stride` elements apart. Eight neighbouring lanes read one
+// 128-byte piece of a row (coalesced) and store it with the swizzle (no bank conflicts). Called by the 128 epilogue
+// threads; returns false if the bounded wait ran out (the caller reports it).
+__device__ __forceinline__ bool mg_fetch_subchunk(const __nv_bfloat16* src, size_t row_stride, uint8_t* dst, int sub_k,
+                                                  int B, int warp, int lane, unsigned long long limit_ns,
+                                                  const volatile int* abort_flag) {
+  constexpr int NPK = 2 * (kMgSubK / 64);  // packets per thread: two rows of every 64-k block
+  const int chunk = lane & 7, r4 = lane >> 3;
+  const int n_blocks = (sub_k + 63) / 64;
+  uint32_t pend = 0;
+#pragma unroll
+  for (int j = 0; j < NPK; ++j) {
+    const int blk = j >> 1, row = 4 * (warp + 4 * (j & 1)) + r4;
+    if (blk < n_blocks && blk * 64 + chunk * 8 < sub_k && row < B) pend |= 1u << j;
+  }
+  uint64_t t0 = 0;
+  uint32_t rounds = 0;
+  bool ok = true;
+  while (pend != 0u) {
+    uint4 v[NPK];
+#pragma unroll
+    for (int j = 0; j < NPK; ++j) {
+      if ((pend >> j) & 1u) {
+        const int blk = j >> 1, row = 4 * (warp + 4 * (j & 1)) + r4;
+        v[j] = ld_relaxed_sys_v4(src + static_cast<size_t>(row) * row_stride + blk * 64 + chunk * 8);
+      }
+    }
+#pragma unroll
+    for (int j = 0; j < NPK; ++j) {
+      if (((pend >> j) & 1u) && xg_arrived(v[j])) {
+        const int blk = j >> 1, row = 4 * (warp + 4 * (j & 1)) + r4;
+        *reinterpret_cast<uint4*>(dst + blk * 4096 + row * 128 + ((chunk ^ (row & 7)) << 4)) = v[j];
+        pend &= ~(1u << j);
+      }
+    }
+    if (pend != 0u && (++rounds & 15u) == 0u) {  // the global timer is slow to read
+      const uint64_t now = global_timer_ns();
+      if (t0 == 0) t0 = now;
+      if (*abort_flag != 0 || now - t0 > limit_ns) {
+        ok = false;
+        break;
+      }
+    }
+  }
+  return ok;
+}
+
 }  // namespace frnn

@@ -71,7 +71,7 @@ frnn_fwd_mg_kernel(const MgFwdParams p, const __grid_constant__ CUtensorMap wx_m
   const int Kc = D / KS;
   const int SCK = Kc < kMgSubK ? Kc : kMgSubK;
   const int NSC = Kc / SCK;
-  const int hb_bytes = BT * SCK * 2;
+  const int hb_bytes = mg_operand_bytes(SCK);
   const int k_tmem = p.k_tmem, n_ring = p.n_ring, NA = p.ring_stages;
   const bool resident = p.resident != 0;
   uint8_t* const ring = smem;                               // 1024-byte aligned stages of 16 KB
@@ -193,9 +193,9 @@ frnn_fwd_mg_kernel(const MgFwdParams p, const __grid_constant__ CUtensorMap wx_m
           if (prof) pf_h += clock64() - w0;
           fence_proxy_async_smem();
           tc_fence_after_sync();
-          // Descriptors advance by constants: 16 k = two 512-byte k-groups of the operand (64 in units of 16 B),
-          // eight 32-bit columns of tensor memory, 32 B inside a 128-byte swizzled row.
-          uint64_t bdesc = umma_smem_desc(smem_u32(hbuf + buf * hb_bytes), BT * 16, 128);
+          // Descriptors advance by constants: 16 k = 32 B inside a 128-byte swizzled row (2 in units of 16 B), the
+          // next 64-k block of the operand is 4096 B further (256); eight 32-bit columns of tensor memory.
+          const uint64_t bdesc0 = umma_smem_desc_k_sw128(smem_u32(hbuf + buf * hb_bytes));
           const int k0 = sc * SCK;
           int n_ts = (k_tmem - k0) / 16;
           n_ts = n_ts < 0 ? 0 : (n_ts > SCK / 16 ? SCK / 16 : n_ts);
@@ -203,9 +203,8 @@ frnn_fwd_mg_kernel(const MgFwdParams p, const __grid_constant__ CUtensorMap wx_m
           int kk = 0;
 #pragma unroll 4
           for (; kk < n_ts; ++kk) {
-            umma_bf16_ts(tbase, acol, bdesc, idesc, (k0 | kk) != 0 ? 1u : 0u);
+            umma_bf16_ts(tbase, acol, bdesc0 + (kk >> 2) * 256 + (kk & 3) * 2, idesc, (k0 | kk) != 0 ? 1u : 0u);
             acol += 8;
-            bdesc += 64;
           }
           for (; kk < SCK / 16; kk += kMgRingK / 16) {
             if (!resident || t == 0) {
@@ -219,11 +218,12 @@ frnn_fwd_mg_kernel(const MgFwdParams p, const __grid_constant__ CUtensorMap wx_m
               tc_fence_after_sync();
             }
             uint64_t adesc = umma_smem_desc_k_sw128(smem_u32(ring + ring_stage * kMgRingBytes));
+            uint64_t bdesc = bdesc0 + (kk >> 2) * 256;
 #pragma unroll
             for (int i = 0; i < kMgRingK / 16; ++i) {
               umma_bf16_ss(tbase, adesc, bdesc, idesc, (k0 | kk | i) != 0 ? 1u : 0u);
               adesc += 2;
-              bdesc += 64;
+              bdesc += 2;
             }
             if (!resident) umma_commit(smem_u32(&s_aempty[ring_stage]));
             if (++ring_stage == NA) {
@@ -308,9 +308,6 @@ frnn_fwd_mg_kernel(const MgFwdParams p, const __grid_constant__ CUtensorMap wx_m
     const bool row_valid = tid < Cfg::ROWS;
     const uint32_t part_local = smem_u32(part) + static_cast<uint32_t>((ks * 128 + tid) * BO) * 4u;
     bool dead = false;  // after a failed wait the warp keeps walking through the loop without waiting
-    // packets this thread fetches from the local history buffer: batch row `lane`, k-groups warp + 4 j
-    constexpr int NPK = kMgSubK / 8 / 4;
-    const int prow = lane;
 
     // round_bf16(h) of the owned items -> slot `slot` of every rank's history buffer
     auto publish = [&](int slot, const uint32_t (&hb16)[NI], bool on) {
@@ -349,38 +346,10 @@ frnn_fwd_mg_kernel(const MgFwdParams p, const __grid_constant__ CUtensorMap wx_m
         }
         const long long f1 = prof ? clock64() : 0;
         if (prof) pf_free += f1 - f0;
-        const __nv_bfloat16* src = p.hbf[rank] + static_cast<size_t>(prow) * hrow + static_cast<size_t>(slot) * D +
-                                   static_cast<size_t>(ks) * Kc + sc * SCK + warp * 8;
-        uint8_t* dst = hbuf + buf * hb_bytes + warp * (BT * 16) + (prow >> 3) * 128 + (prow & 7) * 16;
-        uint32_t pend = 0;
-        if (prow < B && !dead) {
-#pragma unroll
-          for (int j = 0; j < NPK; ++j)
-            if ((warp + 4 * j) * 8 < SCK) pend |= 1u << j;
-        }
-        uint64_t t0 = 0;
-        uint32_t rounds = 0;
-        while (pend != 0u) {
-          uint4 v[NPK];
-#pragma unroll
-          for (int j = 0; j < NPK; ++j)
-            if ((pend >> j) & 1u) v[j] = ld_relaxed_sys_v4(src + j * 32);
-#pragma unroll
-          for (int j = 0; j < NPK; ++j) {
-            if (((pend >> j) & 1u) && xg_arrived(v[j])) {
-              *reinterpret_cast<uint4*>(dst + j * 4 * (BT * 16)) = v[j];
-              pend &= ~(1u << j);
-            }
-          }
-          if (pend != 0u && (++rounds & 15u) == 0u) {
-            const uint64_t now = global_timer_ns();
-            if (t0 == 0) t0 = now;
-            if (*abort_flag != 0 || now - t0 > limit) {
-              mg_report(p.err, kErrWaitH, slot);
-              dead = true;
-              break;
-            }
-          }
+        if (!dead && !mg_fetch_subchunk(p.hbf[rank] + static_cast<size_t>(slot) * D + static_cast<size_t>(ks) * Kc + sc * SCK, hrow,
+                                        hbuf + buf * hb_bytes, SCK, B, warp, lane, limit, abort_flag)) {
+          mg_report(p.err, kErrWaitH, slot);
+          dead = true;
         }
         dead = __any_sync(0xffffffffu, dead);
         fence_proxy_async_smem();
@@ -540,7 +509,7 @@ int launch_fwd_mg(const MgFwdParams& p, const void* wx, cudaStream_t stream, int
   using CT = typename Cfg::CT;
   const int Kc = p.D / KS;
   const int SCK = Kc < kMgSubK ? Kc : kMgSubK;
-  int smem = p.ring_stages * kMgRingBytes + 2 * kMgBT * SCK * 2 + 2 * Cfg::PART_BYTES + ((Cfg::PUB_BYTES + 127) & ~127) +
+  int smem = p.ring_stages * kMgRingBytes + 2 * mg_operand_bytes(SCK) + 2 * Cfg::PART_BYTES + ((Cfg::PUB_BYTES + 127) & ~127) +
              Cfg::NWX * Cfg::WX_STAGE_BYTES;
   if (smem > 227 * 1024) return -2;
   CUtensorMap wx_map, r_map;
@@ -633,7 +602,7 @@ int forward_mg_fixed_smem(int cell, int ksplit, int D, int wx_bf16) {
   const int SCK = Kc < kMgSubK ? Kc : kMgSubK;
   const int wx_stage = bo * gw * 32 * (wx_bf16 ? 2 : 4);
   const int nwx = wx_stage * 4 <= 32768 ? 4 : 2;
-  return 2 * kMgBT * SCK * 2 + 2 * (ksplit * 128 * bo * 4) + ((bo * 32 * 2 + 127) & ~127) + nwx * wx_stage;
+  return 2 * mg_operand_bytes(SCK) + 2 * (ksplit * 128 * bo * 4) + ((bo * 32 * 2 + 127) & ~127) + nwx * wx_stage;
 }
 
 }  // namespace frnn
