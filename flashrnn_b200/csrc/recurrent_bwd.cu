@@ -102,6 +102,7 @@ frnn_bwd_kernel(const BwdParams p, const __grid_constant__ CUtensorMap cache_map
   const int mute_from = p.err[4] != 0 ? p.err[5] : 0x7fffffff;
   const bool prof = p.err[3] != 0 && blockIdx.x == 0 && lane == 0 && (warp == 0 || warp == 4);
   const bool cut = p.cut_recurrent != 0;
+  const bool clip_on = p.grad_clip > 0.0f;
 
   if (tid == 0) {
     mbar_init(smem_u32(&s_part_bar[0]), 1);
@@ -305,7 +306,8 @@ frnn_bwd_kernel(const BwdParams p, const __grid_constant__ CUtensorMap cache_map
             ld_f32_vec<IPT>(q + k * sbu + ib * U + ul, dhv);
 #pragma unroll
             for (int j = 0; j < IPT; ++j) {
-              if (k == 0) dh_ext[j] = dhv[j];  // added after the recurrent part (which may be clipped) is complete
+              // with the recurrent-gradient clip the external dh is added after the carried part is complete and clipped
+              if (k == 0 && clip_on) dh_ext[j] = dhv[j];
               else ds[k][j] += dhv[j];
             }
           }
@@ -407,9 +409,10 @@ frnn_bwd_kernel(const BwdParams p, const __grid_constant__ CUtensorMap cache_map
           }
         }
       }
-      // the gradient carried into h_t from step t + 1 is complete here: clip it, then add the external one
+      if (clip_on) {  // the gradient carried into h_t from step t + 1 is complete here: clip it, then add the external one
 #pragma unroll
-      for (int j = 0; j < IPT; ++j) ds[0][j] = ((it >= 1 && it < T) ? clip_sym(ds[0][j], p.grad_clip) : ds[0][j]) + dh_ext[j];
+        for (int j = 0; j < IPT; ++j) ds[0][j] = ((it >= 1 && it < T) ? clip_sym(ds[0][j], p.grad_clip) : ds[0][j]) + dh_ext[j];
+      }
       const long long c2 = prof ? clock64() : 0;
       if (it == T) {
         if (active) {
