@@ -46,7 +46,7 @@ REFERENCE_BUDGET_S = 150.0                      # wall-clock budget of the refer
 # dram__bytes_read.sum + dram__bytes_write.sum per launch on this workload. NOT measured by this run: quoted from
 # the ncu capture summarised in the profile below (bench.py cannot run ncu on itself); re-capture when a kernel changes.
 NCU_TRAFFIC_PROFILE = "profiles/recurrence_kernels_cfg2_lstm_bf16_B8_T1024_N3_D256.md"
-NCU_TRAFFIC_BYTES = {"fwd": 52.1e6 + 109.8e6, "bwd": 204.0e6 + 74.6e6, "wgrad": 63.0e6 + 2.2e6}
+NCU_TRAFFIC_BYTES = {"fwd": 52.0e6 + 108.2e6, "bwd": 203.1e6 + 39.1e6, "wgrad": 63.0e6 + 2.2e6}
 
 
 def _peaks():
@@ -209,6 +209,8 @@ def main():
     ap.add_argument("--warmup", type=int, default=3)
     ap.add_argument("--impl", default="b200", choices=("b200", "reference"))
     ap.add_argument("--no-cpu-baseline", action="store_true")
+    ap.add_argument("--no-extras", action="store_true",
+                    help="skip the extra keys (wide head, head-sharded configuration); used for profiler runs")
     args = ap.parse_args()
     if args.impl == "reference":
         return run_reference(args)
@@ -331,8 +333,8 @@ def main():
     if dist is not None:
         breakdown["allreduce_dR_db"] = time_allreduce(dev, dist, GR * N * D * D + 4 * N * D)
     del d_wx, h_wx, dev_sets
-    wide = wide_head_sharded(dev, dist, rank, world)
-    heads = head_sharded_config(dev, dist, rank, world)
+    wide = None if args.no_extras else wide_head_sharded(dev, dist, rank, world)
+    heads = None if args.no_extras else head_sharded_config(dev, dist, rank, world)
 
     t_ms = torch.tensor([ms, ms_e2e], dtype=torch.float64, device=dev)
     if dist is not None:

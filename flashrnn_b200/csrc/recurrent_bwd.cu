@@ -52,7 +52,9 @@ __device__ __forceinline__ void report(int* err, int code, int detail) {
   __threadfence();
 }
 
-template <int CELL, int BV, int U, bool WX_BF16, bool XG>
+// OPTS: compiled with the v1 options (recurrent-gradient clip / cut, v1 sLSTM convention); the plain instantiation
+// carries none of that code on its per-step critical path.
+template <int CELL, int BV, int U, bool WX_BF16, bool XG, bool OPTS>
 __global__ void __launch_bounds__(kBwdThreads, (BV == 16 && !XG) ? 2 : 1)  // 16-row tiles are chosen when CTAs outnumber SMs: let two share one
 frnn_bwd_kernel(const BwdParams p, const __grid_constant__ CUtensorMap cache_map,
                 const __grid_constant__ CUtensorMap hist_map, const __grid_constant__ CUtensorMap init_map,
@@ -101,8 +103,8 @@ frnn_bwd_kernel(const BwdParams p, const __grid_constant__ CUtensorMap cache_map
   // test hook: with err[4] = 1 no CTA scatters partial dh from iteration err[5] on, so the next wait runs out
   const int mute_from = p.err[4] != 0 ? p.err[5] : 0x7fffffff;
   const bool prof = p.err[3] != 0 && blockIdx.x == 0 && lane == 0 && (warp == 0 || warp == 4);
-  const bool cut = p.cut_recurrent != 0;
-  const bool clip_on = p.grad_clip > 0.0f;
+  const bool cut = OPTS && p.cut_recurrent != 0;
+  const bool clip_on = OPTS && p.grad_clip > 0.0f;
 
   if (tid == 0) {
     mbar_init(smem_u32(&s_part_bar[0]), 1);
@@ -306,9 +308,8 @@ frnn_bwd_kernel(const BwdParams p, const __grid_constant__ CUtensorMap cache_map
             ld_f32_vec<IPT>(q + k * sbu + ib * U + ul, dhv);
 #pragma unroll
             for (int j = 0; j < IPT; ++j) {
-              // with the recurrent-gradient clip the external dh is added after the carried part is complete and clipped
-              if (k == 0 && clip_on) dh_ext[j] = dhv[j];
-              else ds[k][j] += dhv[j];
+              ds[k][j] += dhv[j];
+              if (k == 0 && clip_on) dh_ext[j] = dhv[j];  // kept aside: only the carried part is clipped below
             }
           }
         }
@@ -409,9 +410,10 @@ frnn_bwd_kernel(const BwdParams p, const __grid_constant__ CUtensorMap cache_map
           }
         }
       }
-      if (clip_on) {  // the gradient carried into h_t from step t + 1 is complete here: clip it, then add the external one
+      if (clip_on && it >= 1 && it < T) {
+        // the gradient carried into h_t from step t + 1 (total minus the external part) is complete here: clip it
 #pragma unroll
-        for (int j = 0; j < IPT; ++j) ds[0][j] = ((it >= 1 && it < T) ? clip_sym(ds[0][j], p.grad_clip) : ds[0][j]) + dh_ext[j];
+        for (int j = 0; j < IPT; ++j) ds[0][j] = clip_sym(ds[0][j] - dh_ext[j], p.grad_clip) + dh_ext[j];
       }
       const long long c2 = prof ? clock64() : 0;
       if (it == T) {
@@ -433,7 +435,7 @@ frnn_bwd_kernel(const BwdParams p, const __grid_constant__ CUtensorMap cache_map
           for (int g = 0; g < GCL; ++g) cj[g] = cache[g][j];
 #pragma unroll
           for (int q = 0; q < S; ++q) { snj[q] = sn[q][j]; spj[q] = sp[q][j]; dsj[q] = ds[q][j]; }
-          cell_backward<CELL>(cj, spj, snj, dsj, gr, gw, gb, take_i, p.slstm_v1 != 0);
+          cell_backward<CELL>(cj, spj, snj, dsj, gr, gw, gb, take_i, OPTS && p.slstm_v1 != 0);
 #pragma unroll
           for (int q = 0; q < S; ++q) dcar[q][j] = dsj[q];
 #pragma unroll
@@ -591,7 +593,7 @@ frnn_bwd_kernel(const BwdParams p, const __grid_constant__ CUtensorMap cache_map
   if (warp == 4) tmem_dealloc(tbase, tmem_cols);
 }
 
-template <int CELL, int BV, int U, bool WX_BF16, bool XG>
+template <int CELL, int BV, int U, bool WX_BF16, bool XG, bool OPTS>
 int launch_bwd(const BwdParams& p, const float* cache, const float* history, const float* initial,
                const float* d_history, cudaStream_t stream) {
   using Cfg = BwdCfg<CELL, BV, U, WX_BF16>;
@@ -622,7 +624,7 @@ int launch_bwd(const BwdParams& p, const float* cache, const float* history, con
     const uint64_t dims1[5] = {uD, uN, 1u, uB, static_cast<uint64_t>(CT::S)};
     if (make_tensor_map(&init_map, initial, 4, 5, dims1, box) != 0) return -4;
   }
-  auto kern = frnn_bwd_kernel<CELL, BV, U, WX_BF16, XG>;
+  auto kern = frnn_bwd_kernel<CELL, BV, U, WX_BF16, XG, OPTS>;
   const int fit = fit_tmem_budget(
       kern, kBwdThreads, tmem_cols_pow2(((MTB * Cfg::BT + 31) / 32 * 32) + MTB * (Cfg::ROWS / 2), 32u), &smem);
   if (fit != 0) return fit;
@@ -664,11 +666,19 @@ int launch_bwd(const BwdParams& p, const float* cache, const float* history, con
 template <int CELL, int BV, int U>
 int launch_bwd_dt(const BwdParams& p, const float* cache, const float* history, const float* initial,
                   const float* d_history, int wx_bf16, cudaStream_t s) {
-  if (p.xg_data != nullptr)  // groups wider than a cluster exchange through global memory
-    return wx_bf16 ? launch_bwd<CELL, BV, U, true, true>(p, cache, history, initial, d_history, s)
-                   : launch_bwd<CELL, BV, U, false, true>(p, cache, history, initial, d_history, s);
-  return wx_bf16 ? launch_bwd<CELL, BV, U, true, false>(p, cache, history, initial, d_history, s)
-                 : launch_bwd<CELL, BV, U, false, false>(p, cache, history, initial, d_history, s);
+  const bool opts = p.grad_clip > 0.0f || p.cut_recurrent != 0 || p.slstm_v1 != 0;
+  if (p.xg_data != nullptr) {  // groups wider than a cluster exchange through global memory
+    if (opts)
+      return wx_bf16 ? launch_bwd<CELL, BV, U, true, true, true>(p, cache, history, initial, d_history, s)
+                     : launch_bwd<CELL, BV, U, false, true, true>(p, cache, history, initial, d_history, s);
+    return wx_bf16 ? launch_bwd<CELL, BV, U, true, true, false>(p, cache, history, initial, d_history, s)
+                   : launch_bwd<CELL, BV, U, false, true, false>(p, cache, history, initial, d_history, s);
+  }
+  if (opts)
+    return wx_bf16 ? launch_bwd<CELL, BV, U, true, false, true>(p, cache, history, initial, d_history, s)
+                   : launch_bwd<CELL, BV, U, false, false, true>(p, cache, history, initial, d_history, s);
+  return wx_bf16 ? launch_bwd<CELL, BV, U, true, false, false>(p, cache, history, initial, d_history, s)
+                 : launch_bwd<CELL, BV, U, false, false, false>(p, cache, history, initial, d_history, s);
 }
 template <int CELL>
 int launch_bwd_cell(const BwdParams& p, const float* cache, const float* history, const float* initial,

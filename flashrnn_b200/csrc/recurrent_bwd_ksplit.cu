@@ -317,7 +317,7 @@ frnn_bwd_ks_kernel(const BwdParams p, const __grid_constant__ CUtensorMap cache_
 #pragma unroll
       for (int j = 0; j < NI; ++j)
 #pragma unroll
-        for (int q = 0; q < S; ++q) ds[j][q] = dcar[j][q] + ((it < T && (q > 0 || !clip_on)) ? dhs[j][q] : 0.0f);
+        for (int q = 0; q < S; ++q) ds[j][q] = dcar[j][q] + (it < T ? dhs[j][q] : 0.0f);
       if (it >= 1) {
         // partial dh of this step from the KS CTAs of the cluster
         if (!dead && !mbar_wait_bounded<true, false>(smem_u32(&s_part_bar[pb]), ((it - 1) >> 1) & 1, limit, abort_flag)) {
@@ -337,10 +337,10 @@ frnn_bwd_ks_kernel(const BwdParams p, const __grid_constant__ CUtensorMap cache_
         // whose phase has completed may be armed again, hence not after a failed wait)
         if (tid == 0 && !dead && it + 2 <= T) mbar_arrive_expect_tx(smem_u32(&s_part_bar[pb]), part_tx);
       }
-      if (clip_on) {  // the gradient carried into h_t from step t + 1 is complete here: clip it, then add the external one
+      if (clip_on && it >= 1 && it < T) {
+        // the gradient carried into h_t from step t + 1 (total minus the external part) is complete here: clip it
 #pragma unroll
-        for (int j = 0; j < NI; ++j)
-          ds[j][0] = ((it >= 1 && it < T) ? clip_sym(ds[j][0], p.grad_clip) : ds[j][0]) + (it < T ? dhs[j][0] : 0.0f);
+        for (int j = 0; j < NI; ++j) ds[j][0] = clip_sym(ds[j][0] - dhs[j][0], p.grad_clip) + dhs[j][0];
       }
       const long long c1 = prof ? clock64() : 0;
       if (it == T) {

@@ -157,11 +157,6 @@ __global__ void __launch_bounds__(kThreads, 1) wgrad_kernel(const WgradParams p)
 constexpr int kTmaThreads = 192;
 constexpr int kTmaStages = 4;
 
-// CLUSTER: the `ksplit` CTAs that share an output tile (grid z) form a thread-block cluster and add their partial
-// tiles through distributed shared memory instead of a scratch round trip and a second kernel: CTA j owns a
-// contiguous range of 8-column groups, every CTA sends that range of its accumulator to it with asynchronous stores
-// (into the idle pipeline stages), and the owner adds the ksplit slabs in a fixed order and writes dR.
-template <bool CLUSTER>
 __global__ void __launch_bounds__(kTmaThreads, 1)
 wgrad_tma_kernel(const WgradParams p, const __grid_constant__ CUtensorMap dgr_map,
                  const __grid_constant__ CUtensorMap hbf_map) {
@@ -169,7 +164,6 @@ wgrad_tma_kernel(const WgradParams p, const __grid_constant__ CUtensorMap dgr_ma
   __shared__ __align__(8) uint64_t s_full[kTmaStages];
   __shared__ __align__(8) uint64_t s_empty[kTmaStages];
   __shared__ __align__(8) uint64_t s_acc;
-  __shared__ __align__(8) uint64_t s_red;
   __shared__ uint32_t s_tmem_base;
   const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
   const int D = p.D, T = p.T, GR = p.GR, NP = p.NP;
@@ -201,13 +195,6 @@ wgrad_tma_kernel(const WgradParams p, const __grid_constant__ CUtensorMap dgr_ma
       mbar_init(smem_u32(&s_empty[s]), 1);
     }
     mbar_init(smem_u32(&s_acc), 1);
-    mbar_init(smem_u32(&s_red), 1);
-    if (CLUSTER) {
-      // bytes this CTA will receive: its column range of the 128-row tile from every CTA of the cluster
-      const int ks = p.ksplit, ng = NP / 8;
-      const int g0 = split * ng / ks, g1 = (split + 1) * ng / ks;
-      mbar_arrive_expect_tx(smem_u32(&s_red), static_cast<uint32_t>(ks) * 128u * static_cast<uint32_t>(g1 - g0) * 32u);
-    }
     fence_mbar_init();
   }
   if (warp == 1) {
@@ -285,9 +272,7 @@ wgrad_tma_kernel(const WgradParams p, const __grid_constant__ CUtensorMap dgr_ma
       have = false;
     }
     tc_fence_after_sync();
-    if (CLUSTER) {
-      // the tile is combined after the cluster barrier below
-    } else if (pack == 1) {
+    if (pack == 1) {
       float* dst = nullptr;
       if (m < M) {
         const int g = m / Dm, o = m % Dm;
@@ -334,50 +319,6 @@ wgrad_tma_kernel(const WgradParams p, const __grid_constant__ CUtensorMap dgr_ma
   }
   tc_fence_before_sync();
   __syncthreads();
-  if (CLUSTER) {
-    // every CTA of the cluster has finished its main loop: the pipeline stages are free to receive the slabs
-    cluster_sync_all();
-    tc_fence_after_sync();
-    const int ks = p.ksplit, ng = NP / 8;
-    if (warp >= 2) {
-      const int q = warp & 3, row = 32 * q + lane;
-      const bool have = n_chunks > 0 && *abort_flag == 0;
-      for (int j = 0; j < ks; ++j) {
-        const int g0 = j * ng / ks, g1 = (j + 1) * ng / ks, ncols = (g1 - g0) * 8;
-        // slab of this CTA inside owner j: [source][row][its columns], fp32
-        const uint32_t slab = map_to_cta(base + static_cast<uint32_t>((split * 128 + row) * ncols) * 4u, j);
-        const uint32_t bar = map_to_cta(smem_u32(&s_red), j);
-        for (int g = g0; g < g1; ++g) {
-          uint32_t r[8] = {0u, 0u, 0u, 0u, 0u, 0u, 0u, 0u};
-          if (have) {
-            tmem_ld_x8(tmem_addr(tbase, 32 * q, g * 8), r);
-            tmem_ld_wait();
-          }
-          st_async_v4_b32(slab + (g - g0) * 32, r[0], r[1], r[2], r[3], bar);
-          st_async_v4_b32(slab + (g - g0) * 32 + 16, r[4], r[5], r[6], r[7], bar);
-        }
-      }
-      const int g0 = split * ng / ks, g1 = (split + 1) * ng / ks, ncols = (g1 - g0) * 8;
-      if (!mbar_wait_bounded<true, true>(smem_u32(&s_red), 0, kLimit, abort_flag)) atomicCAS(p.err, 0, kErrWaitPart);
-      const int m = m0 + row;
-      if (m < M && ncols > 0 && *abort_flag == 0) {
-        const int g = m / Dm, o = m % Dm;
-        float* dst = p.out + ((static_cast<size_t>(g) * p.N + n) * p.out_rows + o) * D + p0 + g0 * 8;
-        const float* mine = reinterpret_cast<const float*>(smem_raw + (base - smem_u32(smem_raw))) + row * ncols;
-        for (int c = 0; c < ncols; c += 4) {
-          float4 acc = *reinterpret_cast<const float4*>(mine + c);
-          for (int src = 1; src < ks; ++src) {
-            const float4 v = *reinterpret_cast<const float4*>(mine + static_cast<size_t>(src) * 128 * ncols + c);
-            acc.x += v.x; acc.y += v.y; acc.z += v.z; acc.w += v.w;
-          }
-          *reinterpret_cast<float4*>(dst + c) = acc;
-        }
-      }
-    }
-    tc_fence_before_sync();
-    __syncthreads();
-    cluster_sync_all();  // nobody leaves while a partner may still read or write its shared memory
-  }
   if (warp == 1) tmem_dealloc(tbase, tmem_cols);
 }
 
@@ -441,8 +382,7 @@ int wgrad_launch(int gr, int gb, const __nv_bfloat16* dgr, const __nv_bfloat16* 
                  float* dR, float* db, float* work, int* err, int B, int T, int N, int D, cudaStream_t s) {
   int np, ksplit, cps;
   if (wgrad_plan(gr, B, T, N, D, &np, &ksplit, &cps) != 0) return -2;
-  const bool can_cluster = wgrad_pack(D) == 1 && wgrad_uses_tma(D, np) && ksplit > 1 && ksplit <= 8;
-  if (ksplit > 1 && work == nullptr && !can_cluster) return -5;
+  if (ksplit > 1 && work == nullptr) return -5;
   WgradParams p{};
   p.dgr = dgr; p.hbf = hbf;
   p.out = ksplit > 1 ? work : dR;
@@ -452,7 +392,6 @@ int wgrad_launch(int gr, int gb, const __nv_bfloat16* dgr, const __nv_bfloat16* 
   p.Dm = D; p.m_off = 0; p.out_rows = D;
   const int pack = wgrad_pack(D);
   p.pack = pack;
-  bool clustered = false;
   const int mtiles = pack > 1 ? (gr + 1) / 2 : (gr * D + 127) / 128;
   dim3 grid(static_cast<unsigned>(pack > 1 ? mtiles : mtiles * (D / np)),
             static_cast<unsigned>(pack > 1 ? (N + pack - 1) / pack : N), static_cast<unsigned>(ksplit));
@@ -467,9 +406,9 @@ int wgrad_launch(int gr, int gb, const __nv_bfloat16* dgr, const __nv_bfloat16* 
     if (make_tensor_map(&dgr_map, dgr, 2, 4, ddims, dbox, true) != 0) return -4;
     if (make_tensor_map(&hbf_map, hbf, 2, 3, hdims, hbox, true) != 0) return -4;
     const int smem = kTmaStages * (16384 + 64 * 128) + 1024;
-    e = cudaFuncSetAttribute(wgrad_tma_kernel<false>, cudaFuncAttributeMaxDynamicSharedMemorySize, smem);
+    e = cudaFuncSetAttribute(wgrad_tma_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, smem);
     if (e != cudaSuccess) return static_cast<int>(e);
-    wgrad_tma_kernel<false><<<grid, kTmaThreads, smem, s>>>(p, dgr_map, hbf_map);
+    wgrad_tma_kernel<<<grid, kTmaThreads, smem, s>>>(p, dgr_map, hbf_map);
   } else if (wgrad_uses_tma(D, np)) {
     CUtensorMap dgr_map, hbf_map;
     const uint64_t ddims[5] = {static_cast<uint64_t>(D), static_cast<uint64_t>(N), static_cast<uint64_t>(gr),
@@ -481,31 +420,9 @@ int wgrad_launch(int gr, int gb, const __nv_bfloat16* dgr, const __nv_bfloat16* 
     if (make_tensor_map(&dgr_map, dgr, 2, 5, ddims, dbox, true) != 0) return -4;
     if (make_tensor_map(&hbf_map, hbf, 2, 4, hdims, hbox, true) != 0) return -4;
     const int smem = kTmaStages * (16384 + np * 128) + 1024;
-    if (can_cluster) {
-      // the split-K partners of a tile add their partial tiles inside a thread-block cluster: no scratch, one kernel
-      clustered = true;
-      p.out = dR;
-      e = cudaFuncSetAttribute(wgrad_tma_kernel<true>, cudaFuncAttributeMaxDynamicSharedMemorySize, smem);
-      if (e != cudaSuccess) return static_cast<int>(e);
-      cudaLaunchConfig_t cfg = {};
-      cfg.gridDim = grid;
-      cfg.blockDim = dim3(kTmaThreads);
-      cfg.dynamicSmemBytes = smem;
-      cfg.stream = s;
-      cudaLaunchAttribute attr[1];
-      attr[0].id = cudaLaunchAttributeClusterDimension;
-      attr[0].val.clusterDim.x = 1;
-      attr[0].val.clusterDim.y = 1;
-      attr[0].val.clusterDim.z = static_cast<unsigned>(ksplit);
-      cfg.attrs = attr;
-      cfg.numAttrs = 1;
-      e = cudaLaunchKernelEx(&cfg, wgrad_tma_kernel<true>, p, dgr_map, hbf_map);
-      if (e != cudaSuccess) return static_cast<int>(e);
-    } else {
-      e = cudaFuncSetAttribute(wgrad_tma_kernel<false>, cudaFuncAttributeMaxDynamicSharedMemorySize, smem);
-      if (e != cudaSuccess) return static_cast<int>(e);
-      wgrad_tma_kernel<false><<<grid, kTmaThreads, smem, s>>>(p, dgr_map, hbf_map);
-    }
+    e = cudaFuncSetAttribute(wgrad_tma_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, smem);
+    if (e != cudaSuccess) return static_cast<int>(e);
+    wgrad_tma_kernel<<<grid, kTmaThreads, smem, s>>>(p, dgr_map, hbf_map);
   } else {
     const int smem = 16 * 1024 + (np / 8) * 1024;
     e = cudaFuncSetAttribute(wgrad_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, smem);
@@ -515,7 +432,7 @@ int wgrad_launch(int gr, int gb, const __nv_bfloat16* dgr, const __nv_bfloat16* 
   e = cudaGetLastError();
   if (e != cudaSuccess) return static_cast<int>(e);
   const long long nR = static_cast<long long>(gr) * N * D * D;
-  if (ksplit > 1 && !clustered) {
+  if (ksplit > 1) {
     reduce_parts_kernel<<<static_cast<unsigned>((nR / 4 + 255) / 256), 256, 0, s>>>(work, dR, nR, ksplit);
     e = cudaGetLastError();
     if (e != cudaSuccess) return static_cast<int>(e);
@@ -550,10 +467,10 @@ int wgrad_launch_rows(int gr, int gb, const __nv_bfloat16* dgr, const __nv_bfloa
   if (make_tensor_map(&dgr_map, dgr, 2, 5, ddims, dbox, true) != 0) return -4;
   if (make_tensor_map(&hbf_map, hbf, 2, 4, hdims, hbox, true, hstride) != 0) return -4;
   const int smem = kTmaStages * (16384 + 256 * 128) + 1024;
-  cudaError_t e = cudaFuncSetAttribute(wgrad_tma_kernel<false>, cudaFuncAttributeMaxDynamicSharedMemorySize, smem);
+  cudaError_t e = cudaFuncSetAttribute(wgrad_tma_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, smem);
   if (e != cudaSuccess) return static_cast<int>(e);
   dim3 grid(static_cast<unsigned>((gr * Dm / 128) * (D / 256)), 1u, 1u);
-  wgrad_tma_kernel<false><<<grid, kTmaThreads, smem, s>>>(p, dgr_map, hbf_map);
+  wgrad_tma_kernel<<<grid, kTmaThreads, smem, s>>>(p, dgr_map, hbf_map);
   e = cudaGetLastError();
   if (e != cudaSuccess) return static_cast<int>(e);
   // db: the window of every gate row is reduced separately (the rows are ldb apart)
