@@ -490,7 +490,7 @@ def kernel_breakdown(_lib, dev, d_wx, d_R, d_b, d_init, flush, reps):
     f32, bf = torch.float32, torch.bfloat16
     history = torch.empty((S, B, T, N, D), dtype=f32, device=dev)
     carry = torch.empty((S, B, 1, N, D), dtype=f32, device=dev)
-    cache = torch.empty(plan.cache_bytes // 4, dtype=f32, device=dev)
+    cache = torch.empty(plan.cache_bytes, dtype=torch.uint8, device=dev)
     hbf = torch.empty(plan.hbf_bytes // 2, dtype=bf, device=dev)
     d_history = torch.zeros_like(history)
     d_history[0] = 1.0

@@ -37,13 +37,14 @@ def time_shape(cell: str, B: int, T: int, N: int, D: int, reps: int = 5, device:
     b, init = b.to(dev), init.to(dev)
     hist = torch.empty((S, B, T, N, D), dtype=f32, device=dev)
     carry = torch.empty((S, B, 1, N, D), dtype=f32, device=dev)
-    cache = torch.empty(max(plan.cache_bytes // 4, 1), dtype=f32, device=dev)
+    cache = torch.empty(max(plan.cache_bytes, 1), dtype=torch.uint8, device=dev)
     hbf = torch.empty(plan.hbf_bytes // 2, dtype=bf, device=dev)
     d_hist = torch.zeros_like(hist)
     d_hist[0] = 1.0
     d_carry = torch.zeros_like(carry)
     dwx = torch.empty_like(wx)
-    dgr = torch.empty(plan.dgr_bytes // 2, dtype=bf, device=dev)
+    # bf16 Wx and W-gates == R-gates: one buffer serves as dWx and as the operand of the dR contraction (as functional.py does)
+    dgr = dwx if cell != "gru" else torch.empty(plan.dgr_bytes // 2, dtype=bf, device=dev)
     d_init = torch.empty_like(carry)
     db_part = torch.empty(plan.dbpart_bytes // 4, dtype=f32, device=dev)
     dR = torch.empty((gr, N, D, D), dtype=f32, device=dev)

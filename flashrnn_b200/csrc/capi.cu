@@ -13,10 +13,10 @@ int forward_ksplit_dispatch(int cell, const FwdParams& p, const void* wx, int wx
 int forward_ksplit_capacity(int cell, int bv, int ksplit, int D);
 int backward_ksplit_width(int gates_r, int D);
 bool backward_ksplit_valid(int cell, int gates_r, int D, int ks);
-int backward_ksplit_dispatch(int cell, const BwdParams& p, const float* cache, const float* history, const float* initial,
+int backward_ksplit_dispatch(int cell, const BwdParams& p, const void* cache, const float* history, const float* initial,
                              const float* d_history, int wx_bf16, int bv, int ksplit, cudaStream_t s, int* capacity_only);
 int backward_ksplit_capacity(int cell, int bv, int ksplit, int D);
-int backward_dispatch(int cell, const BwdParams& p, const float* cache, const float* history, const float* initial,
+int backward_dispatch(int cell, const BwdParams& p, const void* cache, const float* history, const float* initial,
                       const float* d_history, int wx_bf16, int bv, int unit, cudaStream_t s);
 int wgrad_plan(int gr, int B, int T, int N, int D, int* np_out, int* ksplit_out, int* cps_out);
 int wgrad_launch(int gr, int gb, const __nv_bfloat16* dgr, const __nv_bfloat16* hbf, const float* db_part, int n_btiles,
@@ -228,7 +228,7 @@ extern "C" int frnn_b200_plan(int cell, int B, int T, int N, int D, frnn_b200_pl
     out->xchg_bytes = fwd_groups * fwd_b > bwd_groups * bwd_b ? fwd_groups * fwd_b : bwd_groups * bwd_b;
   }
   const int64_t btnd = static_cast<int64_t>(B) * T * N * D;
-  out->cache_bytes = btnd * c.gc * 4;
+  out->cache_bytes = btnd * c.gc * ((cell == kLSTM || cell == kGRU) ? 2 : 4);  // CellTraits::CES
   out->hbf_bytes = static_cast<int64_t>(B) * (T + 1) * N * D * 2;
   out->dgr_bytes = btnd * c.gr * 2;
   out->dbpart_bytes = static_cast<int64_t>(out->n_btiles) * c.gb * N * D * 4;
@@ -245,7 +245,7 @@ extern "C" int frnn_b200_plan(int cell, int B, int T, int N, int D, frnn_b200_pl
 namespace {
 
 int forward_common(int cell, const void* wx, int wx_bf16, const void* r_bf16, const float* bias, const float* initial,
-                   float* history, float* carry, float* cache, void* hbf, void* xchg, int B, int T, int N, int D,
+                   float* history, float* carry, void* cache, void* hbf, void* xchg, int B, int T, int N, int D,
                    int slstm_zero_first, const int* zero_first_dev, int output_mode, int wait_limit_ms, int* err,
                    void* stream, int T_total = 0, int t0 = 0, int out_bf16 = 0, const frnn_b200_options_t* opt = nullptr) {
   frnn_b200_plan_t plan;
@@ -291,7 +291,7 @@ int forward_common(int cell, const void* wx, int wx_bf16, const void* r_bf16, co
 }  // namespace
 
 extern "C" int frnn_b200_forward(int cell, const void* wx, int wx_bf16, const void* r_bf16, const float* bias,
-                                 const float* initial, float* history, float* carry, float* cache, void* hbf,
+                                 const float* initial, float* history, float* carry, void* cache, void* hbf,
                                  void* xchg, int B, int T, int N, int D, int slstm_zero_first, int wait_limit_ms,
                                  int* err, void* stream) {
   return forward_common(cell, wx, wx_bf16, r_bf16, bias, initial, history, carry, cache, hbf, xchg, B, T, N, D,
@@ -299,7 +299,7 @@ extern "C" int frnn_b200_forward(int cell, const void* wx, int wx_bf16, const vo
 }
 
 extern "C" int frnn_b200_forward_ex(int cell, const void* wx, int wx_bf16, const void* r_bf16, const float* bias,
-                                    const float* initial, float* history, float* carry, float* cache, void* hbf,
+                                    const float* initial, float* history, float* carry, void* cache, void* hbf,
                                     void* xchg, int B, int T, int N, int D, int slstm_zero_first, int wait_limit_ms,
                                     int* err, void* stream, const frnn_b200_options_t* options) {
   return forward_common(cell, wx, wx_bf16, r_bf16, bias, initial, history, carry, cache, hbf, xchg, B, T, N, D,
@@ -325,7 +325,7 @@ extern "C" int frnn_b200_forward_chunk(int cell, const void* wx, int wx_bf16, co
                         stream, T_total, t_start, output_bf16 != 0);
 }
 
-extern "C" int frnn_b200_backward(int cell, const float* cache, const float* history, const float* initial,
+extern "C" int frnn_b200_backward(int cell, const void* cache, const float* history, const float* initial,
                                   const void* r_bf16, const float* d_history, const float* d_carry, void* dwx,
                                   int wx_bf16, void* dgr, float* d_initial, float* db_part, void* xchg, int B, int T,
                                   int N, int D, int slstm_zero_first, int wait_limit_ms, int* err, void* stream) {
@@ -333,7 +333,7 @@ extern "C" int frnn_b200_backward(int cell, const float* cache, const float* his
                                db_part, xchg, B, T, N, D, slstm_zero_first, wait_limit_ms, err, stream, nullptr);
 }
 
-extern "C" int frnn_b200_backward_ex(int cell, const float* cache, const float* history, const float* initial,
+extern "C" int frnn_b200_backward_ex(int cell, const void* cache, const float* history, const float* initial,
                                      const void* r_bf16, const float* d_history, const float* d_carry, void* dwx,
                                      int wx_bf16, void* dgr, float* d_initial, float* db_part, void* xchg, int B, int T,
                                      int N, int D, int slstm_zero_first, int wait_limit_ms, int* err, void* stream,

@@ -118,7 +118,7 @@ extern "C" int frnn_b200_mg_plan(int cell, int B, int T, int D, int wx_bf16, con
   out->hbf_bytes = static_cast<int64_t>(B) * (T + 1) * D * 2;
   out->dgr_bytes = static_cast<int64_t>(B) * T * c.gr * D * 2;
   const int64_t lw = here == P ? D : Dl;  // row length of the local tensors of one launch
-  out->cache_bytes = static_cast<int64_t>(B) * T * c.gc * lw * 4;
+  out->cache_bytes = static_cast<int64_t>(B) * T * c.gc * lw * ((cell == kLSTM || cell == kGRU) ? 2 : 4);  // CellTraits::CES
   out->r_cols_bytes = static_cast<int64_t>(c.gr) * D * lw * 2;
   if (B > kMgBT || D % 256 != 0 || Dl % 128 != 0) return 0;  // supported stays 0
   // forward: the widest split of the contraction whose CTAs are all resident (shortest tensor-core chain per step)
@@ -156,7 +156,7 @@ extern "C" int frnn_b200_mg_capacity(int cell, int forward, int ksplit, int D, i
 }
 
 extern "C" int frnn_b200_mg_forward(int cell, const void* wx, int wx_bf16, const void* r_rows, const float* bias,
-                                    const float* initial, float* history, float* carry, float* cache,
+                                    const float* initial, float* history, float* carry, void* cache,
                                     const frnn_b200_mg_shard_t* sh, int B, int T, int D, int slstm_zero_first,
                                     int wait_limit_ms, int* err, void* stream) {
   frnn_b200_mg_plan_t plan;
@@ -201,7 +201,7 @@ extern "C" int frnn_b200_mg_gather_columns(int cell, const void* const* r_rows_a
                                static_cast<cudaStream_t>(stream));
 }
 
-extern "C" int frnn_b200_mg_backward(int cell, const float* cache, const float* history, const float* initial,
+extern "C" int frnn_b200_mg_backward(int cell, const void* cache, const float* history, const float* initial,
                                      const void* r_cols, const float* d_history, const float* d_carry, void* dwx,
                                      int wx_bf16, float* d_initial, float* db_part, const frnn_b200_mg_shard_t* sh, int B,
                                      int T, int D, int slstm_zero_first, int wait_limit_ms, int* err, void* stream) {

@@ -15,10 +15,14 @@ enum : int { kLSTM = 0, kSLSTM = 1, kGRU = 2, kElman = 3 };
 // GR: gates fed by R*h, GW: gates in Wx, GB: bias gates, S: states, GC: values cached per
 // (batch, step, unit) by a training forward for the backward pass.
 template <int CELL> struct CellTraits;
-template <> struct CellTraits<kLSTM>  { static constexpr int GR = 4, GW = 4, GB = 4, S = 2, GC = 4; };
-template <> struct CellTraits<kSLSTM> { static constexpr int GR = 4, GW = 4, GB = 4, S = 4, GC = 4; };
-template <> struct CellTraits<kGRU>   { static constexpr int GR = 3, GW = 3, GB = 4, S = 1, GC = 4; };
-template <> struct CellTraits<kElman> { static constexpr int GR = 1, GW = 1, GB = 1, S = 1, GC = 1; };
+// CES: bytes per cached value. LSTM and GRU cache activations in [-1, 1] (and the GRU's O(1) candidate pre-activation):
+// fp16 keeps 11 significant bits of them, which moves no gradient by more than a few 1e-4 of its scale (the bf16
+// tensor-core operands cost ten times that) and halves the largest stream of a training step. The sLSTM caches raw
+// pre-activations that go through exp(): fp32.
+template <> struct CellTraits<kLSTM>  { static constexpr int GR = 4, GW = 4, GB = 4, S = 2, GC = 4, CES = 2; };
+template <> struct CellTraits<kSLSTM> { static constexpr int GR = 4, GW = 4, GB = 4, S = 4, GC = 4, CES = 4; };
+template <> struct CellTraits<kGRU>   { static constexpr int GR = 3, GW = 3, GB = 4, S = 1, GC = 4, CES = 2; };
+template <> struct CellTraits<kElman> { static constexpr int GR = 1, GW = 1, GB = 1, S = 1, GC = 1, CES = 4; };
 
 // MUFU-based primitives: ex2.approx / rcp.approx are accurate to about 2 ulp, far inside the
 // tolerance of a bf16-operand recurrence, and take one instruction each where the IEEE-rounded

@@ -4,6 +4,7 @@
 
 #include <cuda.h>
 #include <cuda_bf16.h>
+#include <cuda_fp16.h>
 #include <cuda_runtime.h>
 #include <stdint.h>
 
@@ -31,7 +32,7 @@ struct FwdParams {
   const float* initial;    // [S][B][1][N][D]
   float* history;          // [S][B][T][N][D]
   float* carry;            // [S][B][1][N][D]
-  float* cache;            // [B][T][GC][N][D] or null (inference)
+  void* cache;             // [B][T][GC][N][D] (fp16 or fp32 elements, CellTraits::CES) or null (inference)
   __nv_bfloat16* hbf;      // [B][T+1][N][D] bf16 copy of h_{-1..T-1}, or null
   int* err;                // device int[4]
   int B, T, N, D;
@@ -111,6 +112,43 @@ __device__ __forceinline__ void st_f32_vec(float* p, const float* v) {
     for (int i = 0; i < N; ++i) p[i] = v[i];
   }
 }
+// Gate-cache accessors: fp32 or fp16 elements (CES = 4 / 2 bytes, see CellTraits), `off` in elements.
+template <int N, int CES>
+__device__ __forceinline__ void st_cache_vec(void* base, size_t off, const float* v) {
+  if constexpr (CES == 4) {
+    st_f32_vec<N>(static_cast<float*>(base) + off, v);
+  } else {
+    static_assert(N % 2 == 0, "pairs");
+    __half* p = static_cast<__half*>(base) + off;
+#pragma unroll
+    for (int i = 0; i < N; i += 2) *reinterpret_cast<__half2*>(p + i) = __floats2half2_rn(v[i], v[i + 1]);
+  }
+}
+template <int N, int CES>
+__device__ __forceinline__ void ld_cache_vec(const void* base, size_t off, float* v) {
+  if constexpr (CES == 4) {
+    ld_f32_vec<N>(static_cast<const float*>(base) + off, v);
+  } else {
+    static_assert(N % 2 == 0, "pairs");
+    const __half* p = static_cast<const __half*>(base) + off;
+#pragma unroll
+    for (int i = 0; i < N; i += 2) {
+      const float2 t = __half22float2(*reinterpret_cast<const __half2*>(p + i));
+      v[i] = t.x; v[i + 1] = t.y;
+    }
+  }
+}
+template <int CES>
+__device__ __forceinline__ void st_cache(void* base, size_t off, float v) {
+  if constexpr (CES == 4) static_cast<float*>(base)[off] = v;
+  else static_cast<__half*>(base)[off] = __float2half_rn(v);
+}
+template <int CES>
+__device__ __forceinline__ float ld_cache(const void* base, size_t off) {
+  if constexpr (CES == 4) return static_cast<const float*>(base)[off];
+  else return __half2float(static_cast<const __half*>(base)[off]);
+}
+
 template <int N>
 __device__ __forceinline__ void st_bf16_vec(__nv_bfloat16* p, const float* v) {
   static_assert(N % 2 == 0, "pairs");

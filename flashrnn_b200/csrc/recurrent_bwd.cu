@@ -31,8 +31,9 @@ struct BwdCfg {
   static constexpr int IPT = (U * BV / kEpiThreads) < 2 ? 2 : (U * BV / kEpiThreads);
   static constexpr int TPB = U / IPT;
   static constexpr int GCL = CELL == kElman ? 0 : CT::GC;  // cached gates actually loaded
-  static constexpr int STAGE_FLOATS = (GCL + 3 * CT::S) * BV * U;
-  static constexpr int STAGE_BYTES = STAGE_FLOATS * 4;
+  static constexpr int CACHE_BYTES = GCL * BV * U * CT::CES;  // the cached gates come first in a stage
+  static constexpr int STAGE_BYTES = CACHE_BYTES + 3 * CT::S * BV * U * 4;
+  static_assert(CACHE_BYTES % 128 == 0, "TMA destinations after the cached gates stay 128-byte aligned");
   // TMA ring depth: four stages unless a stage is so large (wide batch tiles, many states) that fewer
   // fit. 16-row tiles run where CTAs outnumber SMs, so their ring stays below 80 KB and two CTAs
   // share one SM's shared memory.
@@ -234,7 +235,7 @@ frnn_bwd_kernel(const BwdParams p, const __grid_constant__ CUtensorMap cache_map
     }
   } else if (warp == 5) {
     if (lane == 0) {
-      const uint32_t stage_tx = static_cast<uint32_t>(p.box_b) * U * 4u * (GCL + 3 * S);
+      const uint32_t stage_tx = static_cast<uint32_t>(p.box_b) * U * (GCL * CT::CES + 3 * S * 4);
       const int sbu = p.box_b * U;  // floats per state plane in a stage
       for (int it = 0; it < T; ++it) {
         const int s = it % Cfg::NST;
@@ -251,10 +252,10 @@ frnn_bwd_kernel(const BwdParams p, const __grid_constant__ CUtensorMap cache_map
         // is set before any thread skips a wait, so checking it after the wait above is enough.
         if (*abort_flag != 0) break;
         const uint32_t bar = smem_u32(&s_full[s]);
-        float* sb = reinterpret_cast<float*>(stages + s * Cfg::STAGE_BYTES);
+        uint8_t* sb = stages + s * Cfg::STAGE_BYTES;
         mbar_arrive_expect_tx(bar, stage_tx);
         if (GCL > 0) tma_load_5d(smem_u32(sb), &cache_map, bar, rank * U, n, 0, t, b0);
-        float* q = sb + GCL * sbu;
+        float* q = reinterpret_cast<float*>(sb + GCL * sbu * CT::CES);
         tma_load_5d(smem_u32(q), &hist_map, bar, rank * U, n, t, b0, 0);
         q += S * sbu;
         if (t > 0) tma_load_5d(smem_u32(q), &hist_map, bar, rank * U, n, t - 1, b0, 0);
@@ -292,10 +293,10 @@ frnn_bwd_kernel(const BwdParams p, const __grid_constant__ CUtensorMap cache_map
         }
         if (prof) pc6 += clock64() - c0;
         if (active) {
-          const float* sb = reinterpret_cast<const float*>(stages + s * Cfg::STAGE_BYTES);
+          const uint8_t* sb = stages + s * Cfg::STAGE_BYTES;
 #pragma unroll
-          for (int g = 0; g < GCL; ++g) ld_f32_vec<IPT>(sb + (ib * GCL + g) * U + ul, cache[g]);
-          const float* q = sb + GCL * sbu;
+          for (int g = 0; g < GCL; ++g) ld_cache_vec<IPT, CT::CES>(sb, (ib * GCL + g) * U + ul, cache[g]);
+          const float* q = reinterpret_cast<const float*>(sb + GCL * sbu * CT::CES);
 #pragma unroll
           for (int k = 0; k < S; ++k) ld_f32_vec<IPT>(q + k * sbu + ib * U + ul, sn[k]);
           q += S * sbu;
@@ -594,7 +595,7 @@ frnn_bwd_kernel(const BwdParams p, const __grid_constant__ CUtensorMap cache_map
 }
 
 template <int CELL, int BV, int U, bool WX_BF16, bool XG, bool OPTS>
-int launch_bwd(const BwdParams& p, const float* cache, const float* history, const float* initial,
+int launch_bwd(const BwdParams& p, const void* cache, const float* history, const float* initial,
                const float* d_history, cudaStream_t stream) {
   using Cfg = BwdCfg<CELL, BV, U, WX_BF16>;
   using CT = typename Cfg::CT;
@@ -614,7 +615,7 @@ int launch_bwd(const BwdParams& p, const float* cache, const float* history, con
     const uint32_t box[5] = {U, 1u, static_cast<uint32_t>(Cfg::GCL > 0 ? Cfg::GCL : 1), 1u, ub};
     // Elman has no cache: describe the history instead so that the (unused) map is valid.
     const void* base = Cfg::GCL > 0 ? static_cast<const void*>(cache) : static_cast<const void*>(history);
-    if (make_tensor_map(&cache_map, base, 4, 5, dims, box) != 0) return -4;
+    if (make_tensor_map(&cache_map, base, Cfg::GCL > 0 ? CT::CES : 4, 5, dims, box) != 0) return -4;
   }
   {
     const uint64_t dims[5] = {uD, uN, uT, uB, static_cast<uint64_t>(CT::S)};
@@ -664,7 +665,7 @@ int launch_bwd(const BwdParams& p, const float* cache, const float* history, con
 }
 
 template <int CELL, int BV, int U>
-int launch_bwd_dt(const BwdParams& p, const float* cache, const float* history, const float* initial,
+int launch_bwd_dt(const BwdParams& p, const void* cache, const float* history, const float* initial,
                   const float* d_history, int wx_bf16, cudaStream_t s) {
   const bool opts = p.grad_clip > 0.0f || p.cut_recurrent != 0 || p.slstm_v1 != 0;
   if (p.xg_data != nullptr) {  // groups wider than a cluster exchange through global memory
@@ -681,7 +682,7 @@ int launch_bwd_dt(const BwdParams& p, const float* cache, const float* history, 
                  : launch_bwd<CELL, BV, U, false, false, false>(p, cache, history, initial, d_history, s);
 }
 template <int CELL>
-int launch_bwd_cell(const BwdParams& p, const float* cache, const float* history, const float* initial,
+int launch_bwd_cell(const BwdParams& p, const void* cache, const float* history, const float* initial,
                     const float* d_history, int wx_bf16, int bv, int unit, cudaStream_t s) {
   if (bv == 8 && unit == 32) return launch_bwd_dt<CELL, 8, 32>(p, cache, history, initial, d_history, wx_bf16, s);
   if (bv == 16 && unit == 32) return launch_bwd_dt<CELL, 16, 32>(p, cache, history, initial, d_history, wx_bf16, s);
@@ -692,7 +693,7 @@ int launch_bwd_cell(const BwdParams& p, const float* cache, const float* history
 
 }  // namespace
 
-int backward_dispatch(int cell, const BwdParams& p, const float* cache, const float* history, const float* initial,
+int backward_dispatch(int cell, const BwdParams& p, const void* cache, const float* history, const float* initial,
                       const float* d_history, int wx_bf16, int bv, int unit, cudaStream_t s) {
   switch (cell) {
     case kLSTM: return launch_bwd_cell<kLSTM>(p, cache, history, initial, d_history, wx_bf16, bv, unit, s);

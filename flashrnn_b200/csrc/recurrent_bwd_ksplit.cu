@@ -36,8 +36,9 @@ struct BksCfg {
   static constexpr int NI = BV / RPP < 1 ? 1 : BV / RPP;  // (batch row, unit) items per thread
   static constexpr int A_COL0 = 32;
   static constexpr int GCL = CELL == kElman ? 0 : CT::GC;  // cached gates actually loaded
-  static constexpr int STAGE_FLOATS = (GCL + 3 * CT::S) * BV * UO;
-  static constexpr int STAGE_BYTES = STAGE_FLOATS * 4;
+  static constexpr int CACHE_BYTES = GCL * BV * UO * CT::CES;  // the cached gates come first in a stage
+  static constexpr int STAGE_BYTES = CACHE_BYTES + 3 * CT::S * BV * UO * 4;
+  static_assert(CACHE_BYTES % 128 == 0, "TMA destinations after the cached gates stay 128-byte aligned");
   static constexpr int NST = STAGE_BYTES * 4 <= 65536 ? 4 : (STAGE_BYTES * 3 <= 65536 ? 3 : 2);
   static constexpr int PART_FLOATS = KS * BV * UO;  // one parity: [source][batch][unit]
   static constexpr int PART_BYTES = PART_FLOATS * 4;
@@ -220,7 +221,7 @@ frnn_bwd_ks_kernel(const BwdParams p, const __grid_constant__ CUtensorMap cache_
     }
   } else if (warp == 5) {
     if (lane == 0) {
-      const uint32_t stage_tx = static_cast<uint32_t>(p.box_b) * UO * 4u * (GCL + 3 * S);
+      const uint32_t stage_tx = static_cast<uint32_t>(p.box_b) * UO * (GCL * CT::CES + 3 * S * 4);
       const int sbu = p.box_b * UO;  // floats per state plane in a stage
       for (int it = 0; it < T; ++it) {
         const int s = it % Cfg::NST;
@@ -235,10 +236,10 @@ frnn_bwd_ks_kernel(const BwdParams p, const __grid_constant__ CUtensorMap cache_
         // previous copy may still be in flight (the flag is set before any thread skips a wait)
         if (*abort_flag != 0) break;
         const uint32_t bar = smem_u32(&s_full[s]);
-        float* sb = reinterpret_cast<float*>(stages + s * Cfg::STAGE_BYTES);
+        uint8_t* sb = stages + s * Cfg::STAGE_BYTES;
         mbar_arrive_expect_tx(bar, stage_tx);
         if (GCL > 0) tma_load_5d(smem_u32(sb), &cache_map, bar, u0, n, 0, t, b0);
-        float* q = sb + GCL * sbu;
+        float* q = reinterpret_cast<float*>(sb + GCL * sbu * CT::CES);
         tma_load_5d(smem_u32(q), &hist_map, bar, u0, n, t, b0, 0);
         q += S * sbu;
         if (t > 0) tma_load_5d(smem_u32(q), &hist_map, bar, u0, n, t - 1, b0, 0);
@@ -291,13 +292,13 @@ frnn_bwd_ks_kernel(const BwdParams p, const __grid_constant__ CUtensorMap cache_
         report_bks(p.err, kErrWaitWx, it);
         dead = true;
       }
-      const float* sb = reinterpret_cast<const float*>(stages + s * Cfg::STAGE_BYTES);
+      const uint8_t* sb = stages + s * Cfg::STAGE_BYTES;
 #pragma unroll
       for (int j = 0; j < NI; ++j) {
         const int ib = (ib0 + j * RPP) % BV;
 #pragma unroll
-        for (int g = 0; g < GCL; ++g) cache[j][g] = sb[(ib * GCL + g) * UO + ul];
-        const float* q = sb + GCL * sbu;
+        for (int g = 0; g < GCL; ++g) cache[j][g] = ld_cache<CT::CES>(sb, (ib * GCL + g) * UO + ul);
+        const float* q = reinterpret_cast<const float*>(sb + GCL * sbu * CT::CES);
 #pragma unroll
         for (int k = 0; k < S; ++k) {
           sn[j][k] = q[k * sbu + ib * UO + ul];
@@ -543,7 +544,7 @@ frnn_bwd_ks_kernel(const BwdParams p, const __grid_constant__ CUtensorMap cache_
 }
 
 template <int CELL, int BV, int KS, bool WX_BF16>
-int launch_bwd_ks(const BwdParams& p, const float* cache, const float* history, const float* initial,
+int launch_bwd_ks(const BwdParams& p, const void* cache, const float* history, const float* initial,
                   const float* d_history, cudaStream_t stream, int* capacity_only = nullptr) {
   using Cfg = BksCfg<CELL, BV, KS, WX_BF16>;
   using CT = typename Cfg::CT;
@@ -563,7 +564,7 @@ int launch_bwd_ks(const BwdParams& p, const float* cache, const float* history, 
     const uint32_t box[5] = {uo, 1u, static_cast<uint32_t>(Cfg::GCL > 0 ? Cfg::GCL : 1), 1u, ub};
     // Elman has no cache: describe the history instead so that the (unused) map is valid.
     const void* base = Cfg::GCL > 0 ? static_cast<const void*>(cache) : static_cast<const void*>(history);
-    if (make_tensor_map(&cache_map, base, 4, 5, dims, box) != 0) return -4;
+    if (make_tensor_map(&cache_map, base, Cfg::GCL > 0 ? CT::CES : 4, 5, dims, box) != 0) return -4;
   }
   if (capacity_only == nullptr) {
     const uint64_t dims[5] = {uD, uN, uT, uB, static_cast<uint64_t>(CT::S)};
@@ -607,7 +608,7 @@ int launch_bwd_ks(const BwdParams& p, const float* cache, const float* history, 
 }
 
 template <int CELL, int KS>
-int launch_bwd_ks_bv(const BwdParams& p, const float* cache, const float* history, const float* initial,
+int launch_bwd_ks_bv(const BwdParams& p, const void* cache, const float* history, const float* initial,
                      const float* d_history, int wx_bf16, int bv, cudaStream_t s, int* cap) {
   if (bv == 8)
     return wx_bf16 ? launch_bwd_ks<CELL, 8, KS, true>(p, cache, history, initial, d_history, s, cap)
@@ -619,7 +620,7 @@ int launch_bwd_ks_bv(const BwdParams& p, const float* cache, const float* histor
 }
 template <int CELL> constexpr bool CT_GR_IS_ONE = CellTraits<CELL>::GR == 1;
 template <int CELL>
-int launch_bwd_ks_cell(const BwdParams& p, const float* cache, const float* history, const float* initial,
+int launch_bwd_ks_cell(const BwdParams& p, const void* cache, const float* history, const float* initial,
                        const float* d_history, int wx_bf16, int bv, int ksplit, cudaStream_t s, int* cap) {
   if constexpr (CT_GR_IS_ONE<CELL>) {  // only a single-gate cell is narrow enough in K for two chunks
     if (ksplit == 2) return launch_bwd_ks_bv<CELL, 2>(p, cache, history, initial, d_history, wx_bf16, bv, s, cap);
@@ -650,7 +651,7 @@ bool backward_ksplit_valid(int cell, int gates_r, int D, int ks) {
   return K % (ks * 16) == 0 && K / ks <= kMaxKc;
 }
 
-int backward_ksplit_dispatch(int cell, const BwdParams& p, const float* cache, const float* history,
+int backward_ksplit_dispatch(int cell, const BwdParams& p, const void* cache, const float* history,
                              const float* initial, const float* d_history, int wx_bf16, int bv, int ksplit,
                              cudaStream_t s, int* capacity_only) {
   switch (cell) {

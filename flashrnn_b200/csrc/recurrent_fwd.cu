@@ -248,7 +248,7 @@ frnn_fwd_kernel(const FwdParams p, const __grid_constant__ CUtensorMap wx_map) {
     const size_t hist_off = ((static_cast<size_t>(b0 + ib) * Tt + t0) * N + n) * D + d0;  // elements, fp32 or bf16
     float* hist = p.history + hist_off;
     __nv_bfloat16* hist16 = reinterpret_cast<__nv_bfloat16*>(p.history) + hist_off;
-    float* cache = p.cache == nullptr ? nullptr : p.cache + ((static_cast<size_t>(b0 + ib) * T * CT::GC) * N + n) * D + d0;
+    const size_t cache_off = ((static_cast<size_t>(b0 + ib) * T * CT::GC) * N + n) * D + d0;  // elements
     __nv_bfloat16* hbf = p.hbf == nullptr ? nullptr : p.hbf + ((static_cast<size_t>(b0 + ib) * (T + 1) + 1) * N + n) * D + d0;
     const uint32_t h_off = kmajor_offset(BT, ib, d0);
     // Peers this lane pushes to (it shares the cluster with the other lanes of its packet group)
@@ -453,9 +453,10 @@ frnn_fwd_kernel(const FwdParams p, const __grid_constant__ CUtensorMap wx_map) {
             else st_f32_vec<IPT>(hist + q * sBTND + t * ND, st[q]);
           }
         }
-        if (cache != nullptr && CELL != kElman) {
+        if (p.cache != nullptr && CELL != kElman) {
 #pragma unroll
-          for (int q = 0; q < CT::GC; ++q) st_f32_vec<IPT>(cache + (static_cast<size_t>(t) * CT::GC + q) * ND, cv[q]);
+          for (int q = 0; q < CT::GC; ++q)
+            st_cache_vec<IPT, CT::CES>(p.cache, cache_off + (static_cast<size_t>(t) * CT::GC + q) * ND, cv[q]);
         }
         if (hbf != nullptr) {
 #pragma unroll

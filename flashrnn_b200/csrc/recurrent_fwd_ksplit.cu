@@ -407,7 +407,7 @@ frnn_fwd_ks_kernel(const FwdParams p, const __grid_constant__ CUtensorMap wx_map
           }
           if (p.cache != nullptr && CELL != kElman) {
 #pragma unroll
-            for (int q = 0; q < CT::GC; ++q) p.cache[(row * CT::GC + q) * ND + n * D + d0] = cv[j][q];
+            for (int q = 0; q < CT::GC; ++q) st_cache<CT::CES>(p.cache, (row * CT::GC + q) * ND + n * D + d0, cv[j][q]);
           }
           if (p.hbf != nullptr)
             p.hbf[((static_cast<size_t>(b0 + ib0 + j * RPP) * (T + 1) + t + 1) * N + n) * D + d0] =

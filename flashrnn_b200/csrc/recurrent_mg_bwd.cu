@@ -31,8 +31,9 @@ struct MgBwdCfg {
   using CT = CellTraits<CELL>;
   static constexpr int BO = kMgBT / KS;  // batch rows owned by one CTA of the cluster; thread tid owns unit tid of all of them
   static constexpr int GCL = CELL == kElman ? 0 : CT::GC;
-  static constexpr int STAGE_FLOATS = (GCL + 3 * CT::S) * BO * 128;
-  static constexpr int STAGE_BYTES = STAGE_FLOATS * 4;
+  static constexpr int CACHE_BYTES = GCL * BO * 128 * CT::CES;  // the cached gates come first in a stage
+  static constexpr int STAGE_BYTES = CACHE_BYTES + 3 * CT::S * BO * 128 * 4;
+  static_assert(CACHE_BYTES % 128 == 0, "TMA destinations after the cached gates stay 128-byte aligned");
   static constexpr int NST = STAGE_BYTES * 4 <= 49152 ? 4 : (STAGE_BYTES * 3 <= 65536 ? 3 : 2);
   static constexpr int PART_FLOATS = KS * 128 * BO;  // one parity: [source][unit][owned batch row]
   static constexpr int PART_BYTES = PART_FLOATS * 4;
@@ -262,10 +263,10 @@ frnn_bwd_mg_kernel(const MgBwdParams p, const __grid_constant__ CUtensorMap cach
         }
         if (*abort_flag != 0) break;  // stages are released early after a failed wait: do not arm a busy barrier
         const uint32_t bar = smem_u32(&s_full[s]);
-        float* sb = reinterpret_cast<float*>(stages + s * Cfg::STAGE_BYTES);
+        uint8_t* sb = stages + s * Cfg::STAGE_BYTES;
         mbar_arrive_expect_tx(bar, stage_tx);
         if (GCL > 0) tma_load_5d(smem_u32(sb), &cache_map, bar, xu, 0, 0, t, ks * BO);
-        float* q = sb + GCL * sbu;
+        float* q = reinterpret_cast<float*>(sb + Cfg::CACHE_BYTES);
         tma_load_5d(smem_u32(q), &hist_map, bar, xu, 0, t, ks * BO, 0);
         q += S * sbu;
         if (t > 0) tma_load_5d(smem_u32(q), &hist_map, bar, xu, 0, t - 1, ks * BO, 0);
@@ -310,7 +311,6 @@ frnn_bwd_mg_kernel(const MgBwdParams p, const __grid_constant__ CUtensorMap cach
       }
     }
   } else if (ready_ok) {
-    constexpr int sbu = BO * 128;
     const uint32_t part_local = smem_u32(part) + static_cast<uint32_t>((ks * 128 + tid) * BO) * 4u;
     bool dead = false;
     __nv_bfloat16* const pubw = pub + CT::GR * BO * 128;
@@ -336,7 +336,6 @@ frnn_bwd_mg_kernel(const MgBwdParams p, const __grid_constant__ CUtensorMap cach
       }
     };
 
-    const size_t sBT = static_cast<size_t>(B) * T;
     for (int it = 0; it <= T; ++it) {
       const int t = T - 1 - it;
       const int pb = it & 1;
@@ -350,7 +349,7 @@ frnn_bwd_mg_kernel(const MgBwdParams p, const __grid_constant__ CUtensorMap cach
         mg_report(p.err, kErrWaitWx, it);
         dead = true;
       }
-      const float* sb = reinterpret_cast<const float*>(stages + s * Cfg::STAGE_BYTES);
+      const uint8_t* sb = stages + s * Cfg::STAGE_BYTES;
       const float* pbuf = part + pb * Cfg::PART_FLOATS;
       const bool take_i = CELL == kSLSTM && t == 0 && p.slstm_zero_first != 0;
 #pragma unroll
@@ -373,8 +372,8 @@ frnn_bwd_mg_kernel(const MgBwdParams p, const __grid_constant__ CUtensorMap cach
         }
         float cache[CT::GC], sn[S], sp[S];
 #pragma unroll
-        for (int g = 0; g < GCL; ++g) cache[g] = sb[(j * GCL + g) * 128 + tid];
-        const float* q0 = sb + GCL * sbu;
+        for (int g = 0; g < GCL; ++g) cache[g] = ld_cache<CT::CES>(sb, (j * GCL + g) * 128 + tid);
+        const float* q0 = reinterpret_cast<const float*>(sb + Cfg::CACHE_BYTES);
 #pragma unroll
         for (int k = 0; k < S; ++k) {
           sn[k] = q0[(k * BO + j) * 128 + tid];
@@ -520,7 +519,7 @@ int launch_bwd_mg(const MgBwdParams& p, cudaStream_t stream, int* capacity_only)
       const uint32_t box[5] = {128u, 1u, static_cast<uint32_t>(Cfg::GCL > 0 ? Cfg::GCL : 1), 1u, bo};
       // Elman has no cache: describe the history instead so that the (unused) map is valid.
       const void* base = Cfg::GCL > 0 ? static_cast<const void*>(p.cache) : static_cast<const void*>(p.history);
-      if (make_tensor_map(&cache_map, base, 4, 5, dims, box) != 0) return -4;
+      if (make_tensor_map(&cache_map, base, Cfg::GCL > 0 ? CT::CES : 4, 5, dims, box) != 0) return -4;
     }
     {
       const uint64_t dims[5] = {ux, 1u, uT, uB, static_cast<uint64_t>(CT::S)};
@@ -633,7 +632,8 @@ int backward_mg_fixed_smem(int cell, int ksplit, int D, int wx_bf16) {
   const int bo = kMgBT / ksplit;
   const int Kc = gr * D / ksplit;
   const int SCK = Kc < kMgSubK ? Kc : kMgSubK;
-  const int stage = (gcl + 3 * s) * bo * 128 * 4;
+  const int ces = (cell == kLSTM || cell == kGRU) ? 2 : 4;
+  const int stage = (gcl * ces + 3 * s * 4) * bo * 128;
   const int nst = stage * 4 <= 49152 ? 4 : (stage * 3 <= 65536 ? 3 : 2);
   const int pub = (gr + ((wx_bf16 && cell == kGRU) ? gw : 0)) * bo * 128 * 2;
   return 2 * mg_operand_bytes(SCK) + 2 * (ksplit * 128 * bo * 4) + ((pub + 127) & ~127) + nst * stage;

@@ -43,7 +43,7 @@ struct MgFwdParams {
   const float* initial;     // [S][B][ldx]
   float* history;           // [S][B][T][ldx]
   float* carry;             // [S][B][ldx]
-  float* cache;             // [B][T][GC][ldx] or null (inference)
+  void* cache;              // [B][T][GC][ldx] (fp16 or fp32 elements, CellTraits::CES) or null (inference)
   __nv_bfloat16* hbf[kMgMaxRanks];  // every rank's [B][T+1][D] history of round_bf16(h)
   int* ready[kMgMaxRanks];          // every rank's int[kMgMaxRanks] ready flags
   int* err;
@@ -57,7 +57,7 @@ struct MgFwdParams {
 
 struct MgBwdParams {
   const __nv_bfloat16* Rc;  // columns of R owned here: [GR][D][ldx]
-  const float* cache;       // [B][T][GC][ldx]
+  const void* cache;        // [B][T][GC][ldx] (fp16 or fp32 elements, CellTraits::CES)
   const float* history;     // [S][B][T][ldx]
   const float* initial;     // [S][B][ldx]
   const float* d_history;   // [S][B][T][ldx]

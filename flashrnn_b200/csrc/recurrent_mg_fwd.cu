@@ -471,7 +471,7 @@ frnn_fwd_mg_kernel(const MgFwdParams p, const __grid_constant__ CUtensorMap wx_m
           for (int q = 0; q < S; ++q) p.history[(static_cast<size_t>(q) * sBT + row) * ldx + xu + it_u[j]] = st[j][q];
           if (p.cache != nullptr && CELL != kElman) {
 #pragma unroll
-            for (int q = 0; q < CT::GC; ++q) p.cache[(row * CT::GC + q) * ldx + xu + it_u[j]] = cv[j][q];
+            for (int q = 0; q < CT::GC; ++q) st_cache<CT::CES>(p.cache, (row * CT::GC + q) * ldx + xu + it_u[j], cv[j][q]);
           }
         }
       }

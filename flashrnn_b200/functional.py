@@ -98,7 +98,7 @@ class _Recurrence(torch.autograd.Function):
         cache = hbf = None
         if train:
             if plan.cache_bytes:
-                cache = torch.empty(plan.cache_bytes // 4, dtype=torch.float32, device=dev)
+                cache = torch.empty(plan.cache_bytes, dtype=torch.uint8, device=dev)
             hbf = torch.empty(plan.hbf_bytes // 2, dtype=torch.bfloat16, device=dev)
         xchg = torch.empty(plan.xchg_bytes, dtype=torch.uint8, device=dev) if plan.xchg_bytes else None
         err = torch.zeros(32, dtype=torch.int32, device=dev)

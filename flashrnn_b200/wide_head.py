@@ -218,7 +218,7 @@ class _WideRecurrence(torch.autograd.Function):
             history = torch.empty((S, B, T, 1, lw), dtype=torch.float32, device=dev)
             carry = torch.empty((S, B, 1, 1, lw), dtype=torch.float32, device=dev)
             train = any(ctx.needs_input_grad[:4])
-            cache = torch.empty(head.plan.cache_bytes // 4, dtype=torch.float32, device=dev) if train and head.plan.cache_bytes else None
+            cache = torch.empty(head.plan.cache_bytes, dtype=torch.uint8, device=dev) if train and head.plan.cache_bytes else None
             err = torch.zeros(32, dtype=torch.int32, device=dev)
             if head.profile:
                 err[3] = 1

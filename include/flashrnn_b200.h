@@ -48,7 +48,7 @@ typedef struct frnn_b200_plan {
   int n_btiles;    /* ceil(B / batch_tile)                                        */
   int grid_ctas;   /* N * n_btiles * cluster                                      */
   int supported;   /* 1 if the shape runs on this kernel family                   */
-  int64_t cache_bytes;   /* float  [B,T,cache_gates,N,D]   forward -> backward     */
+  int64_t cache_bytes;   /* [B,T,cache_gates,N,D] forward -> backward: fp16 (lstm, gru) or fp32 (slstm) */
   int64_t hbf_bytes;     /* bf16   [B,T+1,N,D]             forward -> wgrad        */
   int64_t dgr_bytes;     /* bf16   [B,T,gates_r,N,D]       backward -> wgrad       */
   int64_t dbpart_bytes;  /* float  [n_btiles,gates_b,N,D]  backward -> wgrad       */
@@ -91,7 +91,7 @@ int frnn_b200_plan(int cell, int B, int T, int N, int D, frnn_b200_plan_t* out);
  *   slstm_zero_first: 1 if every element of initial n is zero (reference.py:99)
  *   wait_limit_ms: bound for every in-kernel wait (0 = default 2000 ms)              */
 int frnn_b200_forward(int cell, const void* wx, int wx_bf16, const void* r_bf16, const float* bias,
-                      const float* initial, float* history, float* carry, float* cache, void* hbf,
+                      const float* initial, float* history, float* carry, void* cache, void* hbf,
                       void* xchg, int B, int T, int N, int D, int slstm_zero_first, int wait_limit_ms,
                       int* err, void* stream);
 
@@ -112,10 +112,10 @@ typedef struct frnn_b200_options {
 
 /* frnn_b200_forward / frnn_b200_backward with options. */
 int frnn_b200_forward_ex(int cell, const void* wx, int wx_bf16, const void* r_bf16, const float* bias,
-                         const float* initial, float* history, float* carry, float* cache, void* hbf, void* xchg,
+                         const float* initial, float* history, float* carry, void* cache, void* hbf, void* xchg,
                          int B, int T, int N, int D, int slstm_zero_first, int wait_limit_ms, int* err, void* stream,
                          const frnn_b200_options_t* options);
-int frnn_b200_backward_ex(int cell, const float* cache, const float* history, const float* initial,
+int frnn_b200_backward_ex(int cell, const void* cache, const float* history, const float* initial,
                           const void* r_bf16, const float* d_history, const float* d_carry, void* dwx, int wx_bf16,
                           void* dgr, float* d_initial, float* db_part, void* xchg, int B, int T, int N, int D,
                           int slstm_zero_first, int wait_limit_ms, int* err, void* stream,
@@ -156,7 +156,7 @@ int frnn_b200_forward_chunk(int cell, const void* wx, int wx_bf16, const void* r
  *          are its recurrent gates (lstm, slstm, elman) dwx and dgr hold the same values in the same layout: the
  *          caller may pass the SAME buffer for both, which is then written once (saves the second copy's traffic)
  *   d_initial : out fp32 [S,B,1,N,D];  db_part: out scratch fp32 [n_btiles,GB,N,D]    */
-int frnn_b200_backward(int cell, const float* cache, const float* history, const float* initial,
+int frnn_b200_backward(int cell, const void* cache, const float* history, const float* initial,
                        const void* r_bf16, const float* d_history, const float* d_carry, void* dwx,
                        int wx_bf16, void* dgr, float* d_initial, float* db_part, void* xchg, int B,
                        int T, int N, int D, int slstm_zero_first, int wait_limit_ms, int* err,
@@ -231,7 +231,7 @@ typedef struct frnn_b200_mg_plan {
   int bwd_ksplit, bwd_ctas;
   int bwd_k_tmem, bwd_ring_chunks, bwd_ring_stages, bwd_resident;
   int64_t hbf_bytes, dgr_bytes;    /* one rank's exchange buffers                                          */
-  int64_t cache_bytes;             /* fp32 [B][T][GC][row length]                                          */
+  int64_t cache_bytes;             /* [B][T][GC][row length], fp16 (lstm, gru) or fp32 (slstm)             */
   int64_t r_cols_bytes;            /* bf16 [GR][D][row length]                                             */
   int64_t dbpart_bytes;            /* fp32 [bwd_ksplit][GB][row length]                                    */
 } frnn_b200_mg_plan_t;
@@ -247,7 +247,7 @@ int frnn_b200_mg_capacity(int cell, int forward, int ksplit, int D, int P, int w
 /* Forward (multi_gpu.py:87-297). sh->buffers = the ranks' h histories. Outputs: history [S,B,T,Dl], carry [S,B,1,Dl],
  * cache (NULL for inference). The h history of this rank holds round_bf16(h) of ALL units afterwards (slots 0..T-1). */
 int frnn_b200_mg_forward(int cell, const void* wx, int wx_bf16, const void* r_rows, const float* bias,
-                         const float* initial, float* history, float* carry, float* cache,
+                         const float* initial, float* history, float* carry, void* cache,
                          const frnn_b200_mg_shard_t* shard, int B, int T, int D, int slstm_zero_first,
                          int wait_limit_ms, int* err, void* stream);
 
@@ -259,7 +259,7 @@ int frnn_b200_mg_gather_columns(int cell, const void* const* r_rows_all, void* r
 
 /* Backward (hybrid_bw2d.cu:507-552,645-661). sh->buffers = the ranks' dG histories. Outputs: dwx [B,T,GW,Dl] in the
  * Wx dtype, d_initial [S,B,1,Dl], db_part [plan.bwd_ksplit][GB][Dl]. */
-int frnn_b200_mg_backward(int cell, const float* cache, const float* history, const float* initial,
+int frnn_b200_mg_backward(int cell, const void* cache, const float* history, const float* initial,
                           const void* r_cols, const float* d_history, const float* d_carry, void* dwx, int wx_bf16,
                           float* d_initial, float* db_part, const frnn_b200_mg_shard_t* shard, int B, int T, int D,
                           int slstm_zero_first, int wait_limit_ms, int* err, void* stream);

@@ -27,7 +27,7 @@ def test_plan_describes_the_headline_workload():
     p = _lib.plan("lstm", 8, 1024, 3, 256)
     assert (p.gates_r, p.gates_w, p.gates_b, p.states) == (4, 4, 4, 2)
     assert (p.unit, p.cluster, p.batch_tile, p.n_btiles, p.grid_ctas, p.supported) == (32, 8, 8, 1, 24, 1)
-    assert p.cache_bytes == 8 * 1024 * 4 * 3 * 256 * 4 and p.hbf_bytes == 8 * 1025 * 3 * 256 * 2
+    assert p.cache_bytes == 8 * 1024 * 4 * 3 * 256 * 2 and p.hbf_bytes == 8 * 1025 * 3 * 256 * 2
     g = _lib.plan("gru", 16, 10, 2, 48)
     assert (g.gates_r, g.gates_b, g.unit, g.cluster, g.batch_tile, g.n_btiles) == (3, 4, 16, 3, 8, 2)
     big = _lib.plan("lstm", 256, 16, 32, 128)                # more groups than SMs: 16-row batch tiles

@@ -16,7 +16,7 @@ def _buffers(_lib, cell, B, T, N, D, dev):
     wx, R, b, init = make_inputs(cell, B, T, N, D, 9)
     t = dict(wx=wx.to(dev).contiguous(), R=R.to(dev).bfloat16().contiguous(), b=b.to(dev), init=init.to(dev),
              hist=torch.zeros((S, B, T, N, D), device=dev), carry=torch.zeros((S, B, 1, N, D), device=dev),
-             cache=torch.zeros(plan.cache_bytes // 4, device=dev),
+             cache=torch.zeros(plan.cache_bytes, dtype=torch.uint8, device=dev),
              hbf=torch.zeros(plan.hbf_bytes // 2, dtype=torch.bfloat16, device=dev),
              dwx=torch.zeros((B, T, gw, N, D), device=dev), dgr=torch.zeros(plan.dgr_bytes // 2, dtype=torch.bfloat16, device=dev),
              dinit=torch.zeros((S, B, 1, N, D), device=dev), dbp=torch.zeros(plan.dbpart_bytes // 4, device=dev),
