@@ -4,6 +4,7 @@
     python bench_shapes.py lstm 16 1024 3 256
     torchrun ... bench_shapes.py config5b   # N32 D128 B256 T2048, heads sharded over the ranks
     [torchrun ...] bench_shapes.py wide [T [D [B]]]   # one head of D (4096) units row-sharded over the ranks
+    python bench_shapes.py projection      # the input-projection GEMM against torch.matmul (cuBLAS)
 
 The head-dimension sweep mirrors the reference's published one
 (flashrnn/speed_experiments/kernel_speed_benchmark.py:104-127: N*D = 768, B = 16, T = 1024).
@@ -243,7 +244,52 @@ def time_wide_head(T: int = 512, D: int = 4096, B: int = 32, cell: str = "lstm",
     return out
 
 
+def time_projection(reps: int = 20) -> None:
+    """The input-projection kernel (x[B*T, I] @ W[J, I].T -> bf16 Wx) through the C ABI on preallocated buffers,
+    beside torch.matmul on the same operands; CUDA events around `reps` back-to-back launches."""
+    lib = _lib.load()
+    dev = torch.device("cuda:0")
+    stream = torch.cuda.current_stream(dev).cuda_stream
+    print("| B | T | inputs I | outputs J | ours µs | TFLOP/s | torch.matmul µs | TFLOP/s |")
+    print("|---|---|---|---|---|---|---|---|")
+    for (B, T, I, J) in ((8, 1024, 768, 3072), (16, 1024, 768, 3072), (64, 1024, 768, 3072), (64, 2048, 1024, 4096),
+                         (256, 2048, 512, 2048)):
+        g = torch.Generator(device="cpu").manual_seed(3)
+        x = torch.randn(B * T, I, generator=g).to(dev).bfloat16()
+        w = (torch.randn(J, I, generator=g) * I ** -0.5).to(dev).bfloat16()
+        out = torch.empty((B * T, J), dtype=torch.bfloat16, device=dev)
+        ref = torch.empty_like(out)
+        err = torch.zeros(32, dtype=torch.int32, device=dev)
+
+        def ours():
+            _lib.check(lib.frnn_b200_input_projection(x.data_ptr(), w.data_ptr(), None, out.data_ptr(), 1, B, T, J, I,
+                                                      err.data_ptr(), stream), "input_projection")
+
+        def library():
+            torch.matmul(x, w.t(), out=ref)
+
+        def timed(fn) -> float:
+            for _ in range(3):
+                fn()
+            torch.cuda.synchronize()
+            e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+            e0.record()
+            for _ in range(reps):
+                fn()
+            e1.record()
+            e1.synchronize()
+            return e0.elapsed_time(e1) / reps * 1e3
+
+        a, b = timed(ours), timed(library)
+        if int(err[0]) != 0 or not torch.allclose(out.float(), ref.float(), atol=3e-2, rtol=2e-2):
+            raise RuntimeError(f"projection mismatch at B{B} T{T} I{I} J{J} (err {err[:3].tolist()})")
+        fl = 2.0 * B * T * I * J
+        print(f"| {B} | {T} | {I} | {J} | {a:.1f} | {fl / a / 1e6:.0f} | {b:.1f} | {fl / b / 1e6:.0f} |", flush=True)
+
+
 def main(argv) -> None:
+    if argv and argv[0] == "projection":
+        return time_projection()
     if argv and argv[0] == "wide":  # optionally followed by T, D, B
         time_wide_head(*map(int, argv[1:4]))
         return

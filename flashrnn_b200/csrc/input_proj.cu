@@ -2,10 +2,12 @@
 // j = (gate, head, unit), written directly in the layout and dtype the recurrent kernels stream by TMA
 // (Wx[B,T,GW,N,D] is the row-major [B*T][GW*N*D] matrix). bf16 operands, fp32 accumulation in tensor memory.
 //
-// One CTA per 128 x NP output tile (NP = 256, 128 or 64 columns): warp 0 feeds a 4-stage ring of 128-byte-swizzled
-// K-major stages by TMA (x rows and W rows, 64 input features per stage), warp 1 issues tcgen05.mma (both operands
-// from shared memory), warps 2-5 convert the accumulator and store whole rows. Rows and features past the matrix
-// edges are filled with zeros by TMA.
+// Persistent kernel, one CTA per SM, each walking 128 x NP output tiles (NP = 256, 128 or 64 columns; tiles that share
+// rows of x are neighbours in the walk, so x comes from HBM once and W stays in L2): warp 0 feeds a 4-stage ring of
+// 128-byte-swizzled K-major stages by TMA (x rows and W rows, 64 input features per stage), warp 1 issues tcgen05.mma
+// (both operands from shared memory) into one of TWO accumulators in tensor memory, warps 2-5 convert the other one and
+// store 32 consecutive columns per thread, so the epilogue of a tile runs under the contraction of the next. Rows and
+// features past the matrix edges are filled with zeros by TMA.
 //
 // The reference leaves this GEMM to the caller (README.md:16) and times it as the "-withlinear" variant of its
 // benchmark (flashrnn/speed_experiments/kernel_speed_benchmark.py:388-408, a torch.nn.Linear in front of the kernel).
@@ -23,8 +25,8 @@ struct ProjParams {
   void* out;          // [M][J] bf16 or fp32
   const float* bias;  // [J] or null
   int* err;
-  long long M;
-  int J, I, NP;
+  long long M, n_tiles;
+  int J, I, NP, n_jt;
   int out_bf16;
 };
 
@@ -33,16 +35,17 @@ input_proj_kernel(const ProjParams p, const __grid_constant__ CUtensorMap x_map,
   extern __shared__ uint8_t smem_raw[];
   __shared__ __align__(8) uint64_t s_full[kProjStages];
   __shared__ __align__(8) uint64_t s_empty[kProjStages];
-  __shared__ __align__(8) uint64_t s_acc;
+  __shared__ __align__(8) uint64_t s_acc_full[2];
+  __shared__ __align__(8) uint64_t s_acc_empty[2];
+  __shared__ __align__(8) uint64_t s_done;
   __shared__ uint32_t s_tmem_base;
   const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
   const int NP = p.NP;
-  const int m0 = static_cast<int>(blockIdx.x) * 128, j0 = static_cast<int>(blockIdx.y) * NP;
   const int n_chunks = (p.I + kProjKC - 1) / kProjKC;
   const uint32_t stage_bytes = 16384u + static_cast<uint32_t>(NP) * 128u;
   const uint32_t base = (smem_u32(smem_raw) + 1023u) & ~1023u;
   uint32_t tmem_cols = 32;
-  while (tmem_cols < static_cast<uint32_t>(NP)) tmem_cols <<= 1;
+  while (tmem_cols < 2u * static_cast<uint32_t>(NP)) tmem_cols <<= 1;
   const volatile int* abort_flag = p.err;
   constexpr uint64_t kLimit = 2000000000ull;
 
@@ -51,7 +54,11 @@ input_proj_kernel(const ProjParams p, const __grid_constant__ CUtensorMap x_map,
       mbar_init(smem_u32(&s_full[s]), 1);
       mbar_init(smem_u32(&s_empty[s]), 1);
     }
-    mbar_init(smem_u32(&s_acc), 1);
+    for (int a = 0; a < 2; ++a) {
+      mbar_init(smem_u32(&s_acc_full[a]), 1);
+      mbar_init(smem_u32(&s_acc_empty[a]), 4);  // one arrival per epilogue warp
+    }
+    mbar_init(smem_u32(&s_done), 1);
     fence_mbar_init();
   }
   if (warp == 1) {
@@ -67,74 +74,114 @@ input_proj_kernel(const ProjParams p, const __grid_constant__ CUtensorMap x_map,
     if (lane == 0) {
       tma_prefetch_desc(&x_map);
       tma_prefetch_desc(&w_map);
-      for (int i = 0; i < n_chunks; ++i) {
-        const int s = i % kProjStages;
-        if (i >= kProjStages &&
-            !mbar_wait_bounded<false, true>(smem_u32(&s_empty[s]), ((i / kProjStages) - 1) & 1, kLimit, abort_flag)) {
-          atomicCAS(p.err, 0, kErrWaitEmpty);
-          break;
+      uint32_t s = 0, round = 0;  // ring stage and how often the ring has wrapped
+      bool dead = false;
+      for (long long tile = blockIdx.x; tile < p.n_tiles && !dead; tile += gridDim.x) {
+        const int m0 = static_cast<int>(tile / p.n_jt) * 128, j0 = static_cast<int>(tile % p.n_jt) * NP;
+        for (int i = 0; i < n_chunks; ++i) {
+          if (round > 0 && !mbar_wait_bounded<false, true>(smem_u32(&s_empty[s]), (round - 1) & 1, kLimit, abort_flag)) {
+            atomicCAS(p.err, 0, kErrWaitEmpty);
+            dead = true;
+            break;
+          }
+          const uint32_t bar = smem_u32(&s_full[s]);
+          const uint32_t sa = base + s * stage_bytes, sb = sa + 16384u;
+          mbar_arrive_expect_tx(bar, stage_bytes);
+          tma_load_3d(sa, &x_map, bar, i * kProjKC, m0, 0);
+          tma_load_3d(sb, &w_map, bar, i * kProjKC, j0, 0);
+          if (++s == kProjStages) { s = 0; ++round; }
         }
-        const uint32_t bar = smem_u32(&s_full[s]);
-        const uint32_t sa = base + s * stage_bytes, sb = sa + 16384u;
-        mbar_arrive_expect_tx(bar, stage_bytes);
-        tma_load_3d(sa, &x_map, bar, i * kProjKC, m0, 0);
-        tma_load_3d(sb, &w_map, bar, i * kProjKC, j0, 0);
+      }
+      if (dead) {  // give the copies in flight time to land before the CTA leaves
+        const uint64_t t0 = global_timer_ns();
+        while (global_timer_ns() - t0 < 200000ull) __nanosleep(1000);
       }
     }
   } else if (warp == 1) {
     if (lane == 0) {
       const uint32_t idesc = umma_idesc_bf16(128, NP, false, false);
-      for (int i = 0; i < n_chunks; ++i) {
-        const int s = i % kProjStages;
-        if (!mbar_wait_bounded<false, true>(smem_u32(&s_full[s]), (i / kProjStages) & 1, kLimit, abort_flag)) {
-          atomicCAS(p.err, 0, kErrWaitWx);
+      uint32_t s = 0, round = 0, li = 0;
+      bool dead = false;
+      for (long long tile = blockIdx.x; tile < p.n_tiles && !dead; tile += gridDim.x, ++li) {
+        const uint32_t a = li & 1u;
+        if (li >= 2 && !mbar_wait_bounded<false, true>(smem_u32(&s_acc_empty[a]), ((li >> 1) - 1) & 1, kLimit, abort_flag)) {
+          atomicCAS(p.err, 0, kErrWaitMma);
           break;
         }
         tc_fence_after_sync();
-        uint64_t ad = umma_smem_desc_k_sw128(base + s * stage_bytes);
-        uint64_t bd = umma_smem_desc_k_sw128(base + s * stage_bytes + 16384u);
+        const uint32_t d = tbase + a * static_cast<uint32_t>(NP);
+        for (int i = 0; i < n_chunks; ++i) {
+          if (!mbar_wait_bounded<false, true>(smem_u32(&s_full[s]), round & 1, kLimit, abort_flag)) {
+            atomicCAS(p.err, 0, kErrWaitWx);
+            dead = true;
+            break;
+          }
+          tc_fence_after_sync();
+          uint64_t ad = umma_smem_desc_k_sw128(base + s * stage_bytes);
+          uint64_t bd = umma_smem_desc_k_sw128(base + s * stage_bytes + 16384u);
 #pragma unroll
-        for (int kk = 0; kk < kProjKC / 16; ++kk) {
-          umma_bf16_ss(tbase, ad, bd, idesc, (i > 0 || kk > 0) ? 1u : 0u);
-          ad += 2;  // 16 features = 32 bytes inside the swizzled 128-byte row
-          bd += 2;
+          for (int kk = 0; kk < kProjKC / 16; ++kk) {
+            umma_bf16_ss(d, ad, bd, idesc, (i > 0 || kk > 0) ? 1u : 0u);
+            ad += 2;  // 16 features = 32 bytes inside the swizzled 128-byte row
+            bd += 2;
+          }
+          umma_commit(smem_u32(&s_empty[s]));
+          if (++s == kProjStages) { s = 0; ++round; }
         }
-        umma_commit(smem_u32(&s_empty[s]));
+        if (!dead) umma_commit(smem_u32(&s_acc_full[a]));
       }
       // one commit covers every MMA issued so far; the issuing thread waits for it itself so that tensor and shared
       // memory are never released under a running MMA (also after a failed wait)
-      umma_commit(smem_u32(&s_acc));
-      mbar_wait_bounded<false, true>(smem_u32(&s_acc), 0, kLimit, nullptr);
+      umma_commit(smem_u32(&s_done));
+      mbar_wait_bounded<false, true>(smem_u32(&s_done), 0, kLimit, nullptr);
     }
   } else {
     const int q = warp & 3;  // TMEM lane quarter this warp may read
-    const long long m = static_cast<long long>(m0) + 32 * q + lane;
-    bool have = true;
-    if (!mbar_wait_bounded<false, true>(smem_u32(&s_acc), 0, kLimit, abort_flag)) {
-      atomicCAS(p.err, 0, kErrWaitMma);
-      have = false;
-    }
-    tc_fence_after_sync();
-    for (int c8 = 0; c8 < NP; c8 += 8) {
-      uint32_t r[8] = {0u, 0u, 0u, 0u, 0u, 0u, 0u, 0u};
-      if (have) {
-        tmem_ld_x8(tmem_addr(tbase, 32 * q, c8), r);
-        tmem_ld_wait();
+    uint32_t li = 0;
+    for (long long tile = blockIdx.x; tile < p.n_tiles; tile += gridDim.x, ++li) {
+      const uint32_t a = li & 1u;
+      const long long m = (tile / p.n_jt) * 128 + 32 * q + lane;
+      const int j0 = static_cast<int>(tile % p.n_jt) * NP;
+      bool have = mbar_wait_bounded<false, true>(smem_u32(&s_acc_full[a]), (li >> 1) & 1, kLimit, abort_flag);
+      have = __all_sync(0xffffffffu, have);
+      if (!have) {
+        if (lane == 0) atomicCAS(p.err, 0, kErrWaitMma);
+        break;
       }
-      if (m < p.M && j0 + c8 < p.J) {
-        float v[8];
+      tc_fence_after_sync();
+      for (int c0 = 0; c0 < NP; c0 += 32) {
+        uint32_t r[32];
+        tmem_ld_x32(tmem_addr(tbase, 32 * q, a * NP + c0), r);
+        tmem_ld_wait();
+        if (m < p.M) {
+          float v[32];
 #pragma unroll
-        for (int k = 0; k < 8; ++k) v[k] = __uint_as_float(r[k]) + (p.bias != nullptr ? __ldg(p.bias + j0 + c8 + k) : 0.0f);
-        const size_t at = static_cast<size_t>(m) * p.J + j0 + c8;
-        if (p.out_bf16) {
-          *reinterpret_cast<uint4*>(static_cast<__nv_bfloat16*>(p.out) + at) =
-              make_uint4(pack_bf16x2(v[0], v[1]), pack_bf16x2(v[2], v[3]), pack_bf16x2(v[4], v[5]), pack_bf16x2(v[6], v[7]));
-        } else {
-          float* dst = static_cast<float*>(p.out) + at;
-          *reinterpret_cast<float4*>(dst) = make_float4(v[0], v[1], v[2], v[3]);
-          *reinterpret_cast<float4*>(dst + 4) = make_float4(v[4], v[5], v[6], v[7]);
+          for (int k = 0; k < 32; ++k) v[k] = __uint_as_float(r[k]);
+          if (p.bias != nullptr) {
+#pragma unroll
+            for (int k = 0; k < 32; k += 4) {
+              const float4 bv = __ldg(reinterpret_cast<const float4*>(p.bias + j0 + c0 + k));
+              v[k] += bv.x; v[k + 1] += bv.y; v[k + 2] += bv.z; v[k + 3] += bv.w;
+            }
+          }
+          const size_t at = static_cast<size_t>(m) * p.J + j0 + c0;
+          if (p.out_bf16) {
+            uint4* dst = reinterpret_cast<uint4*>(static_cast<__nv_bfloat16*>(p.out) + at);
+#pragma unroll
+            for (int k = 0; k < 4; ++k)
+              dst[k] = make_uint4(pack_bf16x2(v[8 * k], v[8 * k + 1]), pack_bf16x2(v[8 * k + 2], v[8 * k + 3]),
+                                  pack_bf16x2(v[8 * k + 4], v[8 * k + 5]), pack_bf16x2(v[8 * k + 6], v[8 * k + 7]));
+          } else {
+            float4* dst = reinterpret_cast<float4*>(static_cast<float*>(p.out) + at);
+#pragma unroll
+            for (int k = 0; k < 8; ++k) dst[k] = make_float4(v[4 * k], v[4 * k + 1], v[4 * k + 2], v[4 * k + 3]);
+          }
         }
       }
+      // the accumulator has been read into registers: hand it back to the MMA warp
+      tc_fence_before_sync();
+      __syncwarp();
+      if (lane == 0) mbar_arrive(smem_u32(&s_acc_empty[a]));
     }
   }
   tc_fence_before_sync();
@@ -148,10 +195,15 @@ input_proj_kernel(const ProjParams p, const __grid_constant__ CUtensorMap x_map,
 int input_proj_launch(const void* x, const void* w, const float* bias, void* out, int out_bf16, long long M, int J, int I,
                       int* err, cudaStream_t s) {
   if (M < 1 || J < 64 || J % 64 != 0 || I < 8 || I % 8 != 0) return -2;
+  if (((reinterpret_cast<uintptr_t>(out) | reinterpret_cast<uintptr_t>(bias)) & 15u) != 0) return -2;  // vector access
   const int np = J % 256 == 0 ? 256 : (J % 128 == 0 ? 128 : 64);
   ProjParams p{};
   p.out = out; p.bias = bias; p.err = err;
   p.M = M; p.J = J; p.I = I; p.NP = np; p.out_bf16 = out_bf16;
+  const long long mt = (M + 127) / 128;
+  if (mt > 0x7fffffffLL) return -2;
+  p.n_jt = J / np;
+  p.n_tiles = mt * p.n_jt;
   CUtensorMap x_map, w_map;
   const uint64_t xdims[3] = {static_cast<uint64_t>(I), static_cast<uint64_t>(M), 1u};
   const uint32_t xbox[3] = {static_cast<uint32_t>(kProjKC), 128u, 1u};
@@ -162,9 +214,11 @@ int input_proj_launch(const void* x, const void* w, const float* bias, void* out
   const int smem = kProjStages * (16384 + np * 128) + 1024;
   cudaError_t e = cudaFuncSetAttribute(input_proj_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, smem);
   if (e != cudaSuccess) return static_cast<int>(e);
-  const long long mt = (M + 127) / 128;
-  if (mt > 0x7fffffffLL) return -2;
-  dim3 grid(static_cast<unsigned>(mt), static_cast<unsigned>(J / np), 1u);
+  int dev = 0, sms = 0;
+  e = cudaGetDevice(&dev);
+  if (e == cudaSuccess) e = cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev);
+  if (e != cudaSuccess) return static_cast<int>(e);
+  const unsigned grid = static_cast<unsigned>(p.n_tiles < sms ? p.n_tiles : sms);  // persistent: one CTA per SM
   input_proj_kernel<<<grid, kProjThreads, smem, s>>>(p, x_map, w_map);
   return static_cast<int>(cudaGetLastError());
 }
