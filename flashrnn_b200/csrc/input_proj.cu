@@ -5,8 +5,9 @@
 // Persistent kernel, one CTA per SM, each walking 128 x NP output tiles (NP = 256, 128 or 64 columns; tiles that share
 // rows of x are neighbours in the walk, so x comes from HBM once and W stays in L2): warp 0 feeds a 4-stage ring of
 // 128-byte-swizzled K-major stages by TMA (x rows and W rows, 64 input features per stage), warp 1 issues tcgen05.mma
-// (both operands from shared memory) into one of TWO accumulators in tensor memory, warps 2-5 convert the other one and
-// store 32 consecutive columns per thread, so the epilogue of a tile runs under the contraction of the next. Rows and
+// (both operands from shared memory) into one of TWO accumulators in tensor memory, warps 2-5 convert the other one
+// into swizzled 32-row x 128-byte staging buffers that TMA stores write out as whole lines, so the epilogue of a tile
+// runs under the contraction of the next. Rows and
 // features past the matrix edges are filled with zeros by TMA.
 //
 // The reference leaves this GEMM to the caller (README.md:16) and times it as the "-withlinear" variant of its
@@ -31,7 +32,8 @@ struct ProjParams {
 };
 
 __global__ void __launch_bounds__(kProjThreads, 1)
-input_proj_kernel(const ProjParams p, const __grid_constant__ CUtensorMap x_map, const __grid_constant__ CUtensorMap w_map) {
+input_proj_kernel(const ProjParams p, const __grid_constant__ CUtensorMap x_map, const __grid_constant__ CUtensorMap w_map,
+                  const __grid_constant__ CUtensorMap out_map) {
   extern __shared__ uint8_t smem_raw[];
   __shared__ __align__(8) uint64_t s_full[kProjStages];
   __shared__ __align__(8) uint64_t s_empty[kProjStages];
@@ -74,6 +76,7 @@ input_proj_kernel(const ProjParams p, const __grid_constant__ CUtensorMap x_map,
     if (lane == 0) {
       tma_prefetch_desc(&x_map);
       tma_prefetch_desc(&w_map);
+      tma_prefetch_desc(&out_map);
       uint32_t s = 0, round = 0;  // ring stage and how often the ring has wrapped
       bool dead = false;
       for (long long tile = blockIdx.x; tile < p.n_tiles && !dead; tile += gridDim.x) {
@@ -137,10 +140,15 @@ input_proj_kernel(const ProjParams p, const __grid_constant__ CUtensorMap x_map,
     }
   } else {
     const int q = warp & 3;  // TMEM lane quarter this warp may read
-    uint32_t li = 0;
+    // Each warp turns its 32 rows into 128-byte row pieces (64 bf16 or 32 fp32 columns) in a swizzled staging buffer
+    // of its own and lets TMA write them: whole lines per row instead of 32 scattered 16-byte stores per instruction.
+    const int CW = p.out_bf16 ? 64 : 32;
+    const uint32_t stg = base + kProjStages * stage_bytes + static_cast<uint32_t>(q) * 8192u;
+    const uint32_t my_row = static_cast<uint32_t>(lane) * 128u, sw = static_cast<uint32_t>(lane & 7);
+    uint32_t li = 0, piece = 0;
     for (long long tile = blockIdx.x; tile < p.n_tiles; tile += gridDim.x, ++li) {
       const uint32_t a = li & 1u;
-      const long long m = (tile / p.n_jt) * 128 + 32 * q + lane;
+      const long long mw = (tile / p.n_jt) * 128 + 32 * q;  // first row of this warp
       const int j0 = static_cast<int>(tile % p.n_jt) * NP;
       bool have = mbar_wait_bounded<false, true>(smem_u32(&s_acc_full[a]), (li >> 1) & 1, kLimit, abort_flag);
       have = __all_sync(0xffffffffu, have);
@@ -149,40 +157,69 @@ input_proj_kernel(const ProjParams p, const __grid_constant__ CUtensorMap x_map,
         break;
       }
       tc_fence_after_sync();
-      for (int c0 = 0; c0 < NP; c0 += 32) {
-        uint32_t r[32];
-        tmem_ld_x32(tmem_addr(tbase, 32 * q, a * NP + c0), r);
+      for (int c0 = 0; c0 < NP; c0 += CW, ++piece) {
+        uint32_t r0[32], r1[32];
+        tmem_ld_x32(tmem_addr(tbase, 32 * q, a * NP + c0), r0);
+        if (p.out_bf16) tmem_ld_x32(tmem_addr(tbase, 32 * q, a * NP + c0 + 32), r1);
         tmem_ld_wait();
-        if (m < p.M) {
-          float v[32];
+        if (c0 + CW >= NP) {  // the accumulator is in registers: hand it back to the MMA warp
+          tc_fence_before_sync();
+          __syncwarp();
+          if (lane == 0) mbar_arrive(smem_u32(&s_acc_empty[a]));
+        }
+        if (mw >= p.M) continue;  // warp-uniform: all 32 rows lie past the matrix
+        const uint32_t buf = stg + (piece & 1u) * 4096u;
+        if (lane == 0) tma_store_wait_read<1>();  // the store that read this buffer two pieces ago is done with it
+        __syncwarp();
+        if (p.bias != nullptr) {
 #pragma unroll
-          for (int k = 0; k < 32; ++k) v[k] = __uint_as_float(r[k]);
-          if (p.bias != nullptr) {
+          for (int k = 0; k < 32; k += 4) {
+            const float4 bv = __ldg(reinterpret_cast<const float4*>(p.bias + j0 + c0 + k));
+            r0[k] = __float_as_uint(__uint_as_float(r0[k]) + bv.x);
+            r0[k + 1] = __float_as_uint(__uint_as_float(r0[k + 1]) + bv.y);
+            r0[k + 2] = __float_as_uint(__uint_as_float(r0[k + 2]) + bv.z);
+            r0[k + 3] = __float_as_uint(__uint_as_float(r0[k + 3]) + bv.w);
+          }
+          if (p.out_bf16) {
 #pragma unroll
             for (int k = 0; k < 32; k += 4) {
-              const float4 bv = __ldg(reinterpret_cast<const float4*>(p.bias + j0 + c0 + k));
-              v[k] += bv.x; v[k + 1] += bv.y; v[k + 2] += bv.z; v[k + 3] += bv.w;
+              const float4 bv = __ldg(reinterpret_cast<const float4*>(p.bias + j0 + c0 + 32 + k));
+              r1[k] = __float_as_uint(__uint_as_float(r1[k]) + bv.x);
+              r1[k + 1] = __float_as_uint(__uint_as_float(r1[k + 1]) + bv.y);
+              r1[k + 2] = __float_as_uint(__uint_as_float(r1[k + 2]) + bv.z);
+              r1[k + 3] = __float_as_uint(__uint_as_float(r1[k + 3]) + bv.w);
             }
           }
-          const size_t at = static_cast<size_t>(m) * p.J + j0 + c0;
-          if (p.out_bf16) {
-            uint4* dst = reinterpret_cast<uint4*>(static_cast<__nv_bfloat16*>(p.out) + at);
+        }
+        auto put = [&](uint32_t k16, uint32_t w0, uint32_t w1, uint32_t w2, uint32_t w3) {
+          asm volatile("st.shared.v4.b32 [%0], {%1, %2, %3, %4};"
+                       :: "r"(buf + my_row + ((k16 ^ sw) << 4)), "r"(w0), "r"(w1), "r"(w2), "r"(w3) : "memory");
+        };
+        if (p.out_bf16) {
 #pragma unroll
-            for (int k = 0; k < 4; ++k)
-              dst[k] = make_uint4(pack_bf16x2(v[8 * k], v[8 * k + 1]), pack_bf16x2(v[8 * k + 2], v[8 * k + 3]),
-                                  pack_bf16x2(v[8 * k + 4], v[8 * k + 5]), pack_bf16x2(v[8 * k + 6], v[8 * k + 7]));
-          } else {
-            float4* dst = reinterpret_cast<float4*>(static_cast<float*>(p.out) + at);
-#pragma unroll
-            for (int k = 0; k < 8; ++k) dst[k] = make_float4(v[4 * k], v[4 * k + 1], v[4 * k + 2], v[4 * k + 3]);
+          for (int k = 0; k < 4; ++k) {
+            put(k, pack_bf16x2(__uint_as_float(r0[8 * k]), __uint_as_float(r0[8 * k + 1])),
+                pack_bf16x2(__uint_as_float(r0[8 * k + 2]), __uint_as_float(r0[8 * k + 3])),
+                pack_bf16x2(__uint_as_float(r0[8 * k + 4]), __uint_as_float(r0[8 * k + 5])),
+                pack_bf16x2(__uint_as_float(r0[8 * k + 6]), __uint_as_float(r0[8 * k + 7])));
+            put(4 + k, pack_bf16x2(__uint_as_float(r1[8 * k]), __uint_as_float(r1[8 * k + 1])),
+                pack_bf16x2(__uint_as_float(r1[8 * k + 2]), __uint_as_float(r1[8 * k + 3])),
+                pack_bf16x2(__uint_as_float(r1[8 * k + 4]), __uint_as_float(r1[8 * k + 5])),
+                pack_bf16x2(__uint_as_float(r1[8 * k + 6]), __uint_as_float(r1[8 * k + 7])));
           }
+        } else {
+#pragma unroll
+          for (int k = 0; k < 8; ++k) put(k, r0[4 * k], r0[4 * k + 1], r0[4 * k + 2], r0[4 * k + 3]);
+        }
+        fence_proxy_async_smem();
+        __syncwarp();
+        if (lane == 0) {
+          tma_store_2d(&out_map, buf, j0 + c0, static_cast<int>(mw));
+          tma_store_commit();
         }
       }
-      // the accumulator has been read into registers: hand it back to the MMA warp
-      tc_fence_before_sync();
-      __syncwarp();
-      if (lane == 0) mbar_arrive(smem_u32(&s_acc_empty[a]));
     }
+    if (lane == 0) tma_store_wait<0>();  // every store has left shared memory and reached global memory
   }
   tc_fence_before_sync();
   __syncthreads();
@@ -204,14 +241,18 @@ int input_proj_launch(const void* x, const void* w, const float* bias, void* out
   if (mt > 0x7fffffffLL) return -2;
   p.n_jt = J / np;
   p.n_tiles = mt * p.n_jt;
-  CUtensorMap x_map, w_map;
+  CUtensorMap x_map, w_map, out_map;
   const uint64_t xdims[3] = {static_cast<uint64_t>(I), static_cast<uint64_t>(M), 1u};
   const uint32_t xbox[3] = {static_cast<uint32_t>(kProjKC), 128u, 1u};
   const uint64_t wdims[3] = {static_cast<uint64_t>(I), static_cast<uint64_t>(J), 1u};
   const uint32_t wbox[3] = {static_cast<uint32_t>(kProjKC), static_cast<uint32_t>(np), 1u};
   if (make_tensor_map(&x_map, x, 2, 3, xdims, xbox, true) != 0) return -4;
   if (make_tensor_map(&w_map, w, 2, 3, wdims, wbox, true) != 0) return -4;
-  const int smem = kProjStages * (16384 + np * 128) + 1024;
+  // the output as [M][J]; one store = 32 rows x 128 bytes out of a swizzled staging buffer
+  const uint64_t odims[2] = {static_cast<uint64_t>(J), static_cast<uint64_t>(M)};
+  const uint32_t obox[2] = {out_bf16 ? 64u : 32u, 32u};
+  if (make_tensor_map(&out_map, out, out_bf16 ? 2 : 4, 2, odims, obox, true) != 0) return -4;
+  const int smem = kProjStages * (16384 + np * 128) + 4 * 8192 + 1024;  // ring + two staging buffers per epilogue warp
   cudaError_t e = cudaFuncSetAttribute(input_proj_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, smem);
   if (e != cudaSuccess) return static_cast<int>(e);
   int dev = 0, sms = 0;
@@ -219,7 +260,7 @@ int input_proj_launch(const void* x, const void* w, const float* bias, void* out
   if (e == cudaSuccess) e = cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev);
   if (e != cudaSuccess) return static_cast<int>(e);
   const unsigned grid = static_cast<unsigned>(p.n_tiles < sms ? p.n_tiles : sms);  // persistent: one CTA per SM
-  input_proj_kernel<<<grid, kProjThreads, smem, s>>>(p, x_map, w_map);
+  input_proj_kernel<<<grid, kProjThreads, smem, s>>>(p, x_map, w_map, out_map);
   return static_cast<int>(cudaGetLastError());
 }
 
