@@ -10,7 +10,9 @@ pytestmark = pytest.mark.gpu
 
 
 # (B, T, I, J): full tiles, ragged rows, K tail, 128- and 64-column tiles
-@pytest.mark.parametrize("shape", [(8, 64, 768, 3072), (3, 37, 200, 768), (2, 5, 72, 192), (1, 1, 8, 64), (16, 129, 512, 1152)])
+@pytest.mark.parametrize("shape", [(8, 64, 768, 3072), (3, 37, 200, 768), (2, 5, 72, 192), (1, 1, 8, 64), (16, 129, 512, 1152),
+                                   # more tiles than SMs: every CTA walks several tiles through both accumulators
+                                   (32, 256, 256, 2048), (61, 131, 64, 192)])
 @pytest.mark.parametrize("out_dtype", [torch.bfloat16, torch.float32], ids=["bf16", "f32"])
 def test_projection_matches_matmul(shape, out_dtype, cuda_device):
     from flashrnn_b200 import input_projection, poll_errors
