@@ -333,13 +333,16 @@ def main():
     if dist is not None:
         breakdown["allreduce_dR_db"] = time_allreduce(dev, dist, GR * N * D * D + 4 * N * D)
     del d_wx, h_wx, dev_sets
-    wide = None if args.no_extras else wide_head_sharded(dev, dist, rank, world)
-    heads = None if args.no_extras else head_sharded_config(dev, dist, rank, world)
-
     t_ms = torch.tensor([ms, ms_e2e], dtype=torch.float64, device=dev)
     if dist is not None:
         dist.all_reduce(t_ms, op=dist.ReduceOp.MAX)
     ms, ms_e2e = (float(v) for v in t_ms.tolist())
+    # side measurements come last, after every figure of the headline line is final
+    wide = None if args.no_extras else wide_head_sharded(dev, dist, rank, world)
+    try:
+        heads = None if args.no_extras else head_sharded_config(dev, dist, rank, world)
+    except (ValueError, RuntimeError) as exc:   # reported, never fatal for the headline line
+        heads = {"error": repr(exc)[:300]}
     if rank == 0:
         bf16_peak, hbm_peak, peak_kind = _peaks()
         value = world * B * T * args.steps / (ms * 1e-3)
