@@ -338,6 +338,7 @@ def main():
         dist.all_reduce(t_ms, op=dist.ReduceOp.MAX)
     ms, ms_e2e = (float(v) for v in t_ms.tolist())
     # side measurements come last, after every figure of the headline line is final
+    proj = None if args.no_extras else with_input_projection(dev)
     wide = None if args.no_extras else wide_head_sharded(dev, dist, rank, world)
     try:
         heads = None if args.no_extras else head_sharded_config(dev, dist, rank, world)
@@ -371,6 +372,8 @@ def main():
         }
         if shard_check is not None:
             line["sharded_equals_unsharded"] = shard_check
+        if proj is not None:
+            line["with_input_projection"] = proj
         if wide is not None:
             line["wide_head_row_sharded"] = wide
         if heads is not None:
@@ -469,6 +472,40 @@ def head_sharded_config(dev, dist, rank, world, steps=3, warmup=2):
     torch.cuda.empty_cache()
     return {"workload": f"lstm bf16 N32 D128 B256 T2048, {Nh} heads per GPU, no collective", "ms_per_step": ms,
             "value": Bh * Th / ms * 1e3, "unit": "(B*T)/s", "steps": steps, "warmup": warmup}
+
+
+def with_input_projection(dev, steps=5, warmup=2):
+    """Extra keys: the headline workload with the input projection in front (the reference benchmark's "-withlinear"
+    variant, flashrnn/speed_experiments/kernel_speed_benchmark.py:388-408): x[B,T,N*D] -> Wx by this library's tcgen05
+    GEMM -> recurrence, forward + backward with gradients for x, W, R, b and the initial state. Every rank runs it on
+    its own data; rank 0's figure is reported."""
+    from flashrnn_b200 import flashrnn_projected
+
+    try:
+        gen = torch.Generator(device=dev).manual_seed(11)
+        I = N * D
+        x = torch.randn((B, T, I), generator=gen, device=dev)
+        W = torch.randn((4 * N * D, I), generator=gen, device=dev) * I ** -0.5
+        R = torch.randn((4, N, D, D), generator=gen, device=dev) * D ** -0.5
+        b = torch.randn((4, N, D), generator=gen, device=dev) * 0.1
+        init = torch.randn((2, B, 1, N, D), generator=gen, device=dev) * 0.5
+        times = []
+        for i in range(warmup + steps):
+            leaves = [t.detach().requires_grad_(True) for t in (x, W, R, b, init)]
+            torch.cuda.synchronize()
+            e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+            e0.record()
+            hist, _ = flashrnn_projected(leaves[0], leaves[1], leaves[2], leaves[3], leaves[4], function=CELL)
+            hist[0].sum().backward()
+            e1.record()
+            e1.synchronize()
+            if i >= warmup:
+                times.append(e0.elapsed_time(e1))
+        ms = sum(times) / len(times)
+        return {"workload": f"x[B,T,{I}] @ W[{4 * N * D},{I}].T -> {WORKLOAD}, fwd+bwd incl. dx, dW", "ms_per_step": ms,
+                "value": B * T / ms * 1e3, "unit": "(B*T)/s", "steps": steps, "warmup": warmup}
+    except (ValueError, RuntimeError) as exc:   # reported, never fatal for the headline line
+        return {"error": repr(exc)[:300]}
 
 
 def wide_head_sharded(dev, dist, rank, world):
