@@ -55,6 +55,10 @@ EMULATED = [
     ("lstm", 8, 6, 2048, 1, 0, 0, True),     # one GPU, D = 2048: 960 weight columns in tensor memory + a resident stage
     ("lstm", 4, 5, 2048, 1, 64, 3, False),   # the same with the weights streamed through a three-stage ring every step
     ("gru", 4, 5, 2048, 2, 128, 4, True),    # streamed, two ranks
+    # longer sequences on the widths the row-sharded configuration is about (the oracle needs seconds for each)
+    ("lstm", 8, 128, 2048, 1, 0, 0, True),   # D = 2048 on one GPU, resident forward / streamed backward
+    ("lstm", 4, 64, 4096, 1, 0, 0, True),    # D = 4096 on one GPU: the weights streamed every step in both directions
+    ("lstm", 4, 48, 4096, 4, 0, 0, True),    # D = 4096 as four ranks of 1024 units
 ]
 
 
