@@ -186,7 +186,8 @@ int frnn_b200_wgrad_noalloc(int cell, const void* dgr, const void* hbf, const fl
 
 /* Input projection in front of the recurrence: wx[b,t,j] = sum_i x[b,t,i] * w[j,i] (+ bias[j]), j = (gate, head,
  * unit), i.e. Wx[B,T,GW,N,D] in the layout frnn_b200_forward streams, as bf16 (wx_bf16 = 1) or fp32. x [B,T,inputs] and
- * w [GW*N*D, inputs] are bf16, bias fp32 [GW*N*D] or NULL; inputs % 8 == 0, gates_times_width % 64 == 0 (else -2).
+ * w [GW*N*D, inputs] are bf16, bias fp32 [GW*N*D] or NULL; inputs % 8 == 0, gates_times_width % 64 == 0, wx and bias
+ * 16-byte aligned (else -2).
  * The reference leaves this GEMM to the caller (README.md:16) and times it as the "-withlinear" variant of its
  * benchmark: a torch.nn.Linear in front of the kernel (flashrnn/speed_experiments/kernel_speed_benchmark.py:388-408). */
 int frnn_b200_input_projection(const void* x_bf16, const void* w_bf16, const float* bias, void* wx, int wx_bf16, int B,
