@@ -339,6 +339,7 @@ def main():
     ms, ms_e2e = (float(v) for v in t_ms.tolist())
     # side measurements come last, after every figure of the headline line is final
     proj = None if args.no_extras else with_input_projection(dev)
+    infer = None if args.no_extras else inference_e2e(dev)
     wide = None if args.no_extras else wide_head_sharded(dev, dist, rank, world)
     try:
         heads = None if args.no_extras else head_sharded_config(dev, dist, rank, world)
@@ -374,6 +375,8 @@ def main():
             line["sharded_equals_unsharded"] = shard_check
         if proj is not None:
             line["with_input_projection"] = proj
+        if infer is not None:
+            line["inference_e2e"] = infer
         if wide is not None:
             line["wide_head_row_sharded"] = wide
         if heads is not None:
@@ -504,6 +507,49 @@ def with_input_projection(dev, steps=5, warmup=2):
         ms = sum(times) / len(times)
         return {"workload": f"x[B,T,{I}] @ W[{4 * N * D},{I}].T -> {WORKLOAD}, fwd+bwd incl. dx, dW", "ms_per_step": ms,
                 "value": B * T / ms * 1e3, "unit": "(B*T)/s", "steps": steps, "warmup": warmup}
+    except (ValueError, RuntimeError) as exc:   # reported, never fatal for the headline line
+        return {"error": repr(exc)[:300]}
+
+
+def inference_e2e(dev, steps=5, warmup=2):
+    """Extra keys: a forward-only pass of the headline workload from pinned HOST memory back to pinned host memory
+    (host->device copy of Wx, the prepared sequence replayed as a CUDA graph, device->host copy of the result, all
+    inside the timed region), once per output mode: what the output modes and bf16 snapshots of PreparedSequence
+    (flashrnn/flashrnn2/prepared.py:18-192 in the reference) save in state writes and in the copy back."""
+    from flashrnn_b200 import PreparedSequence
+    from flashrnn_b200.workloads import make_inputs
+
+    try:
+        wx, R, b, init = make_inputs(CELL, B, T, N, D, SEED)
+        h_wx = wx.to(torch.bfloat16).pin_memory()
+        d_wx = torch.empty_like(h_wx, device=dev)
+        d_R, d_b, d_init = (t.to(dev) for t in (R, b, init))
+        rows = []
+        for mode, snap in (("full", torch.float32), ("hidden", torch.float32), ("hidden", torch.bfloat16),
+                           ("last", torch.float32)):
+            seq = PreparedSequence(d_wx, d_R, d_b, d_init, CELL, output_mode=mode, snapshot_dtype=snap)
+            d_wx.copy_(h_wx)
+            seq.capture()
+            h_out = torch.empty(seq.output.shape, dtype=seq.output.dtype).pin_memory()
+            times = []
+            for i in range(warmup + steps):
+                torch.cuda.synchronize()
+                e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+                e0.record()
+                d_wx.copy_(h_wx, non_blocking=True)
+                seq.run()
+                h_out.copy_(seq.output, non_blocking=True)
+                e1.record()
+                e1.synchronize()
+                if i >= warmup:
+                    times.append(e0.elapsed_time(e1))
+            seq.check()
+            seq.close()
+            ms = sum(times) / len(times)
+            rows.append({"output_mode": mode, "snapshot": str(snap)[6:], "ms_per_pass": ms, "value": B * T / ms * 1e3,
+                         "h2d_bytes": h_wx.numel() * 2, "d2h_bytes": h_out.numel() * h_out.element_size()})
+            del seq, h_out
+        return {"workload": f"{WORKLOAD}, forward only, CUDA-graph replay", "unit": "(B*T)/s", "passes": rows}
     except (ValueError, RuntimeError) as exc:   # reported, never fatal for the headline line
         return {"error": repr(exc)[:300]}
 
