@@ -101,7 +101,8 @@ __device__ __forceinline__ void cell_forward(const float* ry, const float* wx, c
     const float u = sigmoid_f((wx[1] + ry[2]) + b[2]);
     const float v = tanh_f((wx[2] + b[3]) + r * cand);
     st[0] = u * st[0] + (1.0f - u) * v;
-    cache[0] = cand; cache[1] = r; cache[2] = u; cache[3] = v;
+    // the cache holds fp16 values: keep an (absurdly) large candidate finite there
+    cache[0] = fminf(fmaxf(cand, -60000.0f), 60000.0f); cache[1] = r; cache[2] = u; cache[3] = v;
   } else {
     st[0] = tanh_f((wx[0] + ry[0]) + b[0]);
     cache[0] = 0.0f;
