@@ -77,7 +77,11 @@ frnn_fwd_mg_kernel(const MgFwdParams p, const __grid_constant__ CUtensorMap wx_m
   uint8_t* const ring = smem;                               // 1024-byte aligned stages of 16 KB
   uint8_t* const hbuf = smem + NA * kMgRingBytes;
   float* const part = reinterpret_cast<float*>(hbuf + 2 * hb_bytes);
-  __nv_bfloat16* const pub = reinterpret_cast<__nv_bfloat16*>(reinterpret_cast<uint8_t*>(part) + 2 * Cfg::PART_BYTES);
+  // outgoing partial rows, two parities like `part`: [destination][row][its batch rows]. A block is written again two
+  // steps later, after this CTA has used the partners' sums of the step in between, which they can only have sent
+  // after taking delivery of the block's previous content.
+  float* const part_out = part + 2 * Cfg::PART_FLOATS;
+  __nv_bfloat16* const pub = reinterpret_cast<__nv_bfloat16*>(reinterpret_cast<uint8_t*>(part) + 4 * Cfg::PART_BYTES);
   uint8_t* const wxs = reinterpret_cast<uint8_t*>(pub) + ((Cfg::PUB_BYTES + 127) & ~127);
   const volatile int* abort_flag = p.err;
   const uint64_t limit = p.wait_limit_ns;
@@ -306,7 +310,6 @@ frnn_fwd_mg_kernel(const MgFwdParams p, const __grid_constant__ CUtensorMap wx_m
     }
   } else if (ready_ok) {
     const bool row_valid = tid < Cfg::ROWS;
-    const uint32_t part_local = smem_u32(part) + static_cast<uint32_t>((ks * 128 + tid) * BO) * 4u;
     bool dead = false;  // after a failed wait the warp keeps walking through the loop without waiting
 
     // round_bf16(h) of the owned items -> slot `slot` of every rank's history buffer
@@ -333,7 +336,7 @@ frnn_fwd_mg_kernel(const MgFwdParams p, const __grid_constant__ CUtensorMap wx_m
     };
     // this CTA's K-chunk of slot `slot` -> operand buffers, one sub-chunk at a time
     const bool prof = p.err[3] != 0 && blockIdx.x == 0 && tid == 0;
-    long long pf_free = 0, pf_poll = 0, pf_mma = 0, pf_part = 0;
+    long long pf_free = 0, pf_poll = 0, pf_mma = 0, pf_part = 0, pf_scat = 0, pf_cell = 0, pf_pub = 0, pf_st = 0;
     auto fetch = [&](int slot) {
       for (int sc = 0; sc < NSC; ++sc) {
         const long long q = static_cast<long long>(slot) * NSC + sc;
@@ -395,42 +398,51 @@ frnn_fwd_mg_kernel(const MgFwdParams p, const __grid_constant__ CUtensorMap wx_m
         mg_report(p.err, kErrWaitMma, t);
         dead = true;
       }
-      if (prof) pf_mma += clock64() - e0;
+      const long long e0b = prof ? clock64() : 0;
+      if (prof) pf_mma += e0b - e0;
       tc_fence_after_sync();
-      // partial gates of this row: batch columns [ks'*BO, (ks'+1)*BO) go to CTA ks' of the cluster
+      // partial gates of this row: batch columns [ks'*BO, (ks'+1)*BO) go to CTA ks' of the cluster. The rows are
+      // collected in shared memory as one block per destination, then ONE bulk copy per destination carries a block
+      // into the owner's `part` buffer (a store per 16 bytes would make a thousand updates of the owner's barrier).
       {
         uint32_t r[4][8];
 #pragma unroll
         for (int c = 0; c < 4; ++c) tmem_ld_x8(tmem_addr(tbase, 32 * warp, 8 * c), r[c]);
         tmem_ld_wait();
         tc_fence_before_sync();
-        if (row_valid && !dead) {
-          const uint32_t off = static_cast<uint32_t>(pb) * Cfg::PART_BYTES;
-          const uint32_t bar_local = smem_u32(&s_part_bar[pb]);
+        if (row_valid) {
 #pragma unroll
           for (int d = 0; d < KS; ++d) {
-            const uint32_t dst = map_to_cta(part_local + off, d);
-            const uint32_t bar = map_to_cta(bar_local, d);
+            float* dstrow = part_out + pb * Cfg::PART_FLOATS + (d * 128 + tid) * BO;
             if constexpr (BO >= 4) {
 #pragma unroll
               for (int v = 0; v < BO / 4; ++v) {
                 const int c0 = d * BO + 4 * v;
-                st_async_v4_b32(dst + v * 16, r[c0 / 8][c0 % 8], r[c0 / 8][c0 % 8 + 1], r[c0 / 8][c0 % 8 + 2],
-                                r[c0 / 8][c0 % 8 + 3], bar);
+                *reinterpret_cast<uint4*>(dstrow + 4 * v) =
+                    make_uint4(r[c0 / 8][c0 % 8], r[c0 / 8][c0 % 8 + 1], r[c0 / 8][c0 % 8 + 2], r[c0 / 8][c0 % 8 + 3]);
               }
             } else {
               const int c0 = d * BO;
-              st_async_v2_b32(dst, r[c0 / 8][c0 % 8], r[c0 / 8][c0 % 8 + 1], bar);
+              *reinterpret_cast<uint2*>(dstrow) = make_uint2(r[c0 / 8][c0 % 8], r[c0 / 8][c0 % 8 + 1]);
             }
           }
         }
+        fence_proxy_async_smem();
+        asm volatile("bar.sync 1, 128;" ::: "memory");
+        if (tid < KS && !dead) {
+          const uint32_t off = static_cast<uint32_t>(pb) * Cfg::PART_BYTES + static_cast<uint32_t>(ks * 128 * BO) * 4u;
+          bulk_copy_to_cluster(map_to_cta(smem_u32(part) + off, tid), smem_u32(part_out + pb * Cfg::PART_FLOATS + tid * 128 * BO),
+                               static_cast<uint32_t>(Cfg::ROWS * BO) * 4u, map_to_cta(smem_u32(&s_part_bar[pb]), tid));
+        }
       }
       const long long e1 = prof ? clock64() : 0;
+      if (prof) pf_scat += e1 - e0b;
       if (!dead && !mbar_wait_bounded<true, true>(smem_u32(&s_part_bar[pb]), (t >> 1) & 1, limit, abort_flag)) {
         mg_report(p.err, kErrWaitPart, t);
         dead = true;
       }
-      if (prof) pf_part += clock64() - e1;
+      const long long e2 = prof ? clock64() : 0;
+      if (prof) pf_part += e2 - e1;
       float ry[NI][CT::GR];
       {
         const float* pbuf = part + pb * Cfg::PART_FLOATS;
@@ -461,8 +473,13 @@ frnn_fwd_mg_kernel(const MgFwdParams p, const __grid_constant__ CUtensorMap wx_m
         hb16[j] = act[j] ? static_cast<uint32_t>(__bfloat16_as_ushort(__float2bfloat16_rn(st[j][0]))) : 0u;
       }
       // slot T (h of the last step) has no reader: not the recurrence, and the dR contraction stops at slot T - 1
+      const long long e3 = prof ? clock64() : 0;
       publish(t + 1, hb16, !dead && t < mute_from && t + 1 < T);
-      // state stores first: they leave the SM while the packets of the other CTAs are still on their way
+      const long long e4 = prof ? clock64() : 0;
+      if (prof) { pf_cell += e3 - e2; pf_pub += e4 - e3; }
+      if (t + 1 < T) fetch(t + 1);
+      const long long e5 = prof ? clock64() : 0;
+      // state and cache stores last: the tensor core now works on h_t and this thread would only wait for it
 #pragma unroll
       for (int j = 0; j < NI; ++j) {
         if (act[j]) {
@@ -475,13 +492,18 @@ frnn_fwd_mg_kernel(const MgFwdParams p, const __grid_constant__ CUtensorMap wx_m
           }
         }
       }
-      if (t + 1 < T) fetch(t + 1);
+      if (prof) pf_st += clock64() - e5;
     }
     if (prof) {  // epilogue thread 0: err[8] buffer-free wait, [9] operand poll + copy, [10] tensor-core wait, [11] partner sums
       p.err[8] = static_cast<int>(pf_free >> 10);
       p.err[9] = static_cast<int>(pf_poll >> 10);
       p.err[10] = static_cast<int>(pf_mma >> 10);
       p.err[11] = static_cast<int>(pf_part >> 10);
+      // [12] accumulator read + partial rows sent, [13] sums + cell, [14] publication of h, [15] state and cache stores
+      p.err[12] = static_cast<int>(pf_scat >> 10);
+      p.err[13] = static_cast<int>(pf_cell >> 10);
+      p.err[14] = static_cast<int>(pf_pub >> 10);
+      p.err[15] = static_cast<int>(pf_st >> 10);
     }
 #pragma unroll
     for (int j = 0; j < NI; ++j) {
@@ -509,7 +531,7 @@ int launch_fwd_mg(const MgFwdParams& p, const void* wx, cudaStream_t stream, int
   using CT = typename Cfg::CT;
   const int Kc = p.D / KS;
   const int SCK = Kc < kMgSubK ? Kc : kMgSubK;
-  int smem = p.ring_stages * kMgRingBytes + 2 * mg_operand_bytes(SCK) + 2 * Cfg::PART_BYTES + ((Cfg::PUB_BYTES + 127) & ~127) +
+  int smem = p.ring_stages * kMgRingBytes + 2 * mg_operand_bytes(SCK) + 4 * Cfg::PART_BYTES + ((Cfg::PUB_BYTES + 127) & ~127) +
              Cfg::NWX * Cfg::WX_STAGE_BYTES;
   if (smem > 227 * 1024) return -2;
   CUtensorMap wx_map, r_map;
@@ -602,7 +624,7 @@ int forward_mg_fixed_smem(int cell, int ksplit, int D, int wx_bf16) {
   const int SCK = Kc < kMgSubK ? Kc : kMgSubK;
   const int wx_stage = bo * gw * 32 * (wx_bf16 ? 2 : 4);
   const int nwx = wx_stage * 4 <= 32768 ? 4 : 2;
-  return 2 * mg_operand_bytes(SCK) + 2 * (ksplit * 128 * bo * 4) + ((bo * 32 * 2 + 127) & ~127) + nwx * wx_stage;
+  return 2 * mg_operand_bytes(SCK) + 4 * (ksplit * 128 * bo * 4) + ((bo * 32 * 2 + 127) & ~127) + nwx * wx_stage;
 }
 
 }  // namespace frnn

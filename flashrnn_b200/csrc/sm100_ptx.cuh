@@ -193,6 +193,16 @@ __device__ __forceinline__ void tma_load_3d(uint32_t dst, const void* tmap, uint
       : "memory");
 }
 
+// Bulk copy from this CTA's shared memory into the shared memory of a CTA of the cluster (or itself); the bytes are
+// counted on the DESTINATION's mbarrier (`bar_cluster`, a shared::cluster address like `dst_cluster`). 16-byte
+// aligned addresses, size a multiple of 16. Generic-proxy writes to the source must be fenced
+// (fence_proxy_async_smem) and ordered before the issuing thread by a barrier.
+__device__ __forceinline__ void bulk_copy_to_cluster(uint32_t dst_cluster, uint32_t src_cta, uint32_t bytes,
+                                                     uint32_t bar_cluster) {
+  asm volatile("cp.async.bulk.shared::cluster.shared::cta.mbarrier::complete_tx::bytes [%0], [%1], %2, [%3];"
+               :: "r"(dst_cluster), "r"(src_cta), "r"(bytes), "r"(bar_cluster) : "memory");
+}
+
 // TMA tiled store (this CTA's shared memory -> global; rows and columns past the tensor's extent are dropped). The
 // issuing thread tracks completion with bulk groups; writes to the shared-memory source by other threads must be
 // made visible first (fence_proxy_async_smem + a barrier). x times the element size must be a multiple of 16 bytes
