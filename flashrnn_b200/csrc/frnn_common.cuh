@@ -149,6 +149,18 @@ __device__ __forceinline__ float ld_cache(const void* base, size_t off) {
   else return __half2float(static_cast<const __half*>(base)[off]);
 }
 
+// Test hook for race verification (err[6] = seed, 0 = off): in a quarter of the steps the calling warp role of this
+// CTA sits out a pseudo-random time of up to 8 us, chosen from (seed, CTA, role, step) and therefore the same for all
+// of the role's threads, so that CTAs and roles drift against each other at every hand-off of the exchange
+// protocols. Results must not depend on it.
+__device__ __forceinline__ void jitter_stall(uint32_t seed, uint32_t role, uint32_t step) {
+  uint32_t h = seed ^ (blockIdx.x * 0x9E3779B1u) ^ (role * 0x85EBCA77u) ^ (step * 0xC2B2AE3Du);
+  h ^= h >> 15; h *= 0x2C1B3C6Du; h ^= h >> 12; h *= 0x297A2D39u; h ^= h >> 15;
+  if ((h & 3u) != 0u) return;
+  const uint64_t ns = (h >> 8) & 0x1fffu, t0 = global_timer_ns();
+  while (global_timer_ns() - t0 < ns) __nanosleep(200);
+}
+
 template <int N>
 __device__ __forceinline__ void st_bf16_vec(__nv_bfloat16* p, const float* v) {
   static_assert(N % 2 == 0, "pairs");

@@ -102,7 +102,12 @@ frnn_bwd_kernel(const BwdParams p, const __grid_constant__ CUtensorMap cache_map
   const volatile int* abort_flag = p.err;
   const uint64_t limit = p.wait_limit_ns;
   // test hook: with err[4] = 1 no CTA scatters partial dh from iteration err[5] on, so the next wait runs out
-  const int mute_from = p.err[4] != 0 ? p.err[5] : 0x7fffffff;
+  const int mute_from = p.err[4] != 0 ? p.err[5] : 0x7fffffff;  // test hook: nobody publishes from this step on
+  // Second test hook, race verification by delay injection (err[6] = seed, see jitter_stall). It is compiled into the
+  // fp32-Wx instantiations only: the exchange code is the same for both Wx types, and even the untaken per-step test
+  // costs the bf16 backward more than 1 %.
+  constexpr bool kJitter = !WX_BF16;
+  const uint32_t jitter = kJitter ? static_cast<uint32_t>(p.err[6]) : 0u;
   const bool prof = p.err[3] != 0 && blockIdx.x == 0 && lane == 0 && (warp == 0 || warp == 4);
   const bool cut = OPTS && p.cut_recurrent != 0;
   const bool clip_on = OPTS && p.grad_clip > 0.0f;
@@ -206,6 +211,7 @@ frnn_bwd_kernel(const BwdParams p, const __grid_constant__ CUtensorMap cache_map
       long long pw = 0, pi = 0;
       int committed = 0;  // iterations whose tcgen05.mma have been issued and committed
       for (int it = 0; it < T; ++it) {
+        if (kJitter && jitter != 0u) jitter_stall(jitter, 1u, static_cast<uint32_t>(it));
         const long long m0 = prof ? clock64() : 0;
         if (!mbar_wait_bounded<false, true>(smem_u32(&s_dg_bar), it & 1, limit, abort_flag)) {
           report(p.err, kErrWaitDg, it);
@@ -274,6 +280,7 @@ frnn_bwd_kernel(const BwdParams p, const __grid_constant__ CUtensorMap cache_map
     // that the warp-wide tcgen05.ld below is always executed by all of its lanes.
     bool dead = false;
     for (int it = 0; it <= T; ++it) {
+      if (kJitter && jitter != 0u) jitter_stall(jitter, 0u, static_cast<uint32_t>(it));
       const int t = T - 1 - it;
       const long long c0 = prof ? clock64() : 0;
       float ds[S][IPT];

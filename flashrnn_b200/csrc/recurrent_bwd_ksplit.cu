@@ -96,7 +96,12 @@ frnn_bwd_ks_kernel(const BwdParams p, const __grid_constant__ CUtensorMap cache_
   // four operand slots per group in global memory, each [K-chunk][BT x Kc, K-major]; dG of iteration i goes to slot i % 4
   const size_t slot_bytes = static_cast<size_t>(BT) * K * 2;
   uint8_t* const xg_dg = p.xg_data + static_cast<size_t>(gid) * 4 * slot_bytes;
-  const int mute_from = p.err[4] != 0 ? p.err[5] : 0x7fffffff;  // test hook: nobody publishes dG from this iteration on
+  const int mute_from = p.err[4] != 0 ? p.err[5] : 0x7fffffff;  // test hook: nobody publishes from this step on
+  // Second test hook, race verification by delay injection (err[6] = seed, see jitter_stall). It is compiled into the
+  // fp32-Wx instantiations only: the exchange code is the same for both Wx types, and even the untaken per-step test
+  // costs the bf16 backward more than 1 %.
+  constexpr bool kJitter = !WX_BF16;
+  const uint32_t jitter = kJitter ? static_cast<uint32_t>(p.err[6]) : 0u;
   const bool prof = p.err[3] != 0 && blockIdx.x == 0 && lane == 0 && (warp == 0 || warp == 4);
   uint32_t tmem_cols = 64;
   while (tmem_cols < static_cast<uint32_t>(Cfg::A_COL0 + Kc / 2)) tmem_cols <<= 1;
@@ -194,6 +199,7 @@ frnn_bwd_ks_kernel(const BwdParams p, const __grid_constant__ CUtensorMap cache_
       long long pw = 0, pi = 0;
       int committed = 0;  // steps whose tcgen05.mma have been issued and committed
       for (int it = 0; it < T; ++it) {
+        if (kJitter && jitter != 0u) jitter_stall(jitter, 1u, static_cast<uint32_t>(it));
         const int pb = it & 1;
         const long long m0 = prof ? clock64() : 0;
         if (!mbar_wait_bounded<false, true>(smem_u32(&s_dg_bar[pb]), (it >> 1) & 1, limit, abort_flag)) {
@@ -311,6 +317,7 @@ frnn_bwd_ks_kernel(const BwdParams p, const __grid_constant__ CUtensorMap cache_
     load_stage(0);
 
     for (int it = 0; it <= T; ++it) {
+      if (kJitter && jitter != 0u) jitter_stall(jitter, 0u, static_cast<uint32_t>(it));
       const int t = T - 1 - it;
       const int pb = it & 1;
       const long long c0 = prof ? clock64() : 0;

@@ -80,7 +80,12 @@ frnn_fwd_kernel(const FwdParams p, const __grid_constant__ CUtensorMap wx_map) {
   // four operand slots per group in global memory: h_t goes to slot (t + 1) % 4, see the epilogue
   uint8_t* const xg_h = xg ? p.xg_data + static_cast<size_t>(gid) * 4 * hbuf_bytes : nullptr;
   // test hook: with err[4] = 1 no CTA publishes h from step err[5] on, so the next operand wait runs out
-  const int mute_from = p.err[4] != 0 ? p.err[5] : 0x7fffffff;
+  const int mute_from = p.err[4] != 0 ? p.err[5] : 0x7fffffff;  // test hook: nobody publishes from this step on
+  // Second test hook, race verification by delay injection (err[6] = seed, see jitter_stall). It is compiled into the
+  // fp32-Wx instantiations only: the exchange code is the same for both Wx types, and even the untaken per-step test
+  // costs the bf16 backward more than 1 %.
+  constexpr bool kJitter = !WX_BF16;
+  const uint32_t jitter = kJitter ? static_cast<uint32_t>(p.err[6]) : 0u;
   const bool zero_first = p.zero_first_dev != nullptr ? *p.zero_first_dev != 0 : p.slstm_zero_first != 0;
   const int hist_states = p.output_mode == 0 ? CT::S : (p.output_mode == 1 ? 1 : 0);  // state planes written per step
   const bool prof = p.err[3] != 0 && blockIdx.x == 0 && lane == 0 && (warp == 0 || warp == 4);
@@ -184,6 +189,7 @@ frnn_fwd_kernel(const FwdParams p, const __grid_constant__ CUtensorMap wx_map) {
       long long pw = 0, pi = 0, px = 0, pf = 0;
       int committed = 0;  // steps whose tcgen05.mma have been issued and committed
       for (int t = 0; t < T; ++t) {
+        if (kJitter && jitter != 0u) jitter_stall(jitter, 1u, static_cast<uint32_t>(t));
         const int pb = t & 1;
         const long long m0 = prof ? clock64() : 0;
         if (t >= 1) {
@@ -272,6 +278,7 @@ frnn_fwd_kernel(const FwdParams p, const __grid_constant__ CUtensorMap wx_map) {
     // flag is set, and nothing that is computed from then on matters.
     bool dead = false;
     for (int t = 0; t < T; ++t) {
+      if (kJitter && jitter != 0u) jitter_stall(jitter, 0u, static_cast<uint32_t>(t));
       const int s = t % kWxStages;
       const long long c0 = prof ? clock64() : 0;
       if (!dead && !mbar_wait_bounded<false>(smem_u32(&s_wx_full[s]), (t / kWxStages) & 1, limit, abort_flag)) {

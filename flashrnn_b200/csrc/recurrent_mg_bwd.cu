@@ -87,7 +87,12 @@ frnn_bwd_mg_kernel(const MgBwdParams p, const __grid_constant__ CUtensorMap cach
   uint8_t* const stages = reinterpret_cast<uint8_t*>(pub) + ((Cfg::PUB_BYTES + 127) & ~127);
   const volatile int* abort_flag = p.err;
   const uint64_t limit = p.wait_limit_ns;
-  const int mute_from = p.err[4] != 0 ? p.err[5] : 0x7fffffff;  // test hook: nobody publishes dG from this iteration on
+  const int mute_from = p.err[4] != 0 ? p.err[5] : 0x7fffffff;  // test hook: nobody publishes from this step on
+  // Second test hook, race verification by delay injection (err[6] = seed, see jitter_stall). It is compiled into the
+  // fp32-Wx instantiations only: the exchange code is the same for both Wx types, and even the untaken per-step test
+  // costs the bf16 backward more than 1 %.
+  constexpr bool kJitter = !WX_BF16;
+  const uint32_t jitter = kJitter ? static_cast<uint32_t>(p.err[6]) : 0u;
   constexpr uint32_t tmem_cols = 512;
   const size_t grow = static_cast<size_t>(T) * K;  // elements per batch row of a dG history buffer
 
@@ -189,6 +194,7 @@ frnn_bwd_mg_kernel(const MgBwdParams p, const __grid_constant__ CUtensorMap cach
       uint32_t ring_phase = 0;
       bool ok = true;
       for (int it = 0; it < T && ok; ++it) {
+        if (kJitter && jitter != 0u) jitter_stall(jitter, 1u, static_cast<uint32_t>(it));
         for (int sc = 0; sc < NSC && ok; ++sc) {
           const long long q = static_cast<long long>(it) * NSC + sc;
           const int buf = static_cast<int>(q & 1);
@@ -337,6 +343,7 @@ frnn_bwd_mg_kernel(const MgBwdParams p, const __grid_constant__ CUtensorMap cach
     };
 
     for (int it = 0; it <= T; ++it) {
+      if (kJitter && jitter != 0u) jitter_stall(jitter, 0u, static_cast<uint32_t>(it));
       const int t = T - 1 - it;
       const int pb = it & 1;
       if (it >= 1 && !dead &&

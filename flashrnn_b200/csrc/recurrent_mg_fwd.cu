@@ -85,7 +85,12 @@ frnn_fwd_mg_kernel(const MgFwdParams p, const __grid_constant__ CUtensorMap wx_m
   uint8_t* const wxs = reinterpret_cast<uint8_t*>(pub) + ((Cfg::PUB_BYTES + 127) & ~127);
   const volatile int* abort_flag = p.err;
   const uint64_t limit = p.wait_limit_ns;
-  const int mute_from = p.err[4] != 0 ? p.err[5] : 0x7fffffff;  // test hook: nobody publishes h from this step on
+  const int mute_from = p.err[4] != 0 ? p.err[5] : 0x7fffffff;  // test hook: nobody publishes from this step on
+  // Second test hook, race verification by delay injection (err[6] = seed, see jitter_stall). It is compiled into the
+  // fp32-Wx instantiations only: the exchange code is the same for both Wx types, and even the untaken per-step test
+  // costs the bf16 backward more than 1 %.
+  constexpr bool kJitter = !WX_BF16;
+  const uint32_t jitter = kJitter ? static_cast<uint32_t>(p.err[6]) : 0u;
   const bool zero_first = p.slstm_zero_first != 0;
   constexpr uint32_t tmem_cols = 512;
   const size_t hrow = static_cast<size_t>(T + 1) * D;       // elements per batch row of a history buffer
@@ -185,6 +190,7 @@ frnn_fwd_mg_kernel(const MgFwdParams p, const __grid_constant__ CUtensorMap wx_m
       const bool prof = p.err[3] != 0 && blockIdx.x == 0;  // phase timers of CTA 0 (SM clock cycles, summed over all steps)
       long long pf_h = 0, pf_a = 0, pf_tot = prof ? clock64() : 0;
       for (int t = 0; t < T && ok; ++t) {
+        if (kJitter && jitter != 0u) jitter_stall(jitter, 1u, static_cast<uint32_t>(t));
         for (int sc = 0; sc < NSC && ok; ++sc) {
           const long long q = static_cast<long long>(t) * NSC + sc;
           const int buf = static_cast<int>(q & 1);
@@ -371,6 +377,7 @@ frnn_fwd_mg_kernel(const MgFwdParams p, const __grid_constant__ CUtensorMap wx_m
     }
     const size_t sBT = static_cast<size_t>(B) * T;
     for (int t = 0; t < T; ++t) {
+      if (kJitter && jitter != 0u) jitter_stall(jitter, 0u, static_cast<uint32_t>(t));
       const int s = t % Cfg::NWX, pb = t & 1;
       if (!dead && !mbar_wait_bounded<false>(smem_u32(&s_wx_full[s]), (t / Cfg::NWX) & 1, limit, abort_flag)) {
         mg_report(p.err, kErrWaitWx, t);

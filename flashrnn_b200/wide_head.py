@@ -47,6 +47,7 @@ class WideHead:
         self._epoch = 0
         self.profile = False   # True: CTA 0 of the forward adds up its in-kernel phase timers into last_err[8..19]
         self.last_err = None
+        self.jitter = 0        # test hook (race verification): seed of pseudo-random stalls inside both kernels, 0 = off
         self._owned = []      # cudaMalloc'ed slabs of this process
         self._opened = []     # peer mappings
         gr = SIZES[cell][0]
@@ -223,6 +224,8 @@ class _WideRecurrence(torch.autograd.Function):
             if head.profile:
                 err[3] = 1
                 head.last_err = err
+            if head.jitter:
+                err[6] = int(head.jitter)
             sh = head._shard("hbf", head.next_epoch())
             rc = lib.frnn_b200_mg_forward(
                 _lib.CELLS[head.cell], wx_c.data_ptr(), head.wx_bf16, head.r_stage.data_ptr(), b32.data_ptr(), init32.data_ptr(),
@@ -263,6 +266,8 @@ class _WideRecurrence(torch.autograd.Function):
             dR = torch.empty((gr, 1, lw, D), dtype=torch.float32, device=dev)
             db = torch.empty((gb, 1, lw), dtype=torch.float32, device=dev)
             err = torch.zeros(32, dtype=torch.int32, device=dev)
+            if head.jitter:
+                err[6] = int(head.jitter)
             sh = head._shard("dgr", head.next_epoch())
             rc = lib.frnn_b200_mg_backward(
                 cid, cache.data_ptr() if cache.numel() else None, history.data_ptr(), init32.data_ptr(), r_cols.data_ptr(),
