@@ -122,6 +122,11 @@ def test_every_output_mode_and_chunking_against_the_oracle(shape, cuda_device):
             snap.check()
             assert out16.dtype == torch.bfloat16 and final16.dtype == torch.float32
             assert torch.equal(out16, whole[mode][0].bfloat16()) and torch.equal(final16, whole[mode][1]), (shape, zero, mode, "bf16")
+        # one launch per step (every exchange of the persistent kernel replaced by a kernel boundary) == the persistent run
+        steps = PreparedSequence(wx, R, b, init, cell, output_mode="full", chunks=(1,) * T)
+        out, final = steps.run()
+        steps.check()
+        assert torch.equal(out, whole["full"][0]) and torch.equal(final, whole["full"][1]), (shape, zero, "per-step launches")
 
 
 def test_chunked_sequence_in_a_graph(cuda_device):
