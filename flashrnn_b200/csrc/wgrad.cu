@@ -205,7 +205,6 @@ wgrad_tma_kernel(const WgradParams p, const __grid_constant__ CUtensorMap dgr_ma
   __syncthreads();
   tc_fence_after_sync();
   const uint32_t tbase = s_tmem_base;
-  bool ok = true;
 
   if (warp == 0) {
     if (lane == 0) {
@@ -242,7 +241,6 @@ wgrad_tma_kernel(const WgradParams p, const __grid_constant__ CUtensorMap dgr_ma
         const int s = i % kTmaStages;
         if (!mbar_wait_bounded<false, true>(smem_u32(&s_full[s]), (i / kTmaStages) & 1, kLimit, abort_flag)) {
           atomicCAS(p.err, 0, kErrWaitWx);
-          ok = false;
           break;
         }
         tc_fence_after_sync();
