@@ -271,7 +271,7 @@ int forward_common(int cell, const void* wx, int wx_bf16, const void* r_bf16, co
   p.T_total = T_total > 0 ? T_total : T;
   p.t0 = t0;
   p.out_bf16 = out_bf16;
-  p.fwd_clip = opt != nullptr ? opt->forward_clipval : 0.0f;
+  p.fwd_clip = opt != nullptr && opt->forward_clipval > 0.0f ? opt->forward_clipval : INFINITY;  // branch-free in the kernels
   if (t0 < 0 || t0 + T > p.T_total) return -5;
   if ((cache != nullptr || hbf != nullptr) && (t0 != 0 || p.T_total != T || out_bf16)) return -5;
   p.wait_limit_ns = (wait_limit_ms > 0 ? static_cast<unsigned long long>(wait_limit_ms) : 2000ull) * 1000000ull;

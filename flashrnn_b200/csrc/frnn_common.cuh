@@ -50,7 +50,7 @@ struct FwdParams {
   // otherwise. The gate cache and the bf16 copy of h are only written by whole-sequence calls.
   int T_total, t0;
   int out_bf16;            // 1: the state history is stored as bf16 snapshots (forward-only calls)
-  float fwd_clip;          // > 0: h_t is clipped to [-fwd_clip, fwd_clip] (see clip_sym in cells.cuh)
+  float fwd_clip;          // h_t is clipped to [-fwd_clip, fwd_clip]; +inf = off
   unsigned long long wait_limit_ns;
   // Exchange through global memory (groups wider than a cluster), null for cluster exchange:
   // per group four slots of the bf16 operand (the data words double as arrival flags).

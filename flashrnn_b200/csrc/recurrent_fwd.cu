@@ -47,7 +47,9 @@ __device__ __forceinline__ void report(int* err, int code, int detail) {
   __threadfence();
 }
 
-template <int CELL, int BV, int U, bool WX_BF16, bool XG>
+// EXT: the call is one chunk of a longer sequence (T_total, t0), stores bf16 snapshots or clips h_t; the plain
+// instantiation folds all three away (they cost the narrow heads, whose step is the epilogue loop, 3 - 5 %).
+template <int CELL, int BV, int U, bool WX_BF16, bool XG, bool EXT>
 __global__ void __launch_bounds__(kFwdThreads, 1)
 frnn_fwd_kernel(const FwdParams p, const __grid_constant__ CUtensorMap wx_map) {
   using Cfg = FwdCfg<CELL, BV, U, WX_BF16>;
@@ -152,7 +154,8 @@ frnn_fwd_kernel(const FwdParams p, const __grid_constant__ CUtensorMap wx_map) {
   const int d0 = rank * U + ul;     // unit offset inside the head
   float st[CT::S][IPT];
   float bias[CT::GB][IPT];
-  const int Tt = p.T_total, t0 = p.t0;
+  const int Tt = EXT ? p.T_total : T, t0 = EXT ? p.t0 : 0;
+  const bool out_bf16 = EXT && p.out_bf16 != 0;
   const size_t sBTND = static_cast<size_t>(B) * Tt * N * D;
   const size_t item_bn = (static_cast<size_t>(b0 + ib) * N + n) * D + d0;  // into [B][1][N][D]
   if (active) {
@@ -253,7 +256,6 @@ frnn_fwd_kernel(const FwdParams p, const __grid_constant__ CUtensorMap wx_map) {
   } else {
     const size_t hist_off = ((static_cast<size_t>(b0 + ib) * Tt + t0) * N + n) * D + d0;  // elements, fp32 or bf16
     float* hist = p.history + hist_off;
-    __nv_bfloat16* hist16 = reinterpret_cast<__nv_bfloat16*>(p.history) + hist_off;
     const size_t cache_off = ((static_cast<size_t>(b0 + ib) * T * CT::GC) * N + n) * D + d0;  // elements
     __nv_bfloat16* hbf = p.hbf == nullptr ? nullptr : p.hbf + ((static_cast<size_t>(b0 + ib) * (T + 1) + 1) * N + n) * D + d0;
     const uint32_t h_off = kmajor_offset(BT, ib, d0);
@@ -346,7 +348,7 @@ frnn_fwd_kernel(const FwdParams p, const __grid_constant__ CUtensorMap wx_map) {
 #pragma unroll
           for (int q = 0; q < CT::S; ++q) sj[q] = st[q][j];
           cell_forward<CELL>(ryj, wxj, bj, sj, cj, take_i);
-          sj[0] = clip_sym(sj[0], p.fwd_clip);
+          if constexpr (EXT) sj[0] = fminf(fmaxf(sj[0], -p.fwd_clip), p.fwd_clip);  // +inf when the clip is off
 #pragma unroll
           for (int q = 0; q < CT::S; ++q) st[q][j] = sj[q];
 #pragma unroll
@@ -456,7 +458,8 @@ frnn_fwd_kernel(const FwdParams p, const __grid_constant__ CUtensorMap wx_map) {
 #pragma unroll
         for (int q = 0; q < CT::S; ++q) {
           if (q < hist_states) {
-            if (p.out_bf16) st_bf16_vec<IPT>(hist16 + q * sBTND + t * ND, st[q]);
+            // bf16 snapshots: the same element offsets from the same base, two bytes each (keeps one pointer live)
+            if (out_bf16) st_bf16_vec<IPT>(reinterpret_cast<__nv_bfloat16*>(p.history) + (hist - p.history) + q * sBTND + t * ND, st[q]);
             else st_f32_vec<IPT>(hist + q * sBTND + t * ND, st[q]);
           }
         }
@@ -484,7 +487,7 @@ frnn_fwd_kernel(const FwdParams p, const __grid_constant__ CUtensorMap wx_map) {
 #pragma unroll
       for (int q = 0; q < CT::S; ++q) st_f32_vec<IPT>(p.carry + static_cast<size_t>(q) * B * N * D + item_bn, st[q]);
       if (p.output_mode == 2) {  // "last": h of the final step as [B][1][N][D]
-        if (p.out_bf16) st_bf16_vec<IPT>(reinterpret_cast<__nv_bfloat16*>(p.history) + item_bn, st[0]);
+        if (out_bf16) st_bf16_vec<IPT>(reinterpret_cast<__nv_bfloat16*>(p.history) + item_bn, st[0]);
         else st_f32_vec<IPT>(p.history + item_bn, st[0]);
       }
     }
@@ -502,8 +505,8 @@ frnn_fwd_kernel(const FwdParams p, const __grid_constant__ CUtensorMap wx_map) {
   if (warp == 4) tmem_dealloc(tbase, tmem_cols);
 }
 
-template <int CELL, int BV, int U, bool WX_BF16, bool XG>
-int launch_fwd(const FwdParams& p, const void* wx, cudaStream_t stream) {
+template <int CELL, int BV, int U, bool WX_BF16, bool XG, bool EXT>
+int launch_fwd_ext(const FwdParams& p, const void* wx, cudaStream_t stream) {
   using Cfg = FwdCfg<CELL, BV, U, WX_BF16>;
   using CT = typename Cfg::CT;
   const int hbuf_bytes = Cfg::BT * p.D * 2;
@@ -514,7 +517,7 @@ int launch_fwd(const FwdParams& p, const void* wx, cudaStream_t stream) {
                             static_cast<uint64_t>(p.T_total), static_cast<uint64_t>(p.B)};
   const uint32_t box[5] = {static_cast<uint32_t>(U), 1u, static_cast<uint32_t>(CT::GW), 1u, static_cast<uint32_t>(p.wx_box_b)};
   if (make_tensor_map(&map, wx, Cfg::WX_ES, 5, dims, box) != 0) return -4;
-  auto kern = frnn_fwd_kernel<CELL, BV, U, WX_BF16, XG>;
+  auto kern = frnn_fwd_kernel<CELL, BV, U, WX_BF16, XG, EXT>;
   const int fit = fit_tmem_budget(kern, kFwdThreads, tmem_cols_pow2(Cfg::A_COL0 + Cfg::MT * (p.D / 2), 32u), &smem);
   if (fit != 0) return fit;
   cudaError_t e = cudaSuccess;
@@ -550,6 +553,13 @@ int launch_fwd(const FwdParams& p, const void* wx, cudaStream_t stream) {
   }
   e = cudaLaunchKernelEx(&cfg, kern, p, map);
   return static_cast<int>(e);
+}
+
+template <int CELL, int BV, int U, bool WX_BF16, bool XG>
+int launch_fwd(const FwdParams& p, const void* wx, cudaStream_t stream) {
+  const bool ext = p.T_total != p.T || p.t0 != 0 || p.out_bf16 != 0 || p.fwd_clip < INFINITY;
+  return ext ? launch_fwd_ext<CELL, BV, U, WX_BF16, XG, true>(p, wx, stream)
+             : launch_fwd_ext<CELL, BV, U, WX_BF16, XG, false>(p, wx, stream);
 }
 
 template <int CELL, int BV, int U>

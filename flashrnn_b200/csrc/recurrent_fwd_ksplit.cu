@@ -333,7 +333,7 @@ frnn_fwd_ks_kernel(const FwdParams p, const __grid_constant__ CUtensorMap wx_map
 #pragma unroll
       for (int j = 0; j < NI; ++j) {
         cell_forward<CELL>(ry[j], wx[j], bias, st[j], cv[j], take_i);
-        st[j][0] = clip_sym(st[j][0], p.fwd_clip);
+        st[j][0] = fminf(fmaxf(st[j][0], -p.fwd_clip), p.fwd_clip);  // +inf when the clip is off
         hb16[j] = act[j] ? static_cast<uint32_t>(__bfloat16_as_ushort(__float2bfloat16_rn(st[j][0]))) : 0u;
       }
       const long long c5 = prof ? clock64() : 0;
