@@ -56,7 +56,9 @@ __device__ __forceinline__ void report_bks(int* err, int code, int detail) {
   __threadfence();
 }
 
-template <int CELL, int BV, int KS, bool WX_BF16>
+// OPTS: one of the v1 options (recurrent-gradient clip / cut, v1 sLSTM convention) is set; the plain instantiation
+// folds them away.
+template <int CELL, int BV, int KS, bool WX_BF16, bool OPTS>
 __global__ void __launch_bounds__(kThreads, 1)
 frnn_bwd_ks_kernel(const BwdParams p, const __grid_constant__ CUtensorMap cache_map,
                    const __grid_constant__ CUtensorMap hist_map, const __grid_constant__ CUtensorMap init_map,
@@ -289,7 +291,9 @@ frnn_bwd_ks_kernel(const BwdParams p, const __grid_constant__ CUtensorMap cache_
                           : 0u;
     }
     bool dead = false;  // after a failed wait the warp keeps walking through the loop without waiting
-    const bool clip_on = p.grad_clip > 0.0f;
+    const bool clip_on = OPTS && p.grad_clip > 0.0f;
+    const bool cut = OPTS && p.cut_recurrent != 0;
+    const bool slstm_v1 = OPTS && p.slstm_v1 != 0;
 
     float cache[NI][CT::GC], sn[NI][S], sp[NI][S], dhs[NI][S];
     auto load_stage = [&](int it) {
@@ -336,7 +340,7 @@ frnn_bwd_ks_kernel(const BwdParams p, const __grid_constant__ CUtensorMap cache_
 #pragma unroll
         for (int j = 0; j < NI; ++j) {
           const int ib = (ib0 + j * RPP) % BV;
-          if (p.cut_recurrent == 0) {
+          if (!cut) {
 #pragma unroll
             for (int src = 0; src < KS; ++src) ds[j][0] += pbuf[(src * BV + ib) * UO + ul];
           }
@@ -367,7 +371,7 @@ frnn_bwd_ks_kernel(const BwdParams p, const __grid_constant__ CUtensorMap cache_
 #pragma unroll
       for (int j = 0; j < NI; ++j) {
         float gb[CT::GB];
-        cell_backward<CELL>(cache[j], sp[j], sn[j], ds[j], gr[j], gw[j], gb, take_i, p.slstm_v1 != 0);
+        cell_backward<CELL>(cache[j], sp[j], sn[j], ds[j], gr[j], gw[j], gb, take_i, slstm_v1);
 #pragma unroll
         for (int q = 0; q < S; ++q) dcar[j][q] = ds[j][q];
         if (!act[j]) {
@@ -550,9 +554,9 @@ frnn_bwd_ks_kernel(const BwdParams p, const __grid_constant__ CUtensorMap cache_
   if (warp == 4) tmem_dealloc(tbase, tmem_cols);
 }
 
-template <int CELL, int BV, int KS, bool WX_BF16>
-int launch_bwd_ks(const BwdParams& p, const void* cache, const float* history, const float* initial,
-                  const float* d_history, cudaStream_t stream, int* capacity_only = nullptr) {
+template <int CELL, int BV, int KS, bool WX_BF16, bool OPTS>
+int launch_bwd_ks_opt(const BwdParams& p, const void* cache, const float* history, const float* initial,
+                      const float* d_history, cudaStream_t stream, int* capacity_only) {
   using Cfg = BksCfg<CELL, BV, KS, WX_BF16>;
   using CT = typename Cfg::CT;
   const int K = CT::GR * p.D;
@@ -581,7 +585,7 @@ int launch_bwd_ks(const BwdParams& p, const void* cache, const float* history, c
     const uint64_t dims1[5] = {uD, uN, 1u, uB, static_cast<uint64_t>(CT::S)};
     if (make_tensor_map(&init_map, initial, 4, 5, dims1, box) != 0) return -4;
   }
-  auto kern = frnn_bwd_ks_kernel<CELL, BV, KS, WX_BF16>;
+  auto kern = frnn_bwd_ks_kernel<CELL, BV, KS, WX_BF16, OPTS>;
   const int fit = fit_tmem_budget(kern, kThreads, tmem_cols_pow2(Cfg::A_COL0 + Kc / 2, 64u), &smem);
   if (fit != 0) return fit;
   cudaError_t e = cudaSuccess;
@@ -612,6 +616,14 @@ int launch_bwd_ks(const BwdParams& p, const void* cache, const float* history, c
   if (max_clusters * KS < static_cast<int>(cfg.gridDim.x)) return -2;
   e = cudaLaunchKernelEx(&cfg, kern, p, cache_map, hist_map, init_map, dhist_map);
   return static_cast<int>(e);
+}
+
+template <int CELL, int BV, int KS, bool WX_BF16>
+int launch_bwd_ks(const BwdParams& p, const void* cache, const float* history, const float* initial,
+                  const float* d_history, cudaStream_t stream, int* capacity_only = nullptr) {
+  const bool opts = p.grad_clip > 0.0f || p.cut_recurrent != 0 || p.slstm_v1 != 0;
+  return opts ? launch_bwd_ks_opt<CELL, BV, KS, WX_BF16, true>(p, cache, history, initial, d_history, stream, capacity_only)
+              : launch_bwd_ks_opt<CELL, BV, KS, WX_BF16, false>(p, cache, history, initial, d_history, stream, capacity_only);
 }
 
 template <int CELL, int KS>

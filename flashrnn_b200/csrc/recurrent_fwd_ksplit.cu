@@ -53,7 +53,9 @@ __device__ __forceinline__ void report_ks(int* err, int code, int detail) {
   __threadfence();
 }
 
-template <int CELL, int BV, int KS, bool WX_BF16>
+// EXT: the call is one chunk of a longer sequence (T_total, t0), stores bf16 snapshots or clips h_t; the plain
+// instantiation folds all three away.
+template <int CELL, int BV, int KS, bool WX_BF16, bool EXT>
 __global__ void __launch_bounds__(kThreads, 1)
 frnn_fwd_ks_kernel(const FwdParams p, const __grid_constant__ CUtensorMap wx_map) {
   using Cfg = KsCfg<CELL, BV, KS, WX_BF16>;
@@ -154,7 +156,8 @@ frnn_fwd_ks_kernel(const FwdParams p, const __grid_constant__ CUtensorMap wx_map
   float st[NI][CT::S];
   float bias[CT::GB];
   bool act[NI];
-  const int Tt = p.T_total, t0 = p.t0;
+  const int Tt = EXT ? p.T_total : T, t0 = EXT ? p.t0 : 0;
+  const bool out_bf16 = EXT && p.out_bf16 != 0;
   const size_t sBTND = static_cast<size_t>(B) * Tt * N * D;
   const size_t ND = static_cast<size_t>(N) * D;
 #pragma unroll
@@ -333,7 +336,7 @@ frnn_fwd_ks_kernel(const FwdParams p, const __grid_constant__ CUtensorMap wx_map
 #pragma unroll
       for (int j = 0; j < NI; ++j) {
         cell_forward<CELL>(ry[j], wx[j], bias, st[j], cv[j], take_i);
-        st[j][0] = fminf(fmaxf(st[j][0], -p.fwd_clip), p.fwd_clip);  // +inf when the clip is off
+        if constexpr (EXT) st[j][0] = fminf(fmaxf(st[j][0], -p.fwd_clip), p.fwd_clip);  // +inf when the clip is off
         hb16[j] = act[j] ? static_cast<uint32_t>(__bfloat16_as_ushort(__float2bfloat16_rn(st[j][0]))) : 0u;
       }
       const long long c5 = prof ? clock64() : 0;
@@ -408,7 +411,7 @@ frnn_fwd_ks_kernel(const FwdParams p, const __grid_constant__ CUtensorMap wx_map
 #pragma unroll
           for (int q = 0; q < CT::S; ++q) {
             if (q < hist_states) {
-              if (p.out_bf16) reinterpret_cast<__nv_bfloat16*>(p.history)[q * sBTND + hrow * ND + n * D + d0] = __float2bfloat16_rn(st[j][q]);
+              if (out_bf16) reinterpret_cast<__nv_bfloat16*>(p.history)[q * sBTND + hrow * ND + n * D + d0] = __float2bfloat16_rn(st[j][q]);
               else p.history[q * sBTND + hrow * ND + n * D + d0] = st[j][q];
             }
           }
@@ -438,7 +441,7 @@ frnn_fwd_ks_kernel(const FwdParams p, const __grid_constant__ CUtensorMap wx_map
           p.carry[static_cast<size_t>(q) * B * ND + static_cast<size_t>(b0 + ib0 + j * RPP) * ND + n * D + d0] = st[j][q];
         if (p.output_mode == 2) {  // "last": h of the final step as [B][1][N][D]
           const size_t at = static_cast<size_t>(b0 + ib0 + j * RPP) * ND + n * D + d0;
-          if (p.out_bf16) reinterpret_cast<__nv_bfloat16*>(p.history)[at] = __float2bfloat16_rn(st[j][0]);
+          if (out_bf16) reinterpret_cast<__nv_bfloat16*>(p.history)[at] = __float2bfloat16_rn(st[j][0]);
           else p.history[at] = st[j][0];
         }
       }
@@ -457,8 +460,8 @@ frnn_fwd_ks_kernel(const FwdParams p, const __grid_constant__ CUtensorMap wx_map
   if (warp == 4) tmem_dealloc(tbase, tmem_cols);
 }
 
-template <int CELL, int BV, int KS, bool WX_BF16>
-int launch_fwd_ks(const FwdParams& p, const void* wx, cudaStream_t stream, int* capacity_only = nullptr) {
+template <int CELL, int BV, int KS, bool WX_BF16, bool EXT>
+int launch_fwd_ks_ext(const FwdParams& p, const void* wx, cudaStream_t stream, int* capacity_only) {
   using Cfg = KsCfg<CELL, BV, KS, WX_BF16>;
   using CT = typename Cfg::CT;
   if (p.D % 32 != 0 || p.D % KS != 0 || (p.D / KS) % 16 != 0 || p.D / KS > kMaxKc) return -2;
@@ -471,7 +474,7 @@ int launch_fwd_ks(const FwdParams& p, const void* wx, cudaStream_t stream, int* 
                             static_cast<uint64_t>(p.T_total), static_cast<uint64_t>(p.B)};
   const uint32_t box[5] = {static_cast<uint32_t>(Cfg::UO), 1u, static_cast<uint32_t>(CT::GW), 1u, static_cast<uint32_t>(p.wx_box_b)};
   if (capacity_only == nullptr && make_tensor_map(&map, wx, Cfg::WX_ES, 5, dims, box) != 0) return -4;
-  auto kern = frnn_fwd_ks_kernel<CELL, BV, KS, WX_BF16>;
+  auto kern = frnn_fwd_ks_kernel<CELL, BV, KS, WX_BF16, EXT>;
   const int fit = fit_tmem_budget(kern, kThreads, tmem_cols_pow2(Cfg::A_COL0 + Kc / 2, 64u), &smem);
   if (fit != 0) return fit;
   cudaError_t e = cudaSuccess;
@@ -502,6 +505,13 @@ int launch_fwd_ks(const FwdParams& p, const void* wx, cudaStream_t stream, int* 
   if (max_clusters * KS < static_cast<int>(cfg.gridDim.x)) return -2;
   e = cudaLaunchKernelEx(&cfg, kern, p, map);
   return static_cast<int>(e);
+}
+
+template <int CELL, int BV, int KS, bool WX_BF16>
+int launch_fwd_ks(const FwdParams& p, const void* wx, cudaStream_t stream, int* capacity_only = nullptr) {
+  const bool ext = p.T_total != p.T || p.t0 != 0 || p.out_bf16 != 0 || p.fwd_clip < INFINITY;
+  return ext ? launch_fwd_ks_ext<CELL, BV, KS, WX_BF16, true>(p, wx, stream, capacity_only)
+             : launch_fwd_ks_ext<CELL, BV, KS, WX_BF16, false>(p, wx, stream, capacity_only);
 }
 
 template <int CELL, int KS>
@@ -543,6 +553,7 @@ int forward_ksplit_capacity(int cell, int bv, int ksplit, int D) {
   FwdParams p{};
   p.B = bv; p.T = 1; p.N = 1; p.D = D;
   p.T_total = 1;
+  p.fwd_clip = INFINITY;  // the plain instantiation
   p.wx_box_b = bv;
   int cap = 0;
   const int rc = forward_ksplit_dispatch(cell, p, nullptr, 1, bv, ksplit, nullptr, &cap);
