@@ -209,6 +209,8 @@ def main():
     ap.add_argument("--warmup", type=int, default=3)
     ap.add_argument("--impl", default="b200", choices=("b200", "reference"))
     ap.add_argument("--no-cpu-baseline", action="store_true")
+    ap.add_argument("--no-graph", action="store_true",
+                    help="time the resident step as eager launches only (default: also as a replayed CUDA graph)")
     ap.add_argument("--no-extras", action="store_true",
                     help="skip the extra keys (wide head, head-sharded configuration); used for profiler runs")
     args = ap.parse_args()
@@ -316,13 +318,66 @@ def main():
         torch.cuda.synchronize()
         return sum(e0.elapsed_time(e1) for e0, e1 in pairs)
 
+    def step_local():
+        # N > 1: this rank's shard WITHOUT the all-reduce; it follows each replay as an eager NCCL call on the same buffers
+        leaves = [t.detach().requires_grad_(True) for t in (d_wx, d_R, d_b, d_init)]
+        hist, _ = flashrnn(*leaves, function=CELL, backend="b200", dtype="bfloat16")
+        hist[0].sum().backward()
+        return leaves
+
+    def capture_step():
+        """The resident step (forward, loss, backward, dR/db) recorded once into a CUDA graph: the same launches on the
+        same buffers without the host work between them. With N > 1 the all-reduce of dR+db stays an eager call after
+        every replay (a collective inside the capture hung the two-GPU run). Returns a callable or None if refused."""
+        if args.no_graph:
+            return None
+        try:
+            body = step_resident if dist is None else step_local
+            side = torch.cuda.Stream(device=dev)
+            side.wait_stream(torch.cuda.current_stream(dev))
+            with torch.cuda.stream(side):
+                body()
+            torch.cuda.current_stream(dev).wait_stream(side)
+            torch.cuda.synchronize()
+            graph = torch.cuda.CUDAGraph()
+            with torch.cuda.graph(graph, capture_error_mode="thread_local"):   # other threads (NCCL's watchdog) may query events
+                held = body()
+
+            def replay():
+                graph.replay()
+                if dist is not None:
+                    from flashrnn_b200.sharding import allreduce_weight_grads
+                    allreduce_weight_grads(held[1].grad, held[2].grad, "batch")
+
+            graph.replay()   # without the collective: every rank decides for itself here
+            torch.cuda.synchronize()
+            poll_errors(block=True)
+            if not all(torch.isfinite(t.grad.float()).all() for t in held):
+                return None
+            return replay
+        except Exception as exc:  # an eager step is always available
+            print(f"bench.py: CUDA-graph capture of the step refused ({exc!r:.200}); timing eager launches", file=sys.stderr)
+            torch.cuda.synchronize()
+            return None
+
     for _ in range(args.warmup):
         step_resident()
     run_e2e(args.warmup)
     poll_errors(block=True)
+    graph = capture_step()
+    if dist is not None:   # all ranks time the same kind of step
+        agree = torch.tensor([1 if graph is not None else 0], device=dev)
+        dist.all_reduce(agree, op=dist.ReduceOp.MIN)
+        if int(agree.item()) == 0:
+            graph = None
+    if graph is not None:
+        for _ in range(args.warmup):
+            graph()
     barrier()
     with ClockSampler(local_rank) as clocks:
-        ms = timed(step_resident, args.steps)
+        ms_eager = timed(step_resident, args.steps)
+        barrier()
+        ms = timed(graph, args.steps) if graph is not None else ms_eager
         barrier()
         ms_e2e, _ = run_e2e(args.steps)
         barrier()
@@ -333,10 +388,10 @@ def main():
     if dist is not None:
         breakdown["allreduce_dR_db"] = time_allreduce(dev, dist, GR * N * D * D + 4 * N * D)
     del d_wx, h_wx, dev_sets
-    t_ms = torch.tensor([ms, ms_e2e], dtype=torch.float64, device=dev)
+    t_ms = torch.tensor([ms, ms_e2e, ms_eager], dtype=torch.float64, device=dev)
     if dist is not None:
         dist.all_reduce(t_ms, op=dist.ReduceOp.MAX)
-    ms, ms_e2e = (float(v) for v in t_ms.tolist())
+    ms, ms_e2e, ms_eager = (float(v) for v in t_ms.tolist())
     # side measurements come last, after every figure of the headline line is final
     proj = None if args.no_extras else with_input_projection(dev)
     infer = None if args.no_extras else inference_e2e(dev)
@@ -362,6 +417,12 @@ def main():
                     "d2h_bytes_per_step": 4,
                     "d2h_note": "training step: only the scalar loss returns to the host; history and gradients stay "
                                 "on the device"},
+            "launch": (("the step's launches recorded once into a CUDA graph and replayed"
+                        + ("; the all-reduce of dR+db follows each replay as an eager NCCL call" if world > 1 else ""))
+                       if graph is not None else "eager launches through flashrnn(...)"),
+            "eager": {"value": world * B * T * args.steps / (ms_eager * 1e-3), "unit": "(B*T)/s",
+                      "ms_per_step": ms_eager / args.steps,
+                      "note": "the same step as eager launches through flashrnn(...) + autograd"},
             "gpu_launches": args.steps * 5,
             "kernels_ms": breakdown,
             "roofline": {"bound": "tensor", "kernel": f"frnn_{dom}_kernel", "achieved": achieved, "peak": bf16_peak,

@@ -45,15 +45,32 @@ def _raise_device_error(err: torch.Tensor, what: str) -> None:
         )
 
 
+_captured_errors: list = []   # error words of launches recorded into CUDA graphs: (err, what), newest last
+
+
+def _capturing() -> bool:
+    return torch.cuda.is_available() and torch.cuda.is_current_stream_capturing()
+
+
 def _track(err: torch.Tensor, what: str) -> None:
-    """Remember an error word; it is read once the kernels that write it have finished."""
+    """Remember an error word; it is read once the kernels that write it have finished.
+
+    While a CUDA graph is being captured no event may be queried: the word (which every replay zeroes and rewrites)
+    is then kept for ``poll_errors(block=True)``."""
+    if _capturing():
+        _captured_errors.append((err, what))
+        del _captured_errors[:-256]
+        return
     ev = torch.cuda.Event()
     ev.record(torch.cuda.current_stream(err.device))
     _pending_errors.append((ev, err, what))
 
 
 def poll_errors(block: bool = False) -> None:
-    """Raise if a finished launch reported a device-side error. ``block=True`` waits for all."""
+    """Raise if a finished launch reported a device-side error. ``block=True`` waits for all, including the launches
+    of replayed CUDA graphs (their error words are only looked at here). A no-op while a graph is being captured."""
+    if _capturing():
+        return
     keep = []
     while _pending_errors:
         ev, err, what = _pending_errors.pop(0)
@@ -64,6 +81,11 @@ def poll_errors(block: bool = False) -> None:
         else:
             keep.append((ev, err, what))
     _pending_errors.extend(keep)
+    if block and _captured_errors:
+        for device in {err.device for err, _ in _captured_errors}:
+            torch.cuda.synchronize(device)
+        for err, what in _captured_errors:
+            _raise_device_error(err, what + " (in a replayed CUDA graph)")
 
 
 class _Recurrence(torch.autograd.Function):
