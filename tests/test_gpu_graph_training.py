@@ -9,6 +9,7 @@ import torch
 pytestmark = pytest.mark.gpu
 
 
+@pytest.mark.filterwarnings("ignore:The AccumulateGrad node")   # the warm-up step runs on a side stream on purpose
 @pytest.mark.parametrize("shape", [("lstm", 8, 48, 3, 256), ("gru", 16, 24, 1, 768), ("slstm", 6, 20, 2, 128)],
                          ids=lambda s: f"{s[0]}-B{s[1]}-T{s[2]}-N{s[3]}-D{s[4]}")
 def test_training_step_in_a_cuda_graph(shape, cuda_device):
