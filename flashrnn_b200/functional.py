@@ -15,6 +15,7 @@ stays connected to autograd.
 from __future__ import annotations
 
 from dataclasses import dataclass
+import time
 from typing import Optional
 
 import torch
@@ -27,6 +28,7 @@ BACKEND = "b200"
 _DTYPES = {"bfloat16": torch.bfloat16, "float32": torch.float32}
 
 _pending_errors: list = []
+_last_poll = 0.0
 
 
 def _ptr(t: Optional[torch.Tensor]):
@@ -48,8 +50,14 @@ def _raise_device_error(err: torch.Tensor, what: str) -> None:
 _captured_errors: list = []   # error words of launches recorded into CUDA graphs: (err, what), newest last
 
 
+_has_cuda: Optional[bool] = None
+
+
 def _capturing() -> bool:
-    return torch.cuda.is_available() and torch.cuda.is_current_stream_capturing()
+    global _has_cuda
+    if _has_cuda is None:   # asked once: the availability check costs microseconds on every call otherwise
+        _has_cuda = torch.cuda.is_available()
+    return _has_cuda and torch.cuda.is_current_stream_capturing()
 
 
 def _track(err: torch.Tensor, what: str) -> None:
@@ -71,6 +79,14 @@ def poll_errors(block: bool = False) -> None:
     of replayed CUDA graphs (their error words are only looked at here). A no-op while a graph is being captured."""
     if _capturing():
         return
+    global _last_poll
+    if not block:
+        # reading an error word back costs a device-to-host copy (tens of microseconds): the non-blocking check at the
+        # start of every call looks at most once per 20 ms; the words wait in the queue until then
+        now = time.monotonic()
+        if now - _last_poll < 0.02:
+            return
+        _last_poll = now
     keep = []
     while _pending_errors:
         ev, err, what = _pending_errors.pop(0)
