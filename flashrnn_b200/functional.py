@@ -128,7 +128,8 @@ class _Recurrence(torch.autograd.Function):
         if not plan.supported:
             raise ValueError(
                 f"flashrnn_b200: cell={cell} D={D} is outside the sm_100a kernel family "
-                f"(the recurrent matrix of a head must fit the tensor memory of the CTAs of one launch: D <= 1792)"
+                f"(the recurrent matrix of a head must fit the tensor memory of the CTAs of one launch: D <= 1792; wider heads "
+                f"run through the row-sharded kernels when D is a multiple of 256)"
             )
         history = torch.empty((S, B, T, N, D), dtype=torch.float32, device=dev)
         carry = torch.empty((S, B, 1, N, D), dtype=torch.float32, device=dev)
@@ -248,6 +249,49 @@ def _run(wx, recurrent, bias, initial, cell: str, zero_normalizer: Optional[bool
         return _run_on_current_device(wx, recurrent, bias, initial, cell, zero_normalizer, options)
 
 
+_wide_heads: dict = {}   # (cell, B, T, D, device, Wx dtype) -> [WideHead with all of its ranks on this GPU, ...]
+
+
+def _run_wide(wx, recurrent, bias, initial, cell: str, zero_first: bool):
+    """Heads wider than the single-GPU kernel family (1792 < D, D a multiple of 256) on ONE GPU: every head goes through
+    the row-sharded kernels with a single rank (their K split inside clusters and weight ring take over), at most 32
+    batch rows per launch. The reference covers D <= 2048 on one device with its hybrid kernels
+    (flashrnn/flashrnn2/hybrid_fw2d.py:20-23)."""
+    from .wide_head import WideHead
+
+    B, T, _, N, D = wx.shape
+    dev = wx.device
+
+    def head_for(rows: int) -> "WideHead":
+        # A head's exchange buffers double as the saved operands of its backward pass: one that still has a backward
+        # pending (`in_use`) is not given out again; pools grow to what one training step needs and are then reused.
+        key = (cell, rows, T, D, dev.index, wx.dtype)
+        pool = _wide_heads.setdefault(key, [])
+        for head in pool:
+            if not head.in_use:
+                return head
+        if sum(len(p) for p in _wide_heads.values()) >= 16:   # other shapes' idle heads make room
+            for other in _wide_heads.values():
+                for head in [h for h in other if not h.in_use]:
+                    other.remove(head)
+                    head.close()
+        pool.append(WideHead(cell, rows, T, D, emulate_ranks=1, device=dev, wx_dtype=wx.dtype))
+        return pool[-1]
+
+    per_head = []
+    for n in range(N):
+        pieces = []
+        for i in range(0, B, 32):
+            j = min(B, i + 32)
+            pieces.append(head_for(j - i)(wx[i:j, :, :, n:n + 1], recurrent[:, n:n + 1], bias[:, n:n + 1],
+                                          initial[:, i:j, :, n:n + 1], zero_normalizer=zero_first))
+        per_head.append((torch.cat([h for h, _ in pieces], dim=1), torch.cat([c for _, c in pieces], dim=1))
+                        if len(pieces) > 1 else pieces[0])
+    if N == 1:
+        return per_head[0]
+    return torch.cat([h for h, _ in per_head], dim=3), torch.cat([c for _, c in per_head], dim=3)
+
+
 def _run_on_current_device(wx, recurrent, bias, initial, cell: str, zero_normalizer: Optional[bool], options=None):
     D = wx.shape[-1]
     if cell != "slstm":
@@ -256,6 +300,8 @@ def _run_on_current_device(wx, recurrent, bias, initial, cell: str, zero_normali
         zero_first = bool(zero_normalizer)  # predicate of the whole logical call, given by a sharding caller
     else:
         zero_first = bool(torch.all(initial[2] == 0))
+    if D > 1792 and D % 256 == 0 and options is None and wx.dtype in (torch.float32, torch.bfloat16):
+        return _run_wide(wx, recurrent, bias, initial, cell, zero_first)
     # The kernels tile the head width in multiples of 16 (heads wider than 768: 64, and 128 where only the
     # column-owning backward fits); the smallest such width that a launch supports is used.
     pad = (-D) % 16

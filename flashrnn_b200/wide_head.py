@@ -48,6 +48,7 @@ class WideHead:
         self.profile = False   # True: CTA 0 of the forward adds up its in-kernel phase timers into last_err[8..19]
         self.last_err = None
         self.jitter = 0        # test hook (race verification): seed of pseudo-random stalls inside both kernels, 0 = off
+        self.in_use = False    # True from a training forward until its autograd node is gone (backward done or graph dropped)
         self._owned = []      # cudaMalloc'ed slabs of this process
         self._opened = []     # peer mappings
         gr = SIZES[cell][0]
@@ -189,6 +190,18 @@ class WideHead:
             return _WideRecurrence.apply(Wx, R_rows, b.to(torch.float32), states.to(torch.float32), self, zero_first)
 
 
+class _Lease:
+    """Held by the autograd node of a training forward: the head's exchange buffers are the saved operands of its
+    backward pass, so the head must not run another forward until the node is gone."""
+
+    def __init__(self, head: WideHead):
+        self.head = head
+        head.in_use = True
+
+    def __del__(self):
+        self.head.in_use = False
+
+
 def _as_tensor(ptr: int, numel: int, dtype, device) -> torch.Tensor:
     """A torch view of raw device memory owned by the library's peer allocator."""
     itemsize = torch.empty((), dtype=dtype).element_size()
@@ -219,6 +232,8 @@ class _WideRecurrence(torch.autograd.Function):
             history = torch.empty((S, B, T, 1, lw), dtype=torch.float32, device=dev)
             carry = torch.empty((S, B, 1, 1, lw), dtype=torch.float32, device=dev)
             train = any(ctx.needs_input_grad[:4])
+            if train:
+                ctx.lease = _Lease(head)
             cache = torch.empty(head.plan.cache_bytes, dtype=torch.uint8, device=dev) if train and head.plan.cache_bytes else None
             err = torch.zeros(32, dtype=torch.int32, device=dev)
             if head.profile:

@@ -168,3 +168,31 @@ def test_two_gpus_one_process_each(cell, B, T, D, bf):
         p.join(timeout=120)
         assert p.exitcode == 0
     assert all(ok for _, ok, _ in results), results
+
+
+@pytest.mark.parametrize("case", [("lstm", 5, 6, 2, 2048, False), ("gru", 40, 4, 1, 2048, True)],
+                         ids=lambda c: f"{c[0]}-B{c[1]}-T{c[2]}-N{c[3]}-D{c[4]}-{'bf16' if c[5] else 'f32'}")
+def test_public_call_takes_heads_wider_than_1792(case, cuda_device):
+    """``flashrnn`` / ``flashrnn_torch`` route heads of 2048 units (several heads, more than 32 batch rows) through the
+    row-sharded kernels on one GPU; results against the oracle."""
+    from flashrnn_b200 import flashrnn, flashrnn_torch, poll_errors
+    from flashrnn_b200.workloads import make_inputs
+
+    cell, B, T, N, D, bf = case
+    wx, R, b, init = make_inputs(cell, B, T, N, D, 77)
+    S = port.SIZES[cell][3]
+    gen = torch.Generator().manual_seed(78)
+    d_history = torch.randn((S, B, T, N, D), generator=gen)
+    d_carry = torch.randn((S, B, 1, N, D), generator=gen)
+    wx_seen = wx.bfloat16().float() if bf else wx
+    ref_h, ref_c, ref_g = port.forward_backward(wx_seen, R, b, init, cell, d_history, d_carry)
+    leaves = [t.to(cuda_device).requires_grad_(True) for t in (wx.bfloat16() if bf else wx, R, b, init)]
+    if bf:
+        h, c = flashrnn(*leaves, function=cell, backend="b200", dtype="bfloat16")
+    else:
+        h, c = flashrnn_torch(*leaves, cell=cell, numerics="fp32_state_bf16_mma")
+    ((h * d_history.to(cuda_device)).sum() + (c * d_carry.to(cuda_device)).sum()).backward()
+    torch.cuda.synchronize()
+    poll_errors(block=True)
+    assert h.shape == (S, B, T, N, D) and c.shape == (S, B, 1, N, D)
+    _check(str(case), [h, c] + [t.grad for t in leaves], [ref_h, ref_c] + list(ref_g))
