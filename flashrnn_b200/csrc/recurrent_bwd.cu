@@ -294,7 +294,7 @@ frnn_bwd_kernel(const BwdParams p, const __grid_constant__ CUtensorMap cache_map
       for (int j = 0; j < IPT; ++j) dh_ext[j] = 0.0f;
       if (it < T) {
         const int s = it % Cfg::NST;
-        if (!dead && !mbar_wait_bounded<false>(smem_u32(&s_full[s]), (it / Cfg::NST) & 1, limit, abort_flag)) {
+        if (!dead && !mbar_wait_bounded<false, true>(smem_u32(&s_full[s]), (it / Cfg::NST) & 1, limit, abort_flag)) {
           report(p.err, kErrWaitWx, it);
           dead = true;
         }
@@ -506,7 +506,7 @@ frnn_bwd_kernel(const BwdParams p, const __grid_constant__ CUtensorMap cache_map
       const uint32_t part_base = smem_u32(part) + static_cast<uint32_t>(nb) * part_bytes + static_cast<uint32_t>(rank) * BV * U * 4;
       const uint32_t bar_local = smem_u32(&s_part_bar[nb]);
       for (int j = 0; j < MTB; ++j) {
-        if (!dead && !mbar_wait_bounded<false>(smem_u32(&s_mma_bar[j]), it & 1, limit, abort_flag)) {
+        if (!dead && !mbar_wait_bounded<false, true>(smem_u32(&s_mma_bar[j]), it & 1, limit, abort_flag)) {
           report(p.err, kErrWaitMma, it);
           dead = true;
         }

@@ -298,7 +298,7 @@ frnn_bwd_ks_kernel(const BwdParams p, const __grid_constant__ CUtensorMap cache_
     float cache[NI][CT::GC], sn[NI][S], sp[NI][S], dhs[NI][S];
     auto load_stage = [&](int it) {
       const int s = it % Cfg::NST;
-      if (!dead && !mbar_wait_bounded<false>(smem_u32(&s_full[s]), (it / Cfg::NST) & 1, limit, abort_flag)) {
+      if (!dead && !mbar_wait_bounded<false, true>(smem_u32(&s_full[s]), (it / Cfg::NST) & 1, limit, abort_flag)) {
         report_bks(p.err, kErrWaitWx, it);
         dead = true;
       }
@@ -332,7 +332,7 @@ frnn_bwd_ks_kernel(const BwdParams p, const __grid_constant__ CUtensorMap cache_
         for (int q = 0; q < S; ++q) ds[j][q] = dcar[j][q] + (it < T ? dhs[j][q] : 0.0f);
       if (it >= 1) {
         // partial dh of this step from the KS CTAs of the cluster
-        if (!dead && !mbar_wait_bounded<true, false>(smem_u32(&s_part_bar[pb]), ((it - 1) >> 1) & 1, limit, abort_flag)) {
+        if (!dead && !mbar_wait_bounded<true, true>(smem_u32(&s_part_bar[pb]), ((it - 1) >> 1) & 1, limit, abort_flag)) {
           report_bks(p.err, kErrWaitPart, it);
           dead = true;
         }
@@ -493,7 +493,7 @@ frnn_bwd_ks_kernel(const BwdParams p, const __grid_constant__ CUtensorMap cache_
       }
       const long long c4 = prof ? clock64() : 0;
       const long long c5 = c4;
-      if (!dead && !mbar_wait_bounded<false>(smem_u32(&s_mma_bar), it & 1, limit, abort_flag)) {
+      if (!dead && !mbar_wait_bounded<false, true>(smem_u32(&s_mma_bar), it & 1, limit, abort_flag)) {
         report_bks(p.err, kErrWaitMma, it);
         dead = true;
       }

@@ -283,7 +283,7 @@ frnn_fwd_kernel(const FwdParams p, const __grid_constant__ CUtensorMap wx_map) {
       if (kJitter && jitter != 0u) jitter_stall(jitter, 0u, static_cast<uint32_t>(t));
       const int s = t % kWxStages;
       const long long c0 = prof ? clock64() : 0;
-      if (!dead && !mbar_wait_bounded<false>(smem_u32(&s_wx_full[s]), (t / kWxStages) & 1, limit, abort_flag)) {
+      if (!dead && !mbar_wait_bounded<false, true>(smem_u32(&s_wx_full[s]), (t / kWxStages) & 1, limit, abort_flag)) {
         report(p.err, kErrWaitWx, t);
         dead = true;
       }
@@ -299,7 +299,7 @@ frnn_fwd_kernel(const FwdParams p, const __grid_constant__ CUtensorMap wx_map) {
         }
       }
       mbar_arrive(smem_u32(&s_wx_empty[s]));
-      if (!dead && !mbar_wait_bounded<false>(smem_u32(&s_mma_bar), t & 1, limit, abort_flag)) {
+      if (!dead && !mbar_wait_bounded<false, true>(smem_u32(&s_mma_bar), t & 1, limit, abort_flag)) {
         report(p.err, kErrWaitMma, t);
         dead = true;
       }

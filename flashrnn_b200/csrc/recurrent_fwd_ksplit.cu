@@ -261,7 +261,7 @@ frnn_fwd_ks_kernel(const FwdParams p, const __grid_constant__ CUtensorMap wx_map
       if (kJitter && jitter != 0u) jitter_stall(jitter, 0u, static_cast<uint32_t>(t));
       const int s = t % kWxStages, pb = t & 1;
       const long long c0 = prof ? clock64() : 0;
-      if (!dead && !mbar_wait_bounded<false>(smem_u32(&s_wx_full[s]), (t / kWxStages) & 1, limit, abort_flag)) {
+      if (!dead && !mbar_wait_bounded<false, true>(smem_u32(&s_wx_full[s]), (t / kWxStages) & 1, limit, abort_flag)) {
         report_ks(p.err, kErrWaitWx, t);
         dead = true;
       }
@@ -282,7 +282,7 @@ frnn_fwd_ks_kernel(const FwdParams p, const __grid_constant__ CUtensorMap wx_map
       }
       mbar_arrive(smem_u32(&s_wx_empty[s]));
       const long long c1 = prof ? clock64() : 0;
-      if (!dead && !mbar_wait_bounded<false>(smem_u32(&s_mma_bar), t & 1, limit, abort_flag)) {
+      if (!dead && !mbar_wait_bounded<false, true>(smem_u32(&s_mma_bar), t & 1, limit, abort_flag)) {
         report_ks(p.err, kErrWaitMma, t);
         dead = true;
       }
@@ -305,7 +305,7 @@ frnn_fwd_ks_kernel(const FwdParams p, const __grid_constant__ CUtensorMap wx_map
         }
       }
       const long long c3 = prof ? clock64() : 0;
-      if (!dead && !mbar_wait_bounded<true, false>(smem_u32(&s_part_bar[pb]), (t >> 1) & 1, limit, abort_flag)) {
+      if (!dead && !mbar_wait_bounded<true, true>(smem_u32(&s_part_bar[pb]), (t >> 1) & 1, limit, abort_flag)) {
         report_ks(p.err, kErrWaitPart, t);
         dead = true;
       }

@@ -352,7 +352,7 @@ frnn_bwd_mg_kernel(const MgBwdParams p, const __grid_constant__ CUtensorMap cach
         dead = true;
       }
       const int s = it % Cfg::NST;
-      if (it < T && !dead && !mbar_wait_bounded<false>(smem_u32(&s_full[s]), (it / Cfg::NST) & 1, limit, abort_flag)) {
+      if (it < T && !dead && !mbar_wait_bounded<false, true>(smem_u32(&s_full[s]), (it / Cfg::NST) & 1, limit, abort_flag)) {
         mg_report(p.err, kErrWaitWx, it);
         dead = true;
       }

@@ -379,7 +379,7 @@ frnn_fwd_mg_kernel(const MgFwdParams p, const __grid_constant__ CUtensorMap wx_m
     for (int t = 0; t < T; ++t) {
       if (kJitter && jitter != 0u) jitter_stall(jitter, 0u, static_cast<uint32_t>(t));
       const int s = t % Cfg::NWX, pb = t & 1;
-      if (!dead && !mbar_wait_bounded<false>(smem_u32(&s_wx_full[s]), (t / Cfg::NWX) & 1, limit, abort_flag)) {
+      if (!dead && !mbar_wait_bounded<false, true>(smem_u32(&s_wx_full[s]), (t / Cfg::NWX) & 1, limit, abort_flag)) {
         mg_report(p.err, kErrWaitWx, t);
         dead = true;
       }
