@@ -46,7 +46,7 @@ REFERENCE_BUDGET_S = 150.0                      # wall-clock budget of the refer
 # dram__bytes_read.sum + dram__bytes_write.sum per launch on this workload. NOT measured by this run: quoted from
 # the ncu capture summarised in the profile below (bench.py cannot run ncu on itself); re-capture when a kernel changes.
 NCU_TRAFFIC_PROFILE = "profiles/recurrence_kernels_cfg2_lstm_bf16_B8_T1024_N3_D256.md"
-NCU_TRAFFIC_BYTES = {"fwd": 52.1e6 + 62.7e6, "bwd": 152.8e6 + 32.1e6, "wgrad": 63.0e6 + 2.7e6}
+NCU_TRAFFIC_BYTES = {"fwd": 52.0e6 + 62.5e6, "bwd": 152.7e6 + 32.9e6, "wgrad": 63.0e6 + 2.1e6}
 
 
 def _peaks():
