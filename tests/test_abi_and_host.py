@@ -102,3 +102,41 @@ def test_wide_head_batches_are_split_over_launches():
     assert heads == 1 and rows == 16 and _lib.plan("gru", rows, 4, heads, 1280).supported
     assert functional._launch_split("lstm", 8, 8, 1, 2048) == (1, 8)
 
+
+
+def test_error_polling_on_the_host(monkeypatch):
+    """The bookkeeping around the device error words: nothing is queried while a CUDA graph is being captured, the
+    non-blocking check is rate-limited, a blocking check also reads the words of captured launches."""
+    import torch
+
+    from flashrnn_b200 import functional as F
+
+    class _Done:                       # stands in for a CUDA event that has completed
+        def synchronize(self): pass
+        def query(self): return True
+
+    monkeypatch.setattr(F, "_pending_errors", [])
+    monkeypatch.setattr(F, "_captured_errors", [])
+    monkeypatch.setattr(F, "_last_poll", 0.0)
+    bad = torch.tensor([101, 7, 3] + [0] * 29, dtype=torch.int32)
+
+    # while capturing: neither recorded as an event nor looked at
+    monkeypatch.setattr(F, "_capturing", lambda: True)
+    F._track(bad, "captured launch")
+    assert F._pending_errors == [] and len(F._captured_errors) == 1
+    F.poll_errors(block=True)          # a no-op during capture
+    monkeypatch.setattr(F, "_capturing", lambda: False)
+
+    # outside: the non-blocking poll looks at most once per 20 ms ...
+    F._pending_errors.append((_Done(), torch.zeros(32, dtype=torch.int32), "fine launch"))
+    F.poll_errors()
+    assert F._pending_errors == []
+    F._pending_errors.append((_Done(), bad, "eager launch"))
+    F.poll_errors()                    # within 20 ms of the previous look: the word stays queued
+    assert len(F._pending_errors) == 1
+    # ... the blocking one always does, and reports code, step and CTA
+    with pytest.raises(RuntimeError, match="eager launch.*code 101.*step 7, CTA 3"):
+        F.poll_errors(block=True)
+    monkeypatch.setattr(torch.cuda, "synchronize", lambda device=None: None)
+    with pytest.raises(RuntimeError, match="captured launch.*replayed CUDA graph"):
+        F.poll_errors(block=True)
